@@ -1,0 +1,136 @@
+"""Flat parameter / gradient / optimizer-state storage with an ownership map.
+
+All parameters of the model are re-pointed into one flat fp32 buffer, their gradients into a second
+one and the optimizer moments into three more (AdamW ``exp_avg`` / ``exp_avg_sq``, Muon ``buf``), all with
+the same element offsets.  A bf16 *shadow* of the parameters with the same offsets feeds the tensor-core
+GEMMs, so no per-use fp32 -> bf16 cast of a weight ever runs.
+
+Every parameter tensor is owned by exactly one data-parallel rank.  The buffers are laid out owner by
+owner, and inside an owner by optimizer group (Muon matrices, AdamW with decay, AdamW without decay), so
+
+* the reduce-scatter of gradients is "rank r sums segment r of every rank's gradient buffer",
+* AdamW runs as a flat elementwise kernel over (at most) two contiguous ranges per owner,
+* the parameter all-gather is "rank r publishes segment r".
+
+Ownership balances the estimated Newton-Schulz FLOPs of the Muon matrices first (they dominate the
+optimizer cost) and the byte count of the AdamW tensors second, with a longest-processing-time greedy.
+Muon needs whole matrices, which is why the unit of ownership is a parameter tensor and not a byte range.
+With ``world == 1`` there is a single segment and the layout degenerates to one flat buffer.
+"""
+from dataclasses import dataclass
+
+import torch
+
+from ..optim.hybrid import split_parameters
+
+UNIT_ALIGN = 64          # elements; keeps every tensor 256-byte aligned in fp32 and 128-byte aligned in bf16
+SEGMENT_ALIGN = 1024
+GROUPS = ("muon", "decay", "no_decay")
+
+
+@dataclass
+class Unit:
+    name: str
+    param: torch.nn.Parameter
+    group: str
+    index: int          # registration order
+    owner: int = 0
+    offset: int = 0
+
+    @property
+    def numel(self):
+        return self.param.numel()
+
+
+def newton_schulz_flops(shape, steps=5):
+    """FLOPs of the NS chain for a stack of matrices ``[..., rows, cols]``."""
+    rows, cols = shape[-2], shape[-1]
+    m, n = min(rows, cols), max(rows, cols)
+    stack = 1
+    for d in shape[:-2]:
+        stack *= d
+    return stack * steps * (4 * m * m * n + 2 * m ** 3)
+
+
+def assign_owners(units, world):
+    """Longest-processing-time greedy; deterministic, so every rank derives the same map."""
+    load = [0.0] * world
+
+    def place(batch, cost):
+        for unit in sorted(batch, key=lambda u: (-cost(u), u.index)):
+            owner = min(range(world), key=lambda r: (load[r], r))
+            unit.owner = owner
+            load[owner] += cost(unit)
+
+    place([u for u in units if u.group == "muon"], lambda u: float(newton_schulz_flops(tuple(u.param.shape))))
+    # AdamW is bandwidth bound: ~16 bytes per element; scale so that it only breaks ties between Muon loads.
+    place([u for u in units if u.group != "muon"], lambda u: 16.0 * u.numel)
+    return load
+
+
+def _align(x, a):
+    return (x + a - 1) // a * a
+
+
+class ParamArena:
+    def __init__(self, model, device, world=1, muon=True, allocate=None):
+        """`allocate(numel, dtype)` returns a zero-filled flat tensor (peer-mapped memory for the p2p engine)."""
+        self.device, self.world = torch.device(device), world
+        allocate = allocate or (lambda numel, dtype: torch.zeros(numel, dtype=dtype, device=self.device))
+        matrices, decay, no_decay = split_parameters(model, muon)
+        order = {name: i for i, (name, _) in enumerate(model.named_parameters())}
+        self.units = [Unit(n, p, g, order[n]) for g, items in zip(GROUPS, (matrices, decay, no_decay)) for n, p in items]
+        self.load = assign_owners(self.units, world)
+        self.units.sort(key=lambda u: (u.owner, GROUPS.index(u.group), u.index))
+        # layout
+        self.segments = []                       # per owner: (start, end)
+        self.group_ranges = {}                   # (owner, group) -> (start, end)
+        cursor = 0
+        for owner in range(world):
+            start = cursor
+            for group in GROUPS:
+                g0 = cursor
+                for unit in (u for u in self.units if u.owner == owner and u.group == group):
+                    unit.offset = cursor
+                    cursor = _align(cursor + unit.numel, UNIT_ALIGN)
+                self.group_ranges[(owner, group)] = (g0, cursor)
+            cursor = _align(cursor, SEGMENT_ALIGN)
+            self.segments.append((start, cursor))
+        self.numel = cursor
+        self.params = allocate(self.numel, torch.float32)
+        self.grads = allocate(self.numel, torch.float32)
+        self.exp_avg = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
+        self.exp_avg_sq = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
+        self.muon_buf = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
+        self.shadow = torch.zeros(self.numel, dtype=torch.bfloat16, device=self.device) if self.device.type == "cuda" else None
+        with torch.no_grad():
+            for unit in self.units:
+                p = unit.param
+                view = self.view(self.params, unit)
+                view.copy_(p.data)
+                p.data = view
+                p.grad = self.view(self.grads, unit)
+                if self.shadow is not None:
+                    p._q38_bf16 = self.view(self.shadow, unit)
+        self.by_name = {u.name: u for u in self.units}
+        self.refresh_shadow()
+
+    def view(self, flat, unit):
+        return flat[unit.offset:unit.offset + unit.numel].view(unit.param.shape)
+
+    def owned(self, rank, group=None):
+        return [u for u in self.units if u.owner == rank and (group is None or u.group == group)]
+
+    def refresh_shadow(self, rank=None):
+        """Re-derive the bf16 shadow from the fp32 parameters (all of it, or one owner's segment)."""
+        if self.shadow is None:
+            return
+        s, e = (0, self.numel) if rank is None else self.segments[rank]
+        self.shadow[s:e].copy_(self.params[s:e])
+
+    def zero_grad(self):
+        self.grads.zero_()
+
+    def describe(self):
+        per_owner = [sum(u.numel for u in self.units if u.owner == r) for r in range(self.world)]
+        return dict(numel=self.numel, world=self.world, owner_numel=per_owner, owner_cost=self.load)

@@ -1,0 +1,144 @@
+"""Data-parallel gradient engine with owner-computes optimizer.
+
+One optimizer step on `world` ranks:
+
+1. every rank accumulates its micro-batch gradients into its flat gradient arena (`ParamArena`);
+2. **reduce-scatter**: rank r obtains the mean over ranks of segment r of the gradient arena;
+3. the global gradient norm is the root of the all-reduced sum of the per-segment squared norms; the
+   clip coefficient ``min(1, clip / (norm + 1e-6))`` is folded into the update;
+4. **owner computes**: rank r runs AdamW / Muon on the parameters of segment r only;
+5. **all-gather**: rank r publishes its updated fp32 parameters (and bf16 shadow) to every rank.
+
+Replicas are bit-identical after every step because each parameter is updated by exactly one rank from
+one reduced gradient and then copied.  The result equals DDP with replicated optimizers up to the
+summation order of the gradient mean (reference: DDP wiring at q38/train.py:472-479, update order
+clip -> AdamW -> Muon at q38/train.py:558-559).
+
+Transports
+  ``p2p``         hand-written sm_100a kernels reading/writing peer GPUs' arenas over NVLink
+                  (`q38.parallel.p2p`); launched on a side stream so they overlap the tail of backward.
+  ``collective``  `torch.distributed` reduce / broadcast per segment (NCCL on GPUs, gloo on CPU).  This is the
+                  baseline transport and the one the CPU multi-process tests exercise.
+"""
+import torch
+import torch.distributed as dist
+
+from ..optim.hybrid import HybridOptimizer
+from .arena import ParamArena
+
+
+class GradEngine:
+    def __init__(self, model, device, rank=0, world=1, mode="auto", lr=1e-3, weight_decay=0.1, muon=True):
+        self.model, self.device, self.rank, self.world = model, torch.device(device), rank, world
+        if mode == "auto":
+            mode = "p2p" if (world > 1 and self.device.type == "cuda") else "collective"
+        self.mode = mode
+        self.transport = None
+        allocate = None
+        if world > 1 and mode == "p2p":
+            from .p2p import PeerTransport
+            self.transport = PeerTransport(self.device, rank, world)
+            allocate = self.transport.allocate
+        if world > 1:
+            # rank 0's initial weights win, as with DDP's construction-time broadcast
+            for p in model.parameters():
+                dist.broadcast(p.data, 0)
+        self.arena = ParamArena(model, self.device, world, muon=muon, allocate=allocate)
+        self.optimizer = HybridOptimizer(model, lr=lr, weight_decay=weight_decay, muon=muon, arena=self.arena, rank=rank)
+        if self.transport is not None:
+            self.transport.bind(self.arena)
+        self._last = True
+
+    # ------------------------------------------------------------------ step protocol
+    def set_lr(self, lr):
+        for group in self.optimizer.param_groups:
+            group["lr"] = lr
+
+    def begin_micro_step(self, last):
+        self._last = last
+
+    def zero_grad(self):
+        self.arena.zero_grad()
+
+    def _reduce_scatter(self):
+        if self.world == 1:
+            return
+        if self.transport is not None:
+            self.transport.reduce_scatter_mean()
+            return
+        for owner, (s, e) in enumerate(self.arena.segments):
+            if e > s:
+                dist.reduce(self.arena.grads[s:e], dst=owner, op=dist.ReduceOp.SUM)
+        s, e = self.arena.segments[self.rank]
+        self.arena.grads[s:e].div_(self.world)
+
+    def _all_gather(self):
+        if self.world == 1:
+            self.arena.refresh_shadow()
+            return
+        if self.transport is not None:
+            self.transport.all_gather_params()
+            return
+        for owner, (s, e) in enumerate(self.arena.segments):
+            if e > s:
+                dist.broadcast(self.arena.params[s:e], src=owner)
+        self.arena.refresh_shadow()
+
+    def grad_norm(self):
+        s, e = self.arena.segments[self.rank]
+        sq = self.arena.grads[s:e].double().pow(2).sum() if self.device.type == "cpu" else self._sumsq(s, e)
+        if self.world > 1:
+            sq = sq.clone()
+            dist.all_reduce(sq)
+        return sq.sqrt().float()
+
+    def _sumsq(self, s, e):
+        from .. import ops
+        return ops.sum_squares(self.arena.grads[s:e])
+
+    def finish_step(self, clip):
+        """Reduce, clip, update owned parameters, publish them, clear gradients.  Returns the pre-clip gradient norm."""
+        self._reduce_scatter()
+        norm = self.grad_norm()
+        scale = None
+        if clip and clip > 0:
+            scale = (clip / (norm + 1e-6)).clamp(max=1.0)
+        self.optimizer.step(grad_scale=scale)
+        self._all_gather()
+        self.zero_grad()
+        return norm
+
+    def average_metrics(self, values):
+        """Mean over ranks of the loss terms; the last entry (gradient norm) is already global."""
+        if self.world > 1:
+            head = values[:-1].clone()
+            dist.all_reduce(head)
+            values = torch.cat([head / self.world, values[-1:]])
+        return values
+
+    # ------------------------------------------------------------------ checkpoints
+    def checkpoint_state(self):
+        """(model state_dict, optimizer state_dict) with the layout of a replicated run.
+
+        Optimizer moments are only maintained by the owner of each parameter; before rank 0 serialises them
+        every owner publishes its segments (a collective, so all ranks must call this)."""
+        if self.world > 1:
+            for flat in (self.arena.exp_avg, self.arena.exp_avg_sq, self.arena.muon_buf):
+                for owner, (s, e) in enumerate(self.arena.segments):
+                    if e > s:
+                        dist.broadcast(flat[s:e], src=owner)
+        return self.model.state_dict(), self.optimizer.state_dict()
+
+    def load_checkpoint(self, model_state, opt_state):
+        self.model.load_state_dict(model_state)
+        self.optimizer.load_state_dict(opt_state)
+        self.arena.refresh_shadow()
+
+    def describe(self):
+        info = self.arena.describe()
+        return f"{self.mode} world={self.world} arena={info['numel'] / 1e6:.1f}M elements owner_numel={info['owner_numel']}"
+
+    def close(self):
+        if self.transport is not None:
+            self.transport.close()
+            self.transport = None

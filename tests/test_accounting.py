@@ -1,0 +1,81 @@
+"""Ledger and preset checks (behavioural counterparts of the reference's tests/test_presets.py and
+tests/test_flops_audit.py)."""
+import copy
+import json
+
+import pytest
+
+from q38.flops import _count_backbone, count, validate_resume_accounting
+from q38.presets import ROOT, budget_tokens, load_preset, model_config, preset_budget, preset_names
+
+EXPECTED_TRAIN_FLOPS = {"q38_c1": 291_721_216, "q38_c2": 486_353_152, "q38_c3": 1_057_826_304, "q38_c4": 2_284_543_232}
+EXPECTED_PARAMS = {"q38_c1": 167_752_070, "q38_c2": 326_609_782, "q38_c3": 778_030_326, "q38_c4": 1_804_657_560}
+
+
+def small():
+    return dict(hidden_size=128, num_hidden_layers=4, vocab_size=10112, num_experts=64, num_experts_per_tok=4,
+                moe_intermediate_size=64, shared_expert_intermediate_size=64, num_attention_heads=4,
+                num_key_value_heads=1, head_dim=64, linear_num_key_heads=2, linear_num_value_heads=4,
+                linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4,
+                layer_types=["linear_attention"] * 3 + ["full_attention"])
+
+
+def test_presets_match_published_accounting():
+    assert set(EXPECTED_TRAIN_FLOPS) <= set(preset_names())
+    for name in EXPECTED_TRAIN_FLOPS:
+        p = load_preset(name)
+        cfg = model_config(p["model"], 10112, 4096)
+        assert (cfg.num_experts, cfg.num_experts_per_tok) == (64, 5) and cfg.ngram_rows > 0 and cfg.mtp
+        tokens, fc = preset_budget(name, 10112, 4096)
+        assert fc["train_flops_per_token"] == EXPECTED_TRAIN_FLOPS[name] == p["accounting"]["train_flops_per_token"]
+        assert fc["total_params_all"] == EXPECTED_PARAMS[name]
+        assert tokens == p["train"]["tokens"]
+        assert fc["accounting_method"] == p["accounting"]["accounting_method"]
+        target = p["compute"] * (1 - p["accounting"]["compute_reserve_fraction"])
+        assert tokens * fc["train_flops_per_token"] <= target < (tokens + p["train"]["batch_tokens"]) * fc["train_flops_per_token"]
+        assert fc["active_nonvocab_params"] / fc["total_nonvocab_params"] > 0.10
+
+
+def test_preset_generator_reproduces_files():
+    from q38 import make_configs
+    for name in make_configs.BUDGETS:
+        assert json.loads((ROOT / f"configs/q38_{name}.json").read_text()) == make_configs.build(name)
+
+
+def test_backbone_terms():
+    c = small()
+    r = _count_backbone(c, 8192)
+    assert r["breakdown"]["attn_score"] == 2 * 8192 * 4 * 64                 # two causal matmuls at half density
+    assert _count_backbone(c, 4096)["breakdown"]["attn_score"] == 8192 * 4 * 64
+    q, kv, h = 4 * 64, 64, 128
+    assert r["breakdown"]["full_projections"] == 2 * h * (q + kv + kv + q) + 2 * h * q   # q, k, v, gate, o
+    assert r["breakdown"]["gdn_core"] == 3 * 4 * 8 * 64 ** 2
+    assert r["train_flops_per_token"] == 27_780_096
+    assert r["fwd_flops_per_token"] == sum(r["breakdown"].values())
+    assert r["extra_router_shared_gate_train_flops_per_token"] == 6 * 4 * 128 * (64 + 1)
+    d = copy.deepcopy(c)
+    d["linear_num_value_heads"] = 8
+    assert _count_backbone(d, 8192)["breakdown"]["gdn_core"] == 2 * r["breakdown"]["gdn_core"]
+
+
+def test_indexer_projection_is_charged_twice_not_three_times():
+    for mtp in (False, True):
+        r = count(dict(small(), mtp=mtp), 64)
+        proj = r["breakdown"]["indexer_projections"]
+        assert r["train_flops_per_token"] == 3 * (r["fwd_flops_per_token"] - proj) + 2 * proj + r["distill_target_flops"]
+        assert r["breakdown"]["gdn_core"] == _count_backbone(small(), 64)["breakdown"]["gdn_core"]
+
+
+def test_resume_rejects_changed_accounting():
+    now = count(small(), 4096)
+    validate_resume_accounting(dict(flops_accounting=now["accounting_method"], flops_per_token=now["train_flops_per_token"]), now)
+    with pytest.raises(ValueError, match="FLOPs accounting changed"):
+        validate_resume_accounting(dict(flops_accounting="q38_sparse_mhc_ngram_mtp_v1",
+                                        flops_per_token=now["train_flops_per_token"]), now)
+    with pytest.raises(ValueError, match="FLOPs accounting changed"):
+        validate_resume_accounting(dict(flops_per_token=now["train_flops_per_token"] + 1), now)
+
+
+def test_budget_is_whole_batches():
+    assert budget_tokens(100, 1e9, 4096) % 4096 == 0
+    assert budget_tokens(100, 1e9, 4096) * 100 <= 1e9
