@@ -1,0 +1,236 @@
+// Memory-bound kernels: RMSNorm variants (forward/backward), flat AdamW, sum of squares.
+// One warp handles one row where rows are short (<= 1024 elements per lane-strided pass); all math in fp32.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace q38 {
+
+constexpr int ROWS_PER_CTA = 8;   // 8 warps, one row each
+
+// ---- zero-centred RMSNorm: y = x * rsqrt(mean(x^2) + eps) * (1 + w) ----------------------------------------------
+template <typename InT, typename OutT>
+__global__ void __launch_bounds__(32 * ROWS_PER_CTA) rmsnorm_fwd_kernel(const InT* __restrict__ x, const float* __restrict__ w,
+                                                                        OutT* __restrict__ y, float* __restrict__ rstd,
+                                                                        int rows, int dim, float eps) {
+  const int row = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const InT* xr = x + (size_t)row * dim;
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) { float v = to_float(xr[i]); ss += v * v; }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / dim + eps);
+  if (lane == 0) rstd[row] = r;
+  OutT* yr = y + (size_t)row * dim;
+  for (int i = lane; i < dim; i += 32) yr[i] = from_float<OutT>(to_float(xr[i]) * r * (1.f + w[i]));
+}
+
+// dx = r * (g - xhat * mean(g * xhat)),  g = dy * (1 + w);  dw += dy * xhat (summed over rows)
+template <typename InT, typename GradT>
+__global__ void __launch_bounds__(32 * ROWS_PER_CTA) rmsnorm_bwd_kernel(const GradT* __restrict__ dy, const InT* __restrict__ x,
+                                                                        const float* __restrict__ w, const float* __restrict__ rstd,
+                                                                        InT* __restrict__ dx, float* __restrict__ dw_partial,
+                                                                        int rows, int dim) {
+  extern __shared__ float dw_acc[];            // [dim], accumulated over this CTA's rows
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dw_acc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int row = blockIdx.x * ROWS_PER_CTA + warp; row < rows; row += gridDim.x * ROWS_PER_CTA) {
+    const InT* xr = x + (size_t)row * dim;
+    const GradT* gr = dy + (size_t)row * dim;
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = lane; i < dim; i += 32) dot += to_float(gr[i]) * (1.f + w[i]) * to_float(xr[i]) * r;
+    dot = warp_sum(dot) / dim;
+    InT* dxr = dx + (size_t)row * dim;
+    for (int i = lane; i < dim; i += 32) {
+      const float xhat = to_float(xr[i]) * r, g = to_float(gr[i]);
+      dxr[i] = from_float<InT>(r * (g * (1.f + w[i]) - xhat * dot));
+      atomicAdd(&dw_acc[i], g * xhat);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) atomicAdd(&dw_partial[i], dw_acc[i]);
+}
+
+std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps, bool out_bf16) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && w.scalar_type() == at::kFloat && w.is_contiguous(), "rmsnorm_fwd: bad inputs");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dim = x.size(-1);
+  const int rows = x.numel() / dim;
+  auto y = at::empty(x.sizes(), x.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+  auto rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  if (rows == 0) return {y, rstd};
+  const int grid = (rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+  auto stream = at::cuda::getCurrentCUDAStream();
+#define LAUNCH(InT, OutT) rmsnorm_fwd_kernel<InT, OutT><<<grid, 32 * ROWS_PER_CTA, 0, stream>>>( \
+      (const InT*)x.data_ptr(), w.data_ptr<float>(), (OutT*)y.data_ptr(), rstd.data_ptr<float>(), rows, dim, (float)eps)
+  if (x.scalar_type() == at::kFloat) { if (out_bf16) LAUNCH(float, __nv_bfloat16); else LAUNCH(float, float); }
+  else if (x.scalar_type() == at::kBFloat16) { if (out_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else LAUNCH(__nv_bfloat16, float); }
+  else TORCH_CHECK(false, "rmsnorm_fwd: fp32 or bf16 input required");
+#undef LAUNCH
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {y, rstd};
+}
+
+std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& rstd) {
+  TORCH_CHECK(dy.is_cuda() && dy.is_contiguous() && x.is_contiguous(), "rmsnorm_bwd: bad inputs");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dim = x.size(-1);
+  const int rows = x.numel() / dim;
+  auto dx = at::empty_like(x);
+  auto dw = at::zeros({dim}, x.options().dtype(at::kFloat));
+  if (rows == 0) return {dx, dw};
+  const int grid = std::min((rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA, kNumSMs * 4);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const size_t smem = dim * sizeof(float);
+#define LAUNCH(InT, GradT) rmsnorm_bwd_kernel<InT, GradT><<<grid, 32 * ROWS_PER_CTA, smem, stream>>>( \
+      (const GradT*)dy.data_ptr(), (const InT*)x.data_ptr(), w.data_ptr<float>(), rstd.data_ptr<float>(), (InT*)dx.data_ptr(), \
+      dw.data_ptr<float>(), rows, dim)
+  const bool xf = x.scalar_type() == at::kFloat, gf = dy.scalar_type() == at::kFloat;
+  if (xf && gf) LAUNCH(float, float); else if (xf) LAUNCH(float, __nv_bfloat16);
+  else if (gf) LAUNCH(__nv_bfloat16, float); else LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {dx, dw};
+}
+
+// ---- gated RMSNorm over one 64-wide head: y = bf16( w * bf16(xhat) * silu(gate) ) ------------------------------------
+// One warp per row, two elements per lane (dim is fixed at 64 by the model's linear_value_head_dim).
+__global__ void __launch_bounds__(256) gated_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
+                                                                 const float* __restrict__ w, __nv_bfloat16* __restrict__ y, int rows, float eps) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat162 xv = reinterpret_cast<const __nv_bfloat162*>(x + (size_t)row * 64)[lane];
+  const __nv_bfloat162 gv = reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)row * 64)[lane];
+  const float x0 = __low2float(xv), x1 = __high2float(xv);
+  const float r = rsqrtf(warp_sum(x0 * x0 + x1 * x1) / 64.f + eps);
+  const float y0 = w[2 * lane] * bf16_round(x0 * r) * siluf_(__low2float(gv));
+  const float y1 = w[2 * lane + 1] * bf16_round(x1 * r) * siluf_(__high2float(gv));
+  reinterpret_cast<__nv_bfloat162*>(y + (size_t)row * 64)[lane] = __floats2bfloat162_rn(y0, y1);
+}
+
+__global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                                 const __nv_bfloat16* __restrict__ gate, const float* __restrict__ w,
+                                                                 __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dgate,
+                                                                 float* __restrict__ dw, int rows, float eps) {
+  __shared__ float dw_acc[64];
+  if (threadIdx.x < 64) dw_acc[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float dw0 = 0.f, dw1 = 0.f;
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const __nv_bfloat162 xv = reinterpret_cast<const __nv_bfloat162*>(x + (size_t)row * 64)[lane];
+    const __nv_bfloat162 gv = reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)row * 64)[lane];
+    const __nv_bfloat162 dv = reinterpret_cast<const __nv_bfloat162*>(dy + (size_t)row * 64)[lane];
+    const float x0 = __low2float(xv), x1 = __high2float(xv), g0 = __low2float(gv), g1 = __high2float(gv);
+    const float d0 = __low2float(dv), d1 = __high2float(dv);
+    const float r = rsqrtf(warp_sum(x0 * x0 + x1 * x1) / 64.f + eps);
+    const float h0 = x0 * r, h1 = x1 * r;
+    const float s0 = sigmoidf_(g0), s1 = sigmoidf_(g1);
+    const float w0 = w[2 * lane], w1 = w[2 * lane + 1];
+    // y = w * xhat * g * s
+    dw0 += d0 * h0 * g0 * s0; dw1 += d1 * h1 * g1 * s1;
+    const float dh0 = d0 * w0 * g0 * s0, dh1 = d1 * w1 * g1 * s1;
+    const float dot = warp_sum(dh0 * h0 + dh1 * h1) / 64.f;
+    reinterpret_cast<__nv_bfloat162*>(dx + (size_t)row * 64)[lane] = __floats2bfloat162_rn(r * (dh0 - h0 * dot), r * (dh1 - h1 * dot));
+    // d silu(g) = s * (1 + g * (1 - s))
+    reinterpret_cast<__nv_bfloat162*>(dgate + (size_t)row * 64)[lane] =
+        __floats2bfloat162_rn(d0 * w0 * h0 * s0 * (1.f + g0 * (1.f - s0)), d1 * w1 * h1 * s1 * (1.f + g1 * (1.f - s1)));
+  }
+  atomicAdd(&dw_acc[2 * lane], dw0);
+  atomicAdd(&dw_acc[2 * lane + 1], dw1);
+  __syncthreads();
+  if (threadIdx.x < 64) atomicAdd(&dw[threadIdx.x], dw_acc[threadIdx.x]);
+}
+
+at::Tensor gated_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& gate, const at::Tensor& w, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && gate.scalar_type() == at::kBFloat16 && x.size(-1) == 64 &&
+              x.is_contiguous() && gate.is_contiguous() && w.scalar_type() == at::kFloat, "gated_rmsnorm_fwd: bf16 [.., 64] inputs required");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int rows = x.numel() / 64;
+  auto y = at::empty_like(x);
+  if (rows) gated_rmsnorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)x.data_ptr(), (const __nv_bfloat16*)gate.data_ptr(), w.data_ptr<float>(), (__nv_bfloat16*)y.data_ptr(), rows, (float)eps);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return y;
+}
+
+std::vector<at::Tensor> gated_rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gate, const at::Tensor& w, double eps) {
+  TORCH_CHECK(dy.is_contiguous() && dy.scalar_type() == at::kBFloat16 && x.size(-1) == 64, "gated_rmsnorm_bwd: bad inputs");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int rows = x.numel() / 64;
+  auto dx = at::empty_like(x), dgate = at::empty_like(gate);
+  auto dw = at::zeros({64}, x.options().dtype(at::kFloat));
+  if (rows) gated_rmsnorm_bwd_kernel<<<std::min((rows + 7) / 8, kNumSMs * 8), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)x.data_ptr(), (const __nv_bfloat16*)gate.data_ptr(), w.data_ptr<float>(),
+      (__nv_bfloat16*)dx.data_ptr(), (__nv_bfloat16*)dgate.data_ptr(), dw.data_ptr<float>(), rows, (float)eps);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {dx, dgate, dw};
+}
+
+// ---- flat AdamW (decoupled decay first, torch.optim.AdamW arithmetic), optional bf16 shadow write --------------------
+__global__ void __launch_bounds__(256) adamw_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                                          float* __restrict__ v, __nv_bfloat16* __restrict__ shadow,
+                                                          const float* __restrict__ grad_scale, size_t n, float lr, float wd, float b1,
+                                                          float b2, float eps, float inv_bc1, float inv_sqrt_bc2) {
+  const float gs = grad_scale ? *grad_scale : 1.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float gi = g[i] * gs;
+    float pi = p[i] * (1.f - lr * wd);
+    const float mi = m[i] + (gi - m[i]) * (1.f - b1);
+    const float vi = v[i] * b2 + gi * gi * (1.f - b2);
+    pi -= lr * inv_bc1 * mi / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+    p[i] = pi; m[i] = mi; v[i] = vi;
+    if (shadow) shadow[i] = __float2bfloat16_rn(pi);
+  }
+}
+
+void adamw_flat(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v, c10::optional<at::Tensor> shadow,
+                c10::optional<at::Tensor> grad_scale, int64_t step, double lr, double wd, double beta1, double beta2, double eps) {
+  TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kFloat && p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(),
+              "adamw_flat: contiguous fp32 CUDA tensors required");
+  const c10::cuda::CUDAGuard guard(p.device());
+  const size_t n = p.numel();
+  if (!n) return;
+  const double bc1 = 1.0 - std::pow(beta1, (double)step), bc2 = 1.0 - std::pow(beta2, (double)step);
+  const int grid = (int)std::min<size_t>((n + 255) / 256, (size_t)kNumSMs * 16);
+  adamw_flat_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+      shadow.has_value() ? (__nv_bfloat16*)shadow->data_ptr() : nullptr, grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr,
+      n, (float)lr, (float)wd, (float)beta1, (float)beta2, (float)eps, (float)(1.0 / bc1), (float)(1.0 / std::sqrt(bc2)));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+// ---- sum of squares of a flat fp32 tensor -> one fp32 scalar (double accumulation across CTAs) ------------------------
+__global__ void __launch_bounds__(256) sum_squares_kernel(const float* __restrict__ x, size_t n, double* __restrict__ out) {
+  __shared__ float scratch[32];
+  float acc = 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) acc += x[i] * x[i];
+  acc = block_sum(acc, scratch);
+  if (threadIdx.x == 0) atomicAdd(out, (double)acc);
+}
+
+at::Tensor sum_squares(const at::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous(), "sum_squares: contiguous fp32 CUDA tensor required");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = at::zeros({}, x.options().dtype(at::kDouble));
+  const size_t n = x.numel();
+  if (n) {
+    const int grid = (int)std::min<size_t>((n + 255) / 256, (size_t)kNumSMs * 8);
+    sum_squares_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(x.data_ptr<float>(), n, out.data_ptr<double>());
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  }
+  return out;
+}
+
+}  // namespace q38

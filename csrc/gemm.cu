@@ -1,0 +1,265 @@
+// bf16 GEMM on the 5th-generation tensor cores: TMA -> 128B-swizzled shared memory -> tcgen05.mma -> TMEM -> epilogue.
+//
+//   C[b][M,N] (=|+=) alpha * A[b] . B[b]^T      fp32 accumulation in TMEM, C stored as bf16 or fp32
+//
+// Operand layouts (per batch entry), chosen independently for A and B:
+//   K-major  : the operand is stored [rows, K] with K contiguous        (forward x.W^T, dgrad with a transposed shadow)
+//   MN-major : the operand is stored [K, rows] with rows contiguous     (wgrad dW = dY^T.X reduces over tokens)
+// Both are fed by non-multicast TMA tile loads; the MN-major case uses 64x64 boxes, the K-major case 64 x rows boxes.
+//
+// CTA = 192 threads: warp 0 issues TMA, warp 1 owns TMEM and issues the MMAs (one elected lane), warps 2..5 read
+// the 128 x BN accumulator out of TMEM (warp w owns lanes 32*(w%4)..+31) and write C.  Three pipeline stages let two
+// CTAs share an SM, so one CTA's epilogue overlaps the other's main loop.  Every wait is bounded; on a timeout the
+// role records an error code, falls through to the common exit and TMEM is released.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <mutex>
+
+#include "ptx.cuh"
+#include "host.h"
+
+namespace q38 {
+
+constexpr int BM = 128, BK = 64, UMMA_K = 16, STAGES = 3, GEMM_THREADS = 192;
+
+struct GemmArgs {
+  int M, N, K, batch;
+  void* C;
+  long long ldc, c_batch_stride;
+  float alpha;
+  int* err;
+};
+
+template <int BN>
+constexpr int gemm_smem_bytes() { return STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 /*alignment slack*/ + 256 /*barriers*/; }
+
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                  const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_ready = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tmA);
+    ptx::prefetch_tensormap(&tmB);
+    for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(&full[s], 1); ptx::mbar_init(&empty[s], 1); }
+    ptx::mbar_init(acc_ready, 1);
+    ptx::fence_barrier_init();
+  }
+  if (warp == 1) { ptx::tmem_alloc(tmem_slot, TMEM_COLS); ptx::tmem_relinquish(); }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (ptx::elect_one()) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES, round = kb / STAGES;
+        if (!ptx::mbar_wait(&empty[s], (round & 1) ^ 1, 1u << 20)) { report_error(p.err, ERR_MMA_WAIT); break; }
+        uint8_t* a_dst = smem + s * STAGE_BYTES;
+        uint8_t* b_dst = a_dst + A_BYTES;
+        ptx::mbar_expect_tx(&full[s], STAGE_BYTES);
+        const int k0 = kb * BK;
+        if (A_MN) {
+#pragma unroll
+          for (int i = 0; i < BM / 64; ++i) ptx::tma_load_3d(a_dst + i * 8192, &tmA, &full[s], m0 + 64 * i, k0, bz);
+        } else {
+          ptx::tma_load_3d(a_dst, &tmA, &full[s], k0, m0, bz);
+        }
+        if (B_MN) {
+#pragma unroll
+          for (int i = 0; i < BN / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], n0 + 64 * i, k0, bz);
+        } else {
+          ptx::tma_load_3d(b_dst, &tmB, &full[s], k0, n0, bz);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (ptx::elect_one()) {
+      constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES, round = kb / STAGES;
+        if (!ptx::mbar_wait(&full[s], round & 1, 1u << 20)) { report_error(p.err, ERR_TMA_WAIT); ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t a_base = ptx::smem_u32(smem + s * STAGE_BYTES), b_base = a_base + A_BYTES;
+#pragma unroll
+        for (int j = 0; j < BK / UMMA_K; ++j) {
+          // K-major: 16 K-elements = 32 bytes inside the 128-byte swizzle row; 8-row groups are 1024 bytes apart.
+          // MN-major: 16 K-rows = 2048 bytes; 64-element MN chunks (one TMA box) are 8192 bytes apart.
+          const uint64_t a_desc = A_MN ? ptx::umma_smem_desc_sw128(a_base + j * 2048, 8192, 1024)
+                                       : ptx::umma_smem_desc_sw128(a_base + j * 32, 0, 1024);
+          const uint64_t b_desc = B_MN ? ptx::umma_smem_desc_sw128(b_base + j * 2048, 8192, 1024)
+                                       : ptx::umma_smem_desc_sw128(b_base + j * 32, 0, 1024);
+          ptx::umma_f16(tmem_base, a_desc, b_desc, idesc, (kb | j) != 0);
+        }
+        ptx::umma_commit(&empty[s]);          // the stage may be refilled once these MMAs have read it
+      }
+      ptx::umma_commit(acc_ready);            // arrives when every MMA issued above has completed
+    }
+  } else {
+    const int quarter = warp & 3;             // TMEM lanes this warp may read
+    const int row = m0 + quarter * 32 + lane;
+    bool ok = ptx::mbar_wait(acc_ready, 0, 1u << 22);
+    if (!ok) report_error(p.err, ERR_EPILOGUE_WAIT);
+    ptx::tc_fence_after();
+    if (ok) {
+      OutT* c_row = reinterpret_cast<OutT*>(p.C) + bz * p.c_batch_stride + (long long)row * p.ldc;
+      const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0) && (p.c_batch_stride % 8 == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(tmem_base + (uint32_t(quarter * 32) << 16) + c0, r);
+        ptx::tmem_ld_wait();
+        if (row < p.M) {
+          const int col0 = n0 + c0;
+          if (vec_ok && col0 + 32 <= p.N) {
+            if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]) * p.alpha,
+                                                          __uint_as_float(r[v * 8 + 2 * e + 1]) * p.alpha);
+                  w[e] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(c_row + col0 + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4* dst = reinterpret_cast<float4*>(c_row + col0 + v * 4);
+                float4 o = make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha,
+                                       __uint_as_float(r[v * 4 + 2]) * p.alpha, __uint_as_float(r[v * 4 + 3]) * p.alpha);
+                if (ACCUM) { float4 c = *dst; o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w; }
+                *dst = o;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              if (col0 + e < p.N) {
+                float v = __uint_as_float(r[e]) * p.alpha;
+                if (ACCUM) v += to_float<OutT>(c_row[col0 + e]);
+                c_row[col0 + e] = from_float<OutT>(v);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---- host side ---------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q);
+    TORCH_CHECK(e == cudaSuccess && q == cudaDriverEntryPointSuccess && ptr, "cuTensorMapEncodeTiled is unavailable");
+    fn = reinterpret_cast<EncodeFn>(ptr);
+  });
+  return fn;
+}
+
+// 3-D bf16 tensor map {inner, rows, batch} with a 128-byte-swizzled {64, box_rows, 1} box; out-of-range elements read 0.
+CUtensorMap make_tmap_bf16(const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
+                           int64_t batch_stride_elems, int box_rows) {
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
+  TORCH_CHECK(row_stride_elems % 8 == 0 && (batch <= 1 || batch_stride_elems % 8 == 0), "TMA strides must be multiples of 16 bytes");
+  TORCH_CHECK(box_rows >= 1 && box_rows <= 256, "TMA box rows out of range");
+  CUtensorMap m;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batch < 1 ? 1 : batch)};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * 2, (cuuint64_t)(batch <= 1 ? row_stride_elems * rows : batch_stride_elems) * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  return m;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
+static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& p, cudaStream_t stream) {
+  auto kernel = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, ACCUM>;
+  constexpr int smem = gemm_smem_bytes<BN>();
+  static bool configured = false;
+  if (!configured) {
+    C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, p.batch);
+  kernel<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+template <bool A_MN, bool B_MN>
+static void dispatch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& p, bool out_fp32, bool accum, int bn,
+                     cudaStream_t stream) {
+  TORCH_CHECK(!accum || out_fp32, "accumulating epilogue requires an fp32 output");
+  if (bn == 64) {
+    if (!out_fp32) launch<64, A_MN, B_MN, __nv_bfloat16, false>(ta, tb, p, stream);
+    else if (accum) launch<64, A_MN, B_MN, float, true>(ta, tb, p, stream);
+    else launch<64, A_MN, B_MN, float, false>(ta, tb, p, stream);
+  } else {
+    if (!out_fp32) launch<128, A_MN, B_MN, __nv_bfloat16, false>(ta, tb, p, stream);
+    else if (accum) launch<128, A_MN, B_MN, float, true>(ta, tb, p, stream);
+    else launch<128, A_MN, B_MN, float, false>(ta, tb, p, stream);
+  }
+}
+
+// a: K-major [batch, M, K] or MN-major [batch, K, M]; b likewise with N; c: [batch, M, N] bf16 or fp32 (last dim contiguous).
+void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
+               bool accumulate, at::Tensor& err) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda(), "gemm_bf16: CUDA tensors required");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_bf16: bf16 operands required");
+  TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && c.dim() == 3, "gemm_bf16: [batch, rows, cols] tensors required");
+  TORCH_CHECK(a.stride(2) == 1 && b.stride(2) == 1 && c.stride(2) == 1, "gemm_bf16: innermost dimension must be contiguous");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int batch = a.size(0);
+  const int M = a_mn_major ? a.size(2) : a.size(1), K = a_mn_major ? a.size(1) : a.size(2);
+  const int N = b_mn_major ? b.size(2) : b.size(1), Kb = b_mn_major ? b.size(1) : b.size(2);
+  TORCH_CHECK(K == Kb && b.size(0) == batch && c.size(0) == batch && c.size(1) == M && c.size(2) == N, "gemm_bf16: shape mismatch");
+  const bool out_fp32 = c.scalar_type() == at::kFloat;
+  TORCH_CHECK(out_fp32 || c.scalar_type() == at::kBFloat16, "gemm_bf16: output must be bf16 or fp32");
+  const int bn = (N <= 64) ? 64 : 128;
+  CUtensorMap ta = make_tmap_bf16(a.data_ptr(), a.size(2), a.size(1), batch, a.stride(1), a.stride(0), a_mn_major ? 64 : BM);
+  CUtensorMap tb = make_tmap_bf16(b.data_ptr(), b.size(2), b.size(1), batch, b.stride(1), b.stride(0), b_mn_major ? 64 : bn);
+  GemmArgs p{M, N, K, batch, c.data_ptr(), c.stride(1), c.stride(0), (float)alpha, err.data_ptr<int>()};
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  if (a_mn_major) {
+    if (b_mn_major) dispatch<true, true>(ta, tb, p, out_fp32, accumulate, bn, stream);
+    else dispatch<true, false>(ta, tb, p, out_fp32, accumulate, bn, stream);
+  } else {
+    if (b_mn_major) dispatch<false, true>(ta, tb, p, out_fp32, accumulate, bn, stream);
+    else dispatch<false, false>(ta, tb, p, out_fp32, accumulate, bn, stream);
+  }
+}
+
+}  // namespace q38

@@ -1,0 +1,424 @@
+// mHC (manifold hyper-connections): the 4-branch fp32 residual stream X[T,4,h] around every sub-layer.
+//
+// Forward of one sub-layer, given L_raw = X_flat . A^T (a tensor-core GEMM done by the caller):
+//   mhc_coef_fwd   one warp per token: inv = rsqrt(mean(X^2)+1e-6); z = tanh(B (inv L_raw)); pre/post/res coefficients
+//                  (Sinkhorn on the 4x4 residual mix, one matrix entry per lane); xin = sum_n pre_n X_n; then the
+//                  sub-layer's zero-centred RMSNorm, written as bf16/fp32 -> the GEMM input.  X is read once from HBM.
+//   mhc_post_fwd   X'_m = sum_n res[m,n] X_n + post_m y          (one pass over X, one write of X')
+// Backward:
+//   mhc_post_bwd   dy = sum_m post_m dX'_m; dpost_m = <dX'_m, y>; dres[m,n] = <dX'_m, X_n>
+//   mhc_pre_bwd_a  norm backward, dpre, coefficient/Sinkhorn/tanh backward -> dL_raw, the scalar c1 of the rms path,
+//                  dxin, and the parameter gradients (B, biases, alphas, norm weight)
+//   mhc_pre_bwd_c  dX_n = G_n + c1 X_n + pre_n dxin + sum_m res[m,n] dX'_m   with G = dL_raw . A from a GEMM
+// Coefficient row layout: [0,4) pre, [4,8) post, [8,24) res (row m, column n).  n_branch is fixed at 4.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace q38 {
+
+constexpr int NB = 4, NCOEF = 24, MAX_SINKHORN = 32, WARPS = 8;
+
+struct MhcParams {
+  const float* Bw;      // [24, r]
+  const float* b_pre;   // [4]
+  const float* b_post;  // [4]
+  const float* b_res;   // [16]
+  const float* alphas;  // [3]
+};
+
+// Sinkhorn forward on lanes 0..15 (lane = 4 m + n).  Stores every normalised iterate and divisor for the backward.
+__device__ __forceinline__ float sinkhorn_fwd(float logit, int iters, float* Y, float* S, bool keep) {
+  float mx = logit;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0x0000ffffu, mx, o));
+  float p = __expf(logit - mx);
+  for (int it = 0; it < iters; ++it) {
+    float s = p + __shfl_xor_sync(0x0000ffffu, p, 1);
+    s += __shfl_xor_sync(0x0000ffffu, s, 2);                  // row sum (over n)
+    s = fmaxf(s, 1e-9f);
+    p = p / s;
+    if (keep) { Y[2 * it] = p; S[2 * it] = s; }
+    float c = p + __shfl_xor_sync(0x0000ffffu, p, 4);
+    c += __shfl_xor_sync(0x0000ffffu, c, 8);                  // column sum (over m)
+    c = fmaxf(c, 1e-9f);
+    p = p / c;
+    if (keep) { Y[2 * it + 1] = p; S[2 * it + 1] = c; }
+  }
+  return p;
+}
+
+// d(logit) given d(result); y = p / sum(p)  =>  dp = (dy - sum(dy * y)) / s
+__device__ __forceinline__ float sinkhorn_bwd(float dres, float logit, int iters, const float* Y, const float* S) {
+  float d = dres;
+  for (int it = iters - 1; it >= 0; --it) {
+    float t = d * Y[2 * it + 1];
+    t += __shfl_xor_sync(0x0000ffffu, t, 4);
+    t += __shfl_xor_sync(0x0000ffffu, t, 8);
+    d = (d - t) / S[2 * it + 1];
+    t = d * Y[2 * it];
+    t += __shfl_xor_sync(0x0000ffffu, t, 1);
+    t += __shfl_xor_sync(0x0000ffffu, t, 2);
+    d = (d - t) / S[2 * it];
+  }
+  // p0 = exp(logit - max): the shift cancels in the normalisations, so d(logit) = d(p0) * p0
+  float mx = logit;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0x0000ffffu, mx, o));
+  return d * __expf(logit - mx);
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(32 * WARPS) mhc_coef_fwd_kernel(const float* __restrict__ X, const float* __restrict__ Lraw, MhcParams P,
+                                                                  const float* __restrict__ norm_w, OutT* __restrict__ xout,
+                                                                  float* __restrict__ coef, float* __restrict__ zsave,
+                                                                  float* __restrict__ inv_save, float* __restrict__ rstd_save, int T, int h,
+                                                                  int r, int iters, float norm_eps) {
+  extern __shared__ float sm[];
+  float* Bs = sm;                               // [24 * r]
+  float* xin_s = sm + NCOEF * r;                // [WARPS * h]
+  for (int i = threadIdx.x; i < NCOEF * r; i += blockDim.x) Bs[i] = P.Bw[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * WARPS + warp;
+  if (t >= T) return;
+  const float* Xt = X + (size_t)t * NB * h;
+  const int n4 = NB * h / 4;
+  float ss = 0.f;
+  for (int i = lane; i < n4; i += 32) {
+    const float4 v = reinterpret_cast<const float4*>(Xt)[i];
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (NB * h) + 1e-6f);
+  // z_j for j = lane < 24
+  float z = 0.f;
+  if (lane < NCOEF) {
+    const float* Lt = Lraw + (size_t)t * r;
+    float acc = 0.f;
+    for (int i = 0; i < r; ++i) acc += Bs[lane * r + i] * Lt[i];
+    z = tanhf(acc * inv);
+    zsave[(size_t)t * NCOEF + lane] = z;
+  }
+  // coefficients: lanes 0..3 pre, 4..7 post; residual logits are moved to lanes 0..15 for the Sinkhorn
+  float c = 0.f;
+  if (lane < 4) c = sigmoidf_(P.b_pre[lane] + P.alphas[0] * z);
+  else if (lane < 8) c = 2.f * sigmoidf_(P.b_post[lane - 4] + P.alphas[1] * z);
+  const float zr = __shfl_sync(0xffffffffu, z, (lane & 15) + 8);
+  float res = 0.f;
+  if (lane < 16) {
+    const float logit = P.b_res[lane] + P.alphas[2] * zr;
+    res = sinkhorn_fwd(logit, iters, nullptr, nullptr, false);
+  }
+  if (lane < 8) coef[(size_t)t * NCOEF + lane] = c;
+  if (lane < 16) coef[(size_t)t * NCOEF + 8 + lane] = res;
+  const float p0 = __shfl_sync(0xffffffffu, c, 0), p1 = __shfl_sync(0xffffffffu, c, 1), p2 = __shfl_sync(0xffffffffu, c, 2),
+              p3 = __shfl_sync(0xffffffffu, c, 3);
+  float* xs = xin_s + warp * h;
+  float ss2 = 0.f;
+  for (int i = lane; i < h; i += 32) {
+    const float v = p0 * Xt[i] + p1 * Xt[h + i] + p2 * Xt[2 * h + i] + p3 * Xt[3 * h + i];
+    xs[i] = v;
+    ss2 += v * v;
+  }
+  ss2 = warp_sum(ss2);
+  const float rstd = rsqrtf(ss2 / h + norm_eps);
+  if (lane == 0) { inv_save[t] = inv; rstd_save[t] = rstd; }
+  __syncwarp();
+  OutT* xo = xout + (size_t)t * h;
+  for (int i = lane; i < h; i += 32) xo[i] = from_float<OutT>(xs[i] * rstd * (1.f + norm_w[i]));
+}
+
+template <typename YT>
+__global__ void __launch_bounds__(256) mhc_post_fwd_kernel(const float* __restrict__ X, const YT* __restrict__ y,
+                                                           const float* __restrict__ coef, float* __restrict__ Xout, int T, int h) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)T * h) return;
+  const int t = idx / h, i = idx % h;
+  const float* c = coef + (size_t)t * NCOEF;
+  const float* Xt = X + (size_t)t * NB * h;
+  const float x0 = Xt[i], x1 = Xt[h + i], x2 = Xt[2 * h + i], x3 = Xt[3 * h + i];
+  const float yv = to_float(y[idx]);
+  float* Xo = Xout + (size_t)t * NB * h;
+#pragma unroll
+  for (int m = 0; m < NB; ++m)
+    Xo[m * h + i] = c[8 + 4 * m] * x0 + c[8 + 4 * m + 1] * x1 + c[8 + 4 * m + 2] * x2 + c[8 + 4 * m + 3] * x3 + c[4 + m] * yv;
+}
+
+template <typename YT>
+__global__ void __launch_bounds__(32 * WARPS) mhc_post_bwd_kernel(const float* __restrict__ dXo, const float* __restrict__ X,
+                                                                  const YT* __restrict__ y, const float* __restrict__ coef,
+                                                                  YT* __restrict__ dy, float* __restrict__ dcoef, int T, int h) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * WARPS + warp;
+  if (t >= T) return;
+  const float* c = coef + (size_t)t * NCOEF;
+  const float q0 = c[4], q1 = c[5], q2 = c[6], q3 = c[7];
+  const float* D = dXo + (size_t)t * NB * h;
+  const float* Xt = X + (size_t)t * NB * h;
+  float dpost[NB] = {0.f, 0.f, 0.f, 0.f};
+  float dres[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) dres[k] = 0.f;
+  for (int i = lane; i < h; i += 32) {
+    const float d[NB] = {D[i], D[h + i], D[2 * h + i], D[3 * h + i]};
+    const float x[NB] = {Xt[i], Xt[h + i], Xt[2 * h + i], Xt[3 * h + i]};
+    const float yv = to_float(y[(size_t)t * h + i]);
+    dy[(size_t)t * h + i] = from_float<YT>(q0 * d[0] + q1 * d[1] + q2 * d[2] + q3 * d[3]);
+#pragma unroll
+    for (int m = 0; m < NB; ++m) {
+      dpost[m] += d[m] * yv;
+#pragma unroll
+      for (int n = 0; n < NB; ++n) dres[4 * m + n] += d[m] * x[n];
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < NB; ++m) dpost[m] = warp_sum(dpost[m]);
+#pragma unroll
+  for (int k = 0; k < 16; ++k) dres[k] = warp_sum(dres[k]);
+  if (lane == 0) {
+    float* o = dcoef + (size_t)t * NCOEF;
+#pragma unroll
+    for (int m = 0; m < NB; ++m) { o[m] = 0.f; o[4 + m] = dpost[m]; }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) o[8 + k] = dres[k];
+  }
+}
+
+// Part A of the pre backward.  dcoef holds dpost/dres from mhc_post_bwd in its [4,24) entries; this kernel fills [0,4).
+template <typename GT>
+__global__ void __launch_bounds__(32 * WARPS) mhc_pre_bwd_a_kernel(const GT* __restrict__ dxout, const float* __restrict__ X,
+                                                                   const float* __restrict__ Lraw, MhcParams P, const float* __restrict__ norm_w,
+                                                                   const float* __restrict__ coef, const float* __restrict__ zsave,
+                                                                   const float* __restrict__ inv_save, const float* __restrict__ rstd_save,
+                                                                   float* __restrict__ dcoef, float* __restrict__ dLraw, float* __restrict__ c1_out,
+                                                                   float* __restrict__ dxin_out, float* __restrict__ dBw, float* __restrict__ dbias,
+                                                                   float* __restrict__ dnorm_w, int T, int h, int r, int iters) {
+  extern __shared__ float sm[];
+  float* Bs = sm;                      // [24 * r]
+  float* dB_s = Bs + NCOEF * r;        // [24 * r]   CTA-level accumulation of dB
+  float* dnw_s = dB_s + NCOEF * r;     // [h]        CTA-level accumulation of d(norm weight)
+  float* dbias_s = dnw_s + h;          // [27]       b_pre(4) b_post(4) b_res(16) alphas(3)
+  float* xin_s = dbias_s + 32;         // [WARPS * h]
+  float* dl_s = xin_s + WARPS * h;     // [WARPS * 24]
+  for (int i = threadIdx.x; i < NCOEF * r; i += blockDim.x) { Bs[i] = P.Bw[i]; dB_s[i] = 0.f; }
+  for (int i = threadIdx.x; i < h; i += blockDim.x) dnw_s[i] = 0.f;
+  if (threadIdx.x < 32) dbias_s[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * WARPS + warp;
+  if (t < T) {
+    const float* Xt = X + (size_t)t * NB * h;
+    const float* c = coef + (size_t)t * NCOEF;
+    const float p[NB] = {c[0], c[1], c[2], c[3]};
+    const float rstd = rstd_save[t], inv = inv_save[t];
+    float* xs = xin_s + warp * h;
+    // norm backward: g = dx (1 + w); dxin = rstd (g - xhat mean(g xhat))
+    float dot = 0.f;
+    for (int i = lane; i < h; i += 32) {
+      const float xin = p[0] * Xt[i] + p[1] * Xt[h + i] + p[2] * Xt[2 * h + i] + p[3] * Xt[3 * h + i];
+      const float xhat = xin * rstd, g = to_float(dxout[(size_t)t * h + i]);
+      xs[i] = xhat;
+      dot += g * (1.f + norm_w[i]) * xhat;
+      atomicAdd(&dnw_s[i], g * xhat);
+    }
+    dot = warp_sum(dot) / h;
+    float dpre[NB] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = lane; i < h; i += 32) {
+      const float g = to_float(dxout[(size_t)t * h + i]) * (1.f + norm_w[i]);
+      const float dxin = rstd * (g - xs[i] * dot);
+      dxin_out[(size_t)t * h + i] = dxin;
+#pragma unroll
+      for (int n = 0; n < NB; ++n) dpre[n] += dxin * Xt[n * h + i];
+    }
+#pragma unroll
+    for (int n = 0; n < NB; ++n) dpre[n] = warp_sum(dpre[n]);
+    // coefficient backward, lane j < 24 owns logit j
+    const float z = lane < NCOEF ? zsave[(size_t)t * NCOEF + lane] : 0.f;
+    float dlogit = 0.f;
+    if (lane < 4) {
+      const float dp = lane == 0 ? dpre[0] : lane == 1 ? dpre[1] : lane == 2 ? dpre[2] : dpre[3];
+      dcoef[(size_t)t * NCOEF + lane] = dp;
+      dlogit = dp * c[lane] * (1.f - c[lane]);
+    } else if (lane < 8) {
+      const float q = c[lane];                             // post = 2 sigmoid  =>  d/dlogit = q (1 - q/2)
+      dlogit = dcoef[(size_t)t * NCOEF + lane] * q * (1.f - 0.5f * q);
+    }
+    // Sinkhorn backward on lanes 0..15, result moved to lanes 8..23
+    float dres_logit = 0.f;
+    {
+      const float zr = __shfl_sync(0xffffffffu, z, (lane & 15) + 8);
+      float Y[2 * MAX_SINKHORN], S[2 * MAX_SINKHORN];
+      if (lane < 16) {
+        const float logit = P.b_res[lane] + P.alphas[2] * zr;
+        sinkhorn_fwd(logit, iters, Y, S, true);
+        dres_logit = sinkhorn_bwd(dcoef[(size_t)t * NCOEF + 8 + lane], logit, iters, Y, S);
+      }
+    }
+    const float moved = __shfl_sync(0xffffffffu, dres_logit, (lane + 24) & 31);   // lane j gets lane j-8
+    if (lane >= 8 && lane < NCOEF) dlogit = moved;
+    // biases and alphas
+    if (lane < NCOEF) {
+      atomicAdd(&dbias_s[lane], dlogit);
+      const int a = lane < 4 ? 0 : lane < 8 ? 1 : 2;
+      atomicAdd(&dbias_s[24 + a], dlogit * z);
+    }
+    const float alpha = lane < 4 ? P.alphas[0] : lane < 8 ? P.alphas[1] : P.alphas[2];
+    const float dlin = lane < NCOEF ? dlogit * alpha * (1.f - z * z) : 0.f;       // grad of B (inv L_raw) row j
+    float* dls = dl_s + warp * NCOEF;
+    if (lane < NCOEF) dls[lane] = dlin;
+    __syncwarp();
+    // dB[j,i] += dlin_j * inv * Lraw_i ;  dL_i = sum_j B[j,i] dlin_j ;  dLraw_i = inv dL_i ;  dinv = sum_i dL_i Lraw_i
+    const float* Lt = Lraw + (size_t)t * r;
+    float dinv = 0.f;
+    for (int i = lane; i < r; i += 32) {
+      const float li = Lt[i];
+      float dl = 0.f;
+#pragma unroll
+      for (int j = 0; j < NCOEF; ++j) {
+        dl += Bs[j * r + i] * dls[j];
+        atomicAdd(&dB_s[j * r + i], dls[j] * inv * li);
+      }
+      dLraw[(size_t)t * r + i] = inv * dl;
+      dinv += dl * li;
+    }
+    dinv = warp_sum(dinv);
+    if (lane == 0) c1_out[t] = -dinv * inv * inv * inv / (NB * h);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < NCOEF * r; i += blockDim.x) atomicAdd(&dBw[i], dB_s[i]);
+  for (int i = threadIdx.x; i < h; i += blockDim.x) atomicAdd(&dnorm_w[i], dnw_s[i]);
+  if (threadIdx.x < 27) atomicAdd(&dbias[threadIdx.x], dbias_s[threadIdx.x]);
+}
+
+// dX (holding G on entry) <- G + c1 X + pre_n dxin + sum_m res[m,n] dX'_m
+__global__ void __launch_bounds__(256) mhc_pre_bwd_c_kernel(float* __restrict__ dX, const float* __restrict__ dXo, const float* __restrict__ X,
+                                                            const float* __restrict__ dxin, const float* __restrict__ coef,
+                                                            const float* __restrict__ c1, int T, int h) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)T * h) return;
+  const int t = idx / h, i = idx % h;
+  const float* c = coef + (size_t)t * NCOEF;
+  const size_t base = (size_t)t * NB * h + i;
+  const float d0 = dXo[base], d1 = dXo[base + h], d2 = dXo[base + 2 * h], d3 = dXo[base + 3 * h];
+  const float k1 = c1[t], di = dxin[idx];
+#pragma unroll
+  for (int n = 0; n < NB; ++n) {
+    const size_t o = base + (size_t)n * h;
+    dX[o] = dX[o] + k1 * X[o] + c[n] * di + c[8 + n] * d0 + c[12 + n] * d1 + c[16 + n] * d2 + c[20 + n] * d3;
+  }
+}
+
+// ---- host wrappers -------------------------------------------------------------------------------------------------------
+static MhcParams params_of(const at::Tensor& Bw, const at::Tensor& b_pre, const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas) {
+  return MhcParams{Bw.data_ptr<float>(), b_pre.data_ptr<float>(), b_post.data_ptr<float>(), b_res.data_ptr<float>(), alphas.data_ptr<float>()};
+}
+
+std::vector<at::Tensor> mhc_coef_fwd(const at::Tensor& X, const at::Tensor& Lraw, const at::Tensor& Bw, const at::Tensor& b_pre,
+                                     const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas, const at::Tensor& norm_w,
+                                     int64_t iters, double norm_eps, bool out_bf16) {
+  TORCH_CHECK(X.is_cuda() && X.scalar_type() == at::kFloat && X.is_contiguous() && X.dim() == 3 && X.size(1) == NB, "mhc_coef_fwd: X must be fp32 [T,4,h]");
+  TORCH_CHECK(Lraw.scalar_type() == at::kFloat && Lraw.is_contiguous() && iters <= MAX_SINKHORN && Bw.size(0) == NCOEF, "mhc_coef_fwd: bad operands");
+  const c10::cuda::CUDAGuard guard(X.device());
+  const int T = X.size(0), h = X.size(2), r = Lraw.size(1);
+  TORCH_CHECK(h % 4 == 0, "mhc: hidden size must be a multiple of 4");
+  auto f32 = X.options();
+  auto xout = at::empty({T, h}, f32.dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+  auto coef = at::empty({T, NCOEF}, f32), z = at::empty({T, NCOEF}, f32), inv = at::empty({T}, f32), rstd = at::empty({T}, f32);
+  const size_t smem = (NCOEF * r + WARPS * h) * sizeof(float);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int grid = (T + WARPS - 1) / WARPS;
+  MhcParams P = params_of(Bw, b_pre, b_post, b_res, alphas);
+  if (out_bf16) {
+    auto k = mhc_coef_fwd_kernel<__nv_bfloat16>;
+    C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    k<<<grid, 32 * WARPS, smem, stream>>>(X.data_ptr<float>(), Lraw.data_ptr<float>(), P, norm_w.data_ptr<float>(), (__nv_bfloat16*)xout.data_ptr(),
+                                          coef.data_ptr<float>(), z.data_ptr<float>(), inv.data_ptr<float>(), rstd.data_ptr<float>(), T, h, r, (int)iters, (float)norm_eps);
+  } else {
+    auto k = mhc_coef_fwd_kernel<float>;
+    C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    k<<<grid, 32 * WARPS, smem, stream>>>(X.data_ptr<float>(), Lraw.data_ptr<float>(), P, norm_w.data_ptr<float>(), xout.data_ptr<float>(),
+                                          coef.data_ptr<float>(), z.data_ptr<float>(), inv.data_ptr<float>(), rstd.data_ptr<float>(), T, h, r, (int)iters, (float)norm_eps);
+  }
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {xout, coef, z, inv, rstd};
+}
+
+at::Tensor mhc_post_fwd(const at::Tensor& X, const at::Tensor& y, const at::Tensor& coef) {
+  TORCH_CHECK(X.is_cuda() && X.scalar_type() == at::kFloat && X.is_contiguous() && y.is_contiguous() && coef.is_contiguous(), "mhc_post_fwd: bad inputs");
+  const c10::cuda::CUDAGuard guard(X.device());
+  const int T = X.size(0), h = X.size(2);
+  auto out = at::empty_like(X);
+  const size_t n = (size_t)T * h;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (y.scalar_type() == at::kBFloat16)
+    mhc_post_fwd_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, stream>>>(X.data_ptr<float>(), (const __nv_bfloat16*)y.data_ptr(), coef.data_ptr<float>(), out.data_ptr<float>(), T, h);
+  else
+    mhc_post_fwd_kernel<float><<<(n + 255) / 256, 256, 0, stream>>>(X.data_ptr<float>(), y.data_ptr<float>(), coef.data_ptr<float>(), out.data_ptr<float>(), T, h);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return out;
+}
+
+std::vector<at::Tensor> mhc_post_bwd(const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& y, const at::Tensor& coef) {
+  TORCH_CHECK(dXo.is_cuda() && dXo.scalar_type() == at::kFloat && dXo.is_contiguous() && X.is_contiguous() && y.is_contiguous(), "mhc_post_bwd: bad inputs");
+  const c10::cuda::CUDAGuard guard(X.device());
+  const int T = X.size(0), h = X.size(2);
+  auto dy = at::empty_like(y);
+  auto dcoef = at::empty({T, NCOEF}, X.options());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int grid = (T + WARPS - 1) / WARPS;
+  if (y.scalar_type() == at::kBFloat16)
+    mhc_post_bwd_kernel<__nv_bfloat16><<<grid, 32 * WARPS, 0, stream>>>(dXo.data_ptr<float>(), X.data_ptr<float>(), (const __nv_bfloat16*)y.data_ptr(),
+                                                                        coef.data_ptr<float>(), (__nv_bfloat16*)dy.data_ptr(), dcoef.data_ptr<float>(), T, h);
+  else
+    mhc_post_bwd_kernel<float><<<grid, 32 * WARPS, 0, stream>>>(dXo.data_ptr<float>(), X.data_ptr<float>(), y.data_ptr<float>(), coef.data_ptr<float>(),
+                                                                dy.data_ptr<float>(), dcoef.data_ptr<float>(), T, h);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {dy, dcoef};
+}
+
+// Returns {dLraw [T,r], c1 [T], dxin [T,h], dBw [24,r], dbias [27], dnorm_w [h]}; dcoef is completed in place.
+std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor& X, const at::Tensor& Lraw, const at::Tensor& Bw,
+                                      const at::Tensor& b_pre, const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas,
+                                      const at::Tensor& norm_w, const at::Tensor& coef, const at::Tensor& z, const at::Tensor& inv,
+                                      const at::Tensor& rstd, at::Tensor& dcoef, int64_t iters) {
+  TORCH_CHECK(dxout.is_cuda() && dxout.is_contiguous() && X.is_contiguous() && dcoef.is_contiguous() && iters <= MAX_SINKHORN, "mhc_pre_bwd_a: bad inputs");
+  const c10::cuda::CUDAGuard guard(X.device());
+  const int T = X.size(0), h = X.size(2), r = Lraw.size(1);
+  auto f32 = X.options();
+  auto dLraw = at::empty({T, r}, f32), c1 = at::empty({T}, f32), dxin = at::empty({T, h}, f32);
+  auto dBw = at::zeros({NCOEF, r}, f32), dbias = at::zeros({27}, f32), dnw = at::zeros({h}, f32);
+  const size_t smem = (2 * NCOEF * r + h + 32 + WARPS * h + WARPS * NCOEF) * sizeof(float);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int grid = (T + WARPS - 1) / WARPS;
+  MhcParams P = params_of(Bw, b_pre, b_post, b_res, alphas);
+#define LAUNCH(GT) { auto k = mhc_pre_bwd_a_kernel<GT>; \
+    C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
+    k<<<grid, 32 * WARPS, smem, stream>>>((const GT*)dxout.data_ptr(), X.data_ptr<float>(), Lraw.data_ptr<float>(), P, norm_w.data_ptr<float>(), \
+      coef.data_ptr<float>(), z.data_ptr<float>(), inv.data_ptr<float>(), rstd.data_ptr<float>(), dcoef.data_ptr<float>(), dLraw.data_ptr<float>(), \
+      c1.data_ptr<float>(), dxin.data_ptr<float>(), dBw.data_ptr<float>(), dbias.data_ptr<float>(), dnw.data_ptr<float>(), T, h, r, (int)iters); }
+  if (dxout.scalar_type() == at::kBFloat16) LAUNCH(__nv_bfloat16) else LAUNCH(float)
+#undef LAUNCH
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {dLraw, c1, dxin, dBw, dbias, dnw};
+}
+
+void mhc_pre_bwd_c(at::Tensor& dX, const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& dxin, const at::Tensor& coef, const at::Tensor& c1) {
+  TORCH_CHECK(dX.is_cuda() && dX.is_contiguous() && dXo.is_contiguous() && X.is_contiguous() && dxin.is_contiguous(), "mhc_pre_bwd_c: bad inputs");
+  const c10::cuda::CUDAGuard guard(X.device());
+  const int T = X.size(0), h = X.size(2);
+  const size_t n = (size_t)T * h;
+  mhc_pre_bwd_c_kernel<<<(n + 255) / 256, 256, 0, at::cuda::getCurrentCUDAStream()>>>(dX.data_ptr<float>(), dXo.data_ptr<float>(), X.data_ptr<float>(),
+                                                                                      dxin.data_ptr<float>(), coef.data_ptr<float>(), c1.data_ptr<float>(), T, h);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+}  // namespace q38

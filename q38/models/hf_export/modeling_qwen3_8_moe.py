@@ -52,14 +52,18 @@ def get_backend():
     return _BACKEND
 
 
-def _fast(t: torch.Tensor) -> bool:
-    return _BACKEND is not None and t.is_cuda
+def _hook(name: str, t: torch.Tensor):
+    """The backend's implementation of `name` for tensors like `t`, or ``None`` to use the PyTorch path."""
+    if _BACKEND is None or not t.is_cuda:
+        return None
+    return getattr(_BACKEND, name, None)
 
 
 def _linear(x, weight, bias=None):
     """``x @ weight.T`` in the dtype of ``x`` (fp32 master weights are cast per use)."""
-    if _fast(x) and bias is None:
-        return _BACKEND.linear(x, weight)
+    fast = _hook("linear", x)
+    if fast is not None and bias is None:
+        return fast(x, weight)
     return F.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
 
 
@@ -74,8 +78,9 @@ class Qwen3_8MoeRMSNorm(nn.Module):
 
     def forward(self, x, out_dtype=None):
         out_dtype = out_dtype or x.dtype
-        if _fast(x):
-            return _BACKEND.rmsnorm(x, self.weight, self.eps, out_dtype)
+        fast = _hook("rmsnorm", x)
+        if fast is not None:
+            return fast(x, self.weight, self.eps, out_dtype)
         xf = x.float()
         xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
         return (xf * (1.0 + self.weight.float())).to(out_dtype)
@@ -96,8 +101,9 @@ class Qwen3_8MoeRMSNormGated(nn.Module):
         self.variance_epsilon = eps
 
     def forward(self, x, gate):
-        if _fast(x):
-            return _BACKEND.gated_rmsnorm(x, gate, self.weight, self.variance_epsilon)
+        fast = _hook("gated_rmsnorm", x)
+        if fast is not None and x.dtype == torch.bfloat16 and x.shape[-1] == 64:
+            return fast(x, gate, self.weight, self.variance_epsilon)
         dt = x.dtype
         xf = x.float()
         xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.variance_epsilon)
@@ -223,8 +229,9 @@ class Qwen3_8MoeGatedDeltaNet(nn.Module):
         self.in_proj_a = nn.Linear(self.hidden_size, self.num_v_heads, bias=False)
 
     def forward(self, x):
-        if _fast(x):
-            return _BACKEND.gated_deltanet(self, x)
+        fast = _hook("gated_deltanet", x)
+        if fast is not None:
+            return fast(self, x)
         B, S, _ = x.shape
         qkv = causal_conv_silu(_linear(x, self.in_proj_qkv.weight), self.conv1d.weight)
         q, k, v = qkv.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
@@ -339,8 +346,9 @@ def qsa_attention(attn, x, cos, sin, indexer, budget, dense, want_kl):
     The indexer sees ``x.detach()`` and gets gradient from the KL term only; block selection is not
     differentiated.  (Reference: modeling_qwen3_8_moe.py:1117-1160.)
     """
-    if _fast(x):
-        return _BACKEND.qsa_attention(attn, x, cos, sin, indexer, budget, dense, want_kl)
+    fast = _hook("qsa_attention", x)
+    if fast is not None:
+        return fast(attn, x, cos, sin, indexer, budget, dense, want_kl)
     B, S, _ = x.shape
     hd = attn.head_dim
     qg = _linear(x, attn.q_proj.weight).view(B, S, -1, 2 * hd)
@@ -470,8 +478,9 @@ class Qwen3_8MoeSparseMoeBlock(nn.Module):
         return self.stats_sink is not None and self.training and torch.is_grad_enabled()
 
     def forward(self, x):
-        if _fast(x):
-            return _BACKEND.moe_block(self, x)
+        fast = _hook("moe_block", x)
+        if fast is not None:
+            return fast(self, x)
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         _, top_w, top_idx, probs = self.gate(x2)
@@ -607,8 +616,9 @@ class NGramEmbedding(nn.Module):
 
     def delta(self, h, ids):
         """The increment ``sigmoid(W h + b) * rmsnorm(emb2[i2] + emb3[i3])`` to add to every branch."""
-        if _fast(h):
-            return _BACKEND.ngram_delta(self, h, ids)
+        fast = _hook("ngram_delta", h)
+        if fast is not None:
+            return fast(self, h, ids)
         i2, i3 = self.indices(ids)
         e = self.norm((self.emb2(i2) + self.emb3(i3)).float()).to(h.dtype)
         g = torch.sigmoid(_linear(h, self.gate.weight, self.gate.bias))
@@ -673,14 +683,16 @@ class Q38TextCore(nn.Module):
         return X.sum(2)[:, :length].to(e.dtype), kls
 
     def _sublayer_input(self, mhc, norm, X, dtype):
-        if _fast(X):
-            return _BACKEND.mhc_pre_norm(mhc, norm, X, dtype)
+        fast = _hook("mhc_pre_norm", X)
+        if fast is not None:
+            return fast(mhc, norm, X, dtype)
         xin, state = mhc.pre(X)
         return norm(xin, out_dtype=dtype), state
 
     def _sublayer_output(self, mhc, y, state):
-        if _fast(y):
-            return _BACKEND.mhc_post(mhc, y, state)
+        fast = _hook("mhc_post", y)
+        if fast is not None:
+            return fast(mhc, y, state)
         return mhc.post(y, state)
 
     def _layer(self, i, X, ids, cos, sin, dtype):

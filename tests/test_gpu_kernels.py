@@ -1,0 +1,145 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 evaluation of the same op (run on a B200)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from q38 import ops as module
+    module.install()
+    assert module.loaded_library() is not None and module.loaded_library().endswith("_C.so")
+    yield module
+    module.check_errors()
+
+
+def rel_err(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 576), (200, 72, 136), (1000, 2240, 576), (333, 21, 576), (4096, 576, 1344)])
+def test_gemm_k_major(ops, M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    out32 = ops.gemm(a, b, out_dtype=torch.float32)
+    out16 = ops.gemm(a, b, out_dtype=torch.bfloat16)
+    ops.check_errors()
+    assert rel_err(out32, ref) < 1e-3
+    assert rel_err(out16, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 136, 72), (576, 2240, 16384), (288, 576, 1280)])
+def test_gemm_mn_major_operands(ops, M, N, K):
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    at, bt = a.t().contiguous(), b.t().contiguous()            # [K, M], [K, N]
+    ref = a.float() @ b.float().t()
+    nn = ops.gemm(a, bt, b_mn_major=True, out_dtype=torch.float32)
+    tn = ops.gemm(at, bt, a_mn_major=True, b_mn_major=True, out_dtype=torch.float32)
+    tk = ops.gemm(at, b, a_mn_major=True, out_dtype=torch.float32)
+    ops.check_errors()
+    assert rel_err(nn, ref) < 1e-3, "B MN-major"
+    assert rel_err(tn, ref) < 1e-3, "A and B MN-major"
+    assert rel_err(tk, ref) < 1e-3, "A MN-major"
+
+
+def test_gemm_batched_accumulate_alpha(ops):
+    torch.manual_seed(2)
+    a = torch.randn(5, 288, 576, device="cuda").to(torch.bfloat16)
+    b = torch.randn(5, 288, 576, device="cuda").to(torch.bfloat16)
+    c = torch.randn(5, 288, 288, device="cuda")
+    ref = c + 0.5 * torch.bmm(a.float(), b.float().transpose(1, 2))
+    ops.gemm(a, b, out=c, alpha=0.5, accumulate=True)
+    ops.check_errors()
+    assert rel_err(c, ref) < 1e-3
+
+
+@pytest.mark.parametrize("dim,in_dtype,out_dtype", [(576, torch.float32, torch.bfloat16), (64, torch.bfloat16, torch.bfloat16),
+                                                    (448, torch.float32, torch.float32)])
+def test_rmsnorm(ops, dim, in_dtype, out_dtype):
+    from q38.ops.backend import _RMSNorm
+    torch.manual_seed(3)
+    x = torch.randn(777, dim, device="cuda").to(in_dtype).requires_grad_()
+    w = (0.1 * torch.randn(dim, device="cuda")).requires_grad_()
+    dy = torch.randn(777, dim, device="cuda").to(out_dtype)
+    y = _RMSNorm.apply(x, w, 1e-6, out_dtype)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + wr)
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < (1e-2 if out_dtype == torch.bfloat16 else 1e-5)
+    assert rel_err(x.grad, xr.grad) < (2e-2 if in_dtype == torch.bfloat16 else 1e-4)
+    assert rel_err(w.grad, wr.grad) < 1e-3
+
+
+def test_gated_rmsnorm(ops):
+    from q38.ops.backend import _GatedRMSNorm
+    torch.manual_seed(4)
+    x = torch.randn(1000, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    g = torch.randn(1000, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (1 + 0.1 * torch.randn(64, device="cuda")).requires_grad_()
+    dy = torch.randn(1000, 64, device="cuda").to(torch.bfloat16)
+    y = _GatedRMSNorm.apply(x, g, w, 1e-6)
+    y.backward(dy)
+    xr, gr, wr = (t.detach().float().requires_grad_() for t in (x, g, w))
+    yr = wr * (xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-6)) * torch.nn.functional.silu(gr)
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 2e-2 and rel_err(x.grad, xr.grad) < 3e-2 and rel_err(g.grad, gr.grad) < 3e-2
+    assert rel_err(w.grad, wr.grad) < 1e-2
+
+
+def test_adamw_flat_and_sum_squares(ops):
+    torch.manual_seed(5)
+    n = 100_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    ref = torch.nn.Parameter(p.clone())
+    ref.grad = g.clone() * 0.5
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    shadow = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    scale = torch.tensor(0.5, device="cuda")
+    for step in (1, 2, 3):
+        opt.step()
+        ops.adamw_flat(p, g, m, v, step, 1e-2, 0.1, 0.9, 0.95, 1e-8, grad_scale=scale, shadow=shadow)
+    assert rel_err(p, ref.detach()) < 1e-5
+    assert torch.equal(shadow, p.to(torch.bfloat16))
+    assert abs(ops.sum_squares(g).item() / g.double().pow(2).sum().item() - 1) < 1e-6
+
+
+def test_linear_autograd(ops):
+    from q38.models import modeling
+    backend = modeling.get_backend()
+    torch.manual_seed(6)
+    x = torch.randn(4, 96, 576, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (0.05 * torch.randn(1344, 576, device="cuda")).requires_grad_()
+    dy = torch.randn(4, 96, 1344, device="cuda").to(torch.bfloat16)
+    y = backend.linear(x, w)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = xr @ wr.to(torch.bfloat16).float().t()
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2 and rel_err(x.grad, xr.grad) < 1e-2 and rel_err(w.grad, wr.grad) < 1e-2
+    assert w.grad.dtype == torch.float32
+
+
+def test_muon_gpu_matches_reference(ops, monkeypatch):
+    from q38.optim.muon import Muon
+    torch.manual_seed(7)
+    shapes = [(8, 32, 16), (48, 96), (6, 1, 4), (3, 288, 576)]
+    fast = [torch.nn.Parameter(torch.randn(s, device="cuda")) for s in shapes]
+    slow = [torch.nn.Parameter(p.detach().clone()) for p in fast]
+    for p, q in zip(fast, slow):
+        p.grad = torch.randn_like(p)
+        q.grad = p.grad.clone()
+    a, b = Muon(fast, lr=1e-3), Muon(slow, lr=1e-3)
+    a.step()
+    monkeypatch.setenv("Q38_MUON_BASELINE", "1")
+    b.step()
+    for p, q in zip(fast, slow):
+        torch.testing.assert_close(p, q, rtol=1e-3, atol=2e-4)
+        torch.testing.assert_close(a.state[p]["buf"], b.state[q]["buf"], rtol=0, atol=0)

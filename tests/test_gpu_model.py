@@ -1,0 +1,82 @@
+"""Model-level GPU checks: the kernel backend against the fp32 CPU specification, and the public training step."""
+import copy
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = dict(layers=4, hidden=128, heads=4, kv_heads=2, lin_k_heads=2, lin_v_heads=6, experts=8, topk=2, moe_ffn=32, shared_ffn=32,
+             ngram_rows=1024, mhc_iters=5, qsa_blocks=2)
+
+
+def build(seq=256):
+    from q38.models import Q38ForCausalLM
+    from q38.presets import model_config
+    torch.manual_seed(0)
+    cfg = model_config(dict(SHAPE), 512, seq, eos_token_id=7, pad_token_id=0)
+    return cfg, Q38ForCausalLM(cfg)
+
+
+def losses(model, ids, dense):
+    from q38.losses import LossModel
+    model.train()
+    model.model.qsa_dense = dense
+    ce, aux, mtp, kl = LossModel(model)(ids, ids.roll(-1, 1))
+    return ce, aux, mtp, kl
+
+
+@pytest.mark.parametrize("dense", [True, False])
+def test_backend_matches_cpu_specification(dense):
+    from q38 import ops
+    ops.install()
+    cfg, cpu_model = build()
+    gpu_model = copy.deepcopy(cpu_model).cuda()
+    gpu_model.tie_embeddings()
+    gpu_model.model.compute_dtype = torch.bfloat16
+    ids = torch.randint(1, 512, (2, 256))
+    ids[0, 100] = 7
+    ref = losses(cpu_model, ids, dense)
+    got = losses(gpu_model, ids.cuda(), dense)
+    ops.check_errors()
+    for name, r, g in zip(("ce", "aux", "mtp", "kl"), ref, got):
+        assert abs(g.item() - r.item()) <= 0.03 * abs(r.item()) + 2e-3, (name, g.item(), r.item())
+    (ref[0] + 0.3 * ref[2] + 0.05 * ref[3] + 0.001 * ref[1]).backward()
+    (got[0] + 0.3 * got[2] + 0.05 * got[3] + 0.001 * got[1]).backward()
+    ops.check_errors()
+    worst = []
+    for (name, p), q in zip(cpu_model.named_parameters(), gpu_model.parameters()):
+        assert q.grad is not None and torch.isfinite(q.grad).all(), name
+        denom = p.grad.norm().item()
+        if denom > 1e-6:
+            worst.append(((q.grad.cpu().float() - p.grad).norm().item() / denom, name))
+    worst.sort(reverse=True)
+    # bf16 activations against an fp32 oracle: gradients agree in direction and scale
+    assert worst[0][0] < 0.35, worst[:5]
+    assert sum(w for w, _ in worst) / len(worst) < 0.08, worst[:5]
+
+
+def test_public_training_step_reduces_loss():
+    from q38.train import TRAIN_DEFAULTS, Trainer
+    from q38 import ops
+    cfg, _ = build()
+    args = SimpleNamespace(**{**TRAIN_DEFAULTS, "aux_coef": 0.001, "lr": 3e-3, "grad_sync": "collective"})
+    trainer = Trainer(cfg, args, torch.device("cuda", 0))
+    torch.manual_seed(1)
+    x = torch.randint(1, 512, (4, 256)).pin_memory()
+    y = x.roll(-1, 1).pin_memory()
+    first = trainer.train_step([(x[:2], y[:2]), (x[2:], y[2:])], lr=3e-3, dense=True).tolist()
+    for _ in range(6):
+        last = trainer.train_step([(x[:2], y[:2]), (x[2:], y[2:])], lr=3e-3, dense=False).tolist()
+    ops.check_errors()
+    assert all(v == v for v in last) and last[0] < first[0] - 0.05, (first, last)
+    assert ops.launch_count() > 0
+    # replicated shadow stays in sync with the fp32 master weights
+    arena = trainer.engine.arena
+    assert torch.equal(arena.shadow, arena.params.to(torch.bfloat16))
+
+
+def test_graft_smoke():
+    import __graft_entry__ as entry
+    entry.smoke()
