@@ -15,6 +15,22 @@ TORCH_LIBRARY(q38, m) {
   m.def("gated_rmsnorm_bwd(Tensor dy, Tensor x, Tensor gate, Tensor w, float eps) -> Tensor[]");
   m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps) -> ()");
   m.def("sum_squares(Tensor x) -> Tensor");
+  m.def("moe_route_fwd(Tensor logits, int k) -> Tensor[]");
+  m.def("moe_route_bwd(Tensor probs, Tensor top_idx, Tensor top_w, Tensor d_top_w, Tensor? d_prob_sum) -> Tensor");
+  m.def("moe_sort(Tensor top_idx, int E) -> Tensor[]");
+  m.def("moe_gather(Tensor x, Tensor perm, int k) -> Tensor");
+  m.def("moe_combine_fwd(Tensor y_sorted, Tensor inv_perm, Tensor top_w) -> Tensor");
+  m.def("moe_combine_bwd(Tensor dout, Tensor y_sorted, Tensor inv_perm, Tensor top_w) -> Tensor[]");
+  m.def("moe_unpermute_sum(Tensor dx_sorted, Tensor inv_perm, int T, int k) -> Tensor");
+  m.def("moe_grouped_gemm(Tensor rows, Tensor weight, Tensor(a!) out, Tensor sched, bool b_mn_major, Tensor(b!) err) -> ()");
+  m.def("moe_grouped_swiglu(Tensor rows, Tensor weight, Tensor(a!) hmid, Tensor(b!) gu, Tensor sched, Tensor(c!) err) -> ()");
+  m.def("moe_grouped_dswiglu(Tensor dy, Tensor w_down, Tensor gu, Tensor(a!) dgu, Tensor sched, Tensor(b!) err) -> ()");
+  m.def("moe_grouped_wgrad(Tensor a, Tensor b, Tensor(a!) grad, Tensor offsets, Tensor(b!) err) -> ()");
+  m.def("mhc_coef_fwd(Tensor X, Tensor Lraw, Tensor Bw, Tensor b_pre, Tensor b_post, Tensor b_res, Tensor alphas, Tensor norm_w, int iters, float norm_eps, bool out_bf16) -> Tensor[]");
+  m.def("mhc_post_fwd(Tensor X, Tensor y, Tensor coef) -> Tensor");
+  m.def("mhc_post_bwd(Tensor dXo, Tensor X, Tensor y, Tensor coef) -> Tensor[]");
+  m.def("mhc_pre_bwd_a(Tensor dxout, Tensor X, Tensor Lraw, Tensor Bw, Tensor b_pre, Tensor b_post, Tensor b_res, Tensor alphas, Tensor norm_w, Tensor coef, Tensor z, Tensor inv, Tensor rstd, Tensor(a!) dcoef, int iters) -> Tensor[]");
+  m.def("mhc_pre_bwd_c(Tensor(a!) dX, Tensor dXo, Tensor X, Tensor dxin, Tensor coef, Tensor c1) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(q38, CUDA, m) {
@@ -30,4 +46,36 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
     q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps);
   });
   m.impl("sum_squares", &q38::sum_squares);
+  m.impl("moe_route_fwd", &q38::moe_route_fwd);
+  m.impl("moe_route_bwd", [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, const at::Tensor& d, c10::optional<at::Tensor> e) {
+    return q38::moe_route_bwd(a, b, c, d, e);
+  });
+  m.impl("moe_sort", &q38::moe_sort);
+  m.impl("moe_gather", &q38::moe_gather);
+  m.impl("moe_combine_fwd", &q38::moe_combine_fwd);
+  m.impl("moe_combine_bwd", &q38::moe_combine_bwd);
+  m.impl("moe_unpermute_sum", &q38::moe_unpermute_sum);
+  m.impl("moe_grouped_gemm", [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, const at::Tensor& d, bool mn, at::Tensor& err) {
+    q38::moe_grouped_gemm(a, b, c, d, mn, err);
+  });
+  m.impl("moe_grouped_swiglu", [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, at::Tensor& d, const at::Tensor& e, at::Tensor& err) {
+    q38::moe_grouped_swiglu(a, b, c, d, e, err);
+  });
+  m.impl("moe_grouped_dswiglu", [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, at::Tensor& d, const at::Tensor& e, at::Tensor& err) {
+    q38::moe_grouped_dswiglu(a, b, c, d, e, err);
+  });
+  m.impl("moe_grouped_wgrad", [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, const at::Tensor& d, at::Tensor& err) {
+    q38::moe_grouped_wgrad(a, b, c, d, err);
+  });
+  m.impl("mhc_coef_fwd", &q38::mhc_coef_fwd);
+  m.impl("mhc_post_fwd", &q38::mhc_post_fwd);
+  m.impl("mhc_post_bwd", &q38::mhc_post_bwd);
+  m.impl("mhc_pre_bwd_a", [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, const at::Tensor& d, const at::Tensor& e,
+                             const at::Tensor& f, const at::Tensor& g, const at::Tensor& h, const at::Tensor& i, const at::Tensor& j,
+                             const at::Tensor& k, const at::Tensor& l, const at::Tensor& mm, at::Tensor& n, int64_t it) {
+    return q38::mhc_pre_bwd_a(a, b, c, d, e, f, g, h, i, j, k, l, mm, n, it);
+  });
+  m.impl("mhc_pre_bwd_c", [](at::Tensor& dX, const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, const at::Tensor& d, const at::Tensor& e) {
+    q38::mhc_pre_bwd_c(dX, a, b, c, d, e);
+  });
 }

@@ -27,4 +27,30 @@ void adamw_flat(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v
                 c10::optional<at::Tensor> grad_scale, int64_t step, double lr, double wd, double beta1, double beta2, double eps);
 at::Tensor sum_squares(const at::Tensor& x);
 
+// mhc.cu
+std::vector<at::Tensor> mhc_coef_fwd(const at::Tensor& X, const at::Tensor& Lraw, const at::Tensor& Bw, const at::Tensor& b_pre,
+                                     const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas, const at::Tensor& norm_w,
+                                     int64_t iters, double norm_eps, bool out_bf16);
+at::Tensor mhc_post_fwd(const at::Tensor& X, const at::Tensor& y, const at::Tensor& coef);
+std::vector<at::Tensor> mhc_post_bwd(const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& y, const at::Tensor& coef);
+std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor& X, const at::Tensor& Lraw, const at::Tensor& Bw,
+                                      const at::Tensor& b_pre, const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas,
+                                      const at::Tensor& norm_w, const at::Tensor& coef, const at::Tensor& z, const at::Tensor& inv,
+                                      const at::Tensor& rstd, at::Tensor& dcoef, int64_t iters);
+void mhc_pre_bwd_c(at::Tensor& dX, const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& dxin, const at::Tensor& coef, const at::Tensor& c1);
+
+// moe.cu
+std::vector<at::Tensor> moe_route_fwd(const at::Tensor& logits, int64_t k);
+at::Tensor moe_route_bwd(const at::Tensor& probs, const at::Tensor& top_idx, const at::Tensor& top_w, const at::Tensor& d_top_w,
+                         const c10::optional<at::Tensor>& d_prob_sum);
+std::vector<at::Tensor> moe_sort(const at::Tensor& top_idx, int64_t E);
+at::Tensor moe_gather(const at::Tensor& x, const at::Tensor& perm, int64_t k);
+at::Tensor moe_combine_fwd(const at::Tensor& y_sorted, const at::Tensor& inv_perm, const at::Tensor& top_w);
+std::vector<at::Tensor> moe_combine_bwd(const at::Tensor& dout, const at::Tensor& y_sorted, const at::Tensor& inv_perm, const at::Tensor& top_w);
+at::Tensor moe_unpermute_sum(const at::Tensor& dx_sorted, const at::Tensor& inv_perm, int64_t T, int64_t k);
+void moe_grouped_gemm(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err);
+void moe_grouped_swiglu(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& hmid, at::Tensor& gu, const at::Tensor& sched, at::Tensor& err);
+void moe_grouped_dswiglu(const at::Tensor& dy, const at::Tensor& w_down, const at::Tensor& gu, at::Tensor& dgu, const at::Tensor& sched, at::Tensor& err);
+void moe_grouped_wgrad(const at::Tensor& a, const at::Tensor& b, at::Tensor& grad, const at::Tensor& offsets, at::Tensor& err);
+
 }  // namespace q38

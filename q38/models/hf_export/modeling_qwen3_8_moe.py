@@ -480,7 +480,9 @@ class Qwen3_8MoeSparseMoeBlock(nn.Module):
     def forward(self, x):
         fast = _hook("moe_block", x)
         if fast is not None:
-            return fast(self, x)
+            out = fast(self, x)
+            if out is not None:
+                return out
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         _, top_w, top_idx, probs = self.gate(x2)

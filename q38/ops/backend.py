@@ -86,6 +86,146 @@ class _GatedRMSNorm(torch.autograd.Function):
         return dx, dgate, dw.to(weight.dtype), None
 
 
+class _MhcLink:
+    """Carries the gradient of a sub-layer's output stream from `_MhcPost.backward` to `_MhcPreNorm.backward`, which
+    writes the complete gradient of the input stream in one pass (the residual-mix term is folded in there)."""
+    __slots__ = ("dXo",)
+
+    def __init__(self):
+        self.dXo = None
+
+
+class _MhcPreNorm(torch.autograd.Function):
+    """(X, mHC parameters, norm weight) -> (normalised sub-layer input, coefficient rows)."""
+
+    @staticmethod
+    def forward(ctx, X, A_w, B_w, b_pre, b_post, b_res, alphas, norm_w, iters, eps, out_dtype, link):
+        ops = load()
+        B_, S, n, h = X.shape
+        Xc = X.contiguous()
+        Xf = Xc.view(B_ * S, n * h)
+        Lraw = Xf @ A_w.float().t()                          # low-rank projection, fp32
+        xout, coef, z, inv, rstd = ops.mhc_coef_fwd(Xc.view(B_ * S, n, h), Lraw, B_w.float().contiguous(), b_pre.float().contiguous(),
+                                                    b_post.float().contiguous(), b_res.float().contiguous(), alphas.float().contiguous(),
+                                                    norm_w.float().contiguous(), iters, eps, out_dtype == torch.bfloat16)
+        ctx.save_for_backward(Xc, Lraw, coef, z, inv, rstd, A_w, B_w, b_pre, b_post, b_res, alphas, norm_w)
+        ctx.iters, ctx.link, ctx.shape = iters, link, X.shape
+        ctx.mark_non_differentiable(z)
+        return xout.view(B_, S, h), coef
+
+    @staticmethod
+    def backward(ctx, dxout, dcoef):
+        ops = load()
+        Xc, Lraw, coef, z, inv, rstd, A_w, B_w, b_pre, b_post, b_res, alphas, norm_w = ctx.saved_tensors
+        B_, S, n, h = ctx.shape
+        T = B_ * S
+        if dcoef is None:
+            dcoef = torch.zeros_like(coef)
+        dcoef = dcoef.contiguous()
+        dLraw, c1, dxin, dBw, dbias, dnw = ops.mhc_pre_bwd_a(
+            dxout.reshape(T, h).contiguous(), Xc.view(T, n, h), Lraw, B_w.float().contiguous(), b_pre.float().contiguous(),
+            b_post.float().contiguous(), b_res.float().contiguous(), alphas.float().contiguous(), norm_w.float().contiguous(),
+            coef, z, inv, rstd, dcoef, ctx.iters)
+        Xf = Xc.view(T, n * h)
+        dA = dLraw.t() @ Xf
+        dX = dLraw @ A_w.float()                              # G, completed in place below
+        dXo = ctx.link.dXo if ctx.link.dXo is not None else torch.zeros_like(Xf)
+        ctx.link.dXo = None
+        ops.mhc_pre_bwd_c(dX.view(T, n, h), dXo.contiguous().view(T, n, h), Xc.view(T, n, h), dxin, coef, c1)
+        return (dX.view(B_, S, n, h), dA.to(A_w.dtype), dBw.to(B_w.dtype), dbias[0:4].to(b_pre.dtype), dbias[4:8].to(b_post.dtype),
+                dbias[8:24].view(4, 4).to(b_res.dtype), dbias[24:27].to(alphas.dtype), dnw.to(norm_w.dtype), None, None, None, None)
+
+
+class _MhcPost(torch.autograd.Function):
+    """X'_m = sum_n res[m,n] X_n + post_m y.  The gradient w.r.t. X is delivered through `link` (see `_MhcLink`)."""
+
+    @staticmethod
+    def forward(ctx, X, y, coef, link):
+        B_, S, n, h = X.shape
+        Xc, yc = X.contiguous(), y.contiguous()
+        out = load().mhc_post_fwd(Xc.view(B_ * S, n, h), yc.view(B_ * S, h), coef)
+        ctx.save_for_backward(Xc, yc, coef)
+        ctx.link, ctx.shape = link, X.shape
+        return out.view(B_, S, n, h)
+
+    @staticmethod
+    def backward(ctx, dXo):
+        Xc, yc, coef = ctx.saved_tensors
+        B_, S, n, h = ctx.shape
+        dXo = dXo.contiguous()
+        dy, dcoef = load().mhc_post_bwd(dXo.view(B_ * S, n, h), Xc.view(B_ * S, n, h), yc.view(B_ * S, h), coef)
+        ctx.link.dXo = dXo
+        return None, dy.view(B_, S, h), dcoef, None
+
+
+class _Route(torch.autograd.Function):
+    """bf16 router logits -> (top-k weights, indices, per-expert probability sums, per-expert assignment counts)."""
+
+    @staticmethod
+    def forward(ctx, logits, k):
+        top_w, top_idx, probs, counts, prob_sum = load().moe_route_fwd(logits.contiguous(), k)
+        ctx.save_for_backward(probs, top_idx, top_w)
+        ctx.mark_non_differentiable(top_idx, counts)
+        return top_w, top_idx, prob_sum, counts
+
+    @staticmethod
+    def backward(ctx, d_top_w, _idx, d_prob_sum, _counts):
+        probs, top_idx, top_w = ctx.saved_tensors
+        if d_top_w is None:
+            d_top_w = torch.zeros_like(top_w)
+        dps = None if d_prob_sum is None else d_prob_sum.float().contiguous()
+        return load().moe_route_bwd(probs, top_idx, top_w, d_top_w.float().contiguous(), dps), None
+
+
+class _Experts(torch.autograd.Function):
+    """Routed experts over expert-sorted rows: gather -> grouped gate/up GEMM with SwiGLU epilogue -> grouped down GEMM ->
+    weighted combine in slot order.  Backward runs the mirrored grouped GEMMs; weight gradients are accumulated in fp32
+    straight into the parameters' gradient buffers when those exist."""
+
+    @staticmethod
+    def forward(ctx, x, top_w, top_idx, w_gate_up, w_down):
+        ops, err = load(), error_flag(x.device)
+        T, h = x.shape
+        E, f2, _ = w_gate_up.shape
+        k = top_idx.shape[1]
+        perm, inv, offsets, sched = ops.moe_sort(top_idx, E)
+        xs = ops.moe_gather(x.contiguous(), perm, k)
+        hmid = torch.empty(T * k, f2 // 2, dtype=torch.bfloat16, device=x.device)
+        gu = torch.empty(T * k, f2, dtype=torch.bfloat16, device=x.device)
+        ops.moe_grouped_swiglu(xs, _bf16_weight(w_gate_up), hmid, gu, sched, err)
+        ys = torch.empty(T * k, h, dtype=torch.bfloat16, device=x.device)
+        ops.moe_grouped_gemm(hmid, _bf16_weight(w_down), ys, sched, False, err)
+        out = ops.moe_combine_fwd(ys, inv, top_w)
+        ctx.save_for_backward(xs, gu, hmid, ys, inv, offsets, sched, top_w, w_gate_up, w_down)
+        ctx.dims = (T, k)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ops, err = load(), error_flag(dout.device)
+        xs, gu, hmid, ys, inv, offsets, sched, top_w, w_gate_up, w_down = ctx.saved_tensors
+        T, k = ctx.dims
+        dy, d_top_w = ops.moe_combine_bwd(dout.to(torch.bfloat16).contiguous(), ys, inv, top_w)
+        dgu = torch.empty_like(gu)
+        ops.moe_grouped_dswiglu(dy, _bf16_weight(w_down), gu, dgu, sched, err)
+        dxs = torch.empty_like(xs)
+        ops.moe_grouped_gemm(dgu, _bf16_weight(w_gate_up), dxs, sched, True, err)
+        dx = ops.moe_unpermute_sum(dxs, inv, T, k)
+
+        def weight_grad(a, b, weight):
+            grad = weight.grad
+            if grad is not None and grad.dtype == torch.float32 and grad.is_contiguous():
+                ops.moe_grouped_wgrad(a, b, grad, offsets, err)          # accumulate in place; autograd gets no extra tensor
+                return None
+            fresh = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+            ops.moe_grouped_wgrad(a, b, fresh, offsets, err)
+            return fresh.to(weight.dtype)
+
+        d_down = weight_grad(dy, hmid, w_down) if ctx.needs_input_grad[4] else None
+        d_gate_up = weight_grad(dgu, xs, w_gate_up) if ctx.needs_input_grad[3] else None
+        return dx, d_top_w, None, d_gate_up, d_down
+
+
 class Backend:
     def __init__(self, self_check=True):
         self.ops = load()
@@ -146,6 +286,33 @@ class Backend:
         if x.dtype != torch.bfloat16 or x.shape[-1] != 64:
             return None
         return _GatedRMSNorm.apply(x, gate, weight, eps)
+
+    def mhc_pre_norm(self, mhc, norm, X, dtype):
+        link = _MhcLink()
+        x, coef = _MhcPreNorm.apply(X, mhc.A.weight, mhc.B.weight, mhc.b_pre, mhc.b_post, mhc.b_res, mhc.alphas, norm.weight,
+                                    mhc.iters, norm.eps, dtype, link)
+        return x, (X, coef, link)
+
+    def mhc_post(self, mhc, y, state):
+        X, coef, link = state
+        return _MhcPost.apply(X, y, coef, link)
+
+    def moe_block(self, block, x):
+        experts = block.experts
+        E, f, h = experts.num_experts, experts.intermediate_dim, experts.hidden_dim
+        if x.dtype != torch.bfloat16 or E > 64 or block.gate.top_k > 8 or f % 16 or f > 256 or h % 8:
+            return None
+        shape = x.shape
+        x2 = x.reshape(-1, h)
+        logits = self.linear(x2, block.gate.weight)
+        top_w, top_idx, prob_sum, counts = _Route.apply(logits, block.gate.top_k)
+        if block._recording():
+            block.stats_sink.add(counts, prob_sum, x2.shape[0])
+        routed = _Experts.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj)
+        shared_gate = torch.sigmoid(self.linear(x2, block.shared_expert_gate.weight))
+        shared = block.shared_expert
+        mid = torch.nn.functional.silu(self.linear(x2, shared.gate_proj.weight)) * self.linear(x2, shared.up_proj.weight)
+        return (routed + shared_gate * self.linear(mid, shared.down_proj.weight)).reshape(shape)
 
     def linear_cross_entropy(self, weight, hidden, target, reduction):
         """Chunked logits + CE; logits of one chunk only ever exist, in fp32."""

@@ -143,3 +143,120 @@ def test_muon_gpu_matches_reference(ops, monkeypatch):
     for p, q in zip(fast, slow):
         torch.testing.assert_close(p, q, rtol=1e-3, atol=2e-4)
         torch.testing.assert_close(a.state[p]["buf"], b.state[q]["buf"], rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("h,iters,dtype", [(128, 5, torch.bfloat16), (576, 20, torch.bfloat16), (64, 3, torch.float32)])
+def test_mhc_sublayer_matches_specification(ops, h, iters, dtype):
+    """pre -> (toy sub-layer) -> post through the fused kernels against the PyTorch mHC module, values and all gradients."""
+    from q38.models import modeling
+    backend = modeling.get_backend()
+    torch.manual_seed(8)
+    mhc = modeling.MHC(h, 4, max(1, round(h / 8)), slot=1, iters=iters).cuda()
+    with torch.no_grad():
+        mhc.B.weight.normal_(0, 0.3)
+        mhc.alphas.fill_(0.7)
+        mhc.b_res.add_(torch.randn(4, 4, device="cuda"))
+    norm = modeling.Qwen3_8MoeRMSNorm(h).cuda()
+    with torch.no_grad():
+        norm.weight.normal_(0, 0.1)
+    X = torch.randn(2, 96, 4, h, device="cuda")
+    W = (torch.randn(h, h, device="cuda") / h ** 0.5)
+    dXo = torch.randn(2, 96, 4, h, device="cuda")
+
+    def run(fast):
+        Xl = X.clone().requires_grad_()
+        for p in list(mhc.parameters()) + list(norm.parameters()):
+            p.grad = None
+        if fast:
+            x, state = backend.mhc_pre_norm(mhc, norm, Xl, dtype)
+        else:
+            xin, state = mhc.pre(Xl)
+            x = norm(xin, out_dtype=dtype)
+        y = (x.float() @ W).to(dtype)
+        out = backend.mhc_post(mhc, y, state) if fast else mhc.post(y, state)
+        out.backward(dXo)
+        grads = {n: p.grad.clone() for n, p in list(mhc.named_parameters()) + [("norm", norm.weight)]}
+        return x, out, Xl.grad, grads
+
+    xa, oa, ga, pa = run(True)
+    xb, ob, gb, pb = run(False)
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-4
+    assert rel_err(xa, xb) < tol and rel_err(oa, ob) < tol
+    assert rel_err(ga, gb) < tol
+    for name in pb:
+        assert rel_err(pa[name], pb[name]) < 3 * tol, name
+
+
+def test_moe_sort_is_a_stable_sort(ops):
+    torch.manual_seed(9)
+    T, k, E = 3000, 5, 64
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    idx[:500] = torch.tensor([3, 1, 4, 15, 9], dtype=torch.int32, device="cuda")          # heavy skew
+    perm, inv, offsets, sched = ops.load().moe_sort(idx, E)
+    order = torch.sort(idx.reshape(-1).long(), stable=True).indices
+    assert torch.equal(perm.long(), order)
+    assert torch.equal(inv.long()[order], torch.arange(T * k, device="cuda"))
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E)
+    assert torch.equal(offsets.long(), torch.cat([counts.new_zeros(1), counts.cumsum(0)]))
+    n_tiles = int(sched[0])
+    tiles = sched[1:1 + 3 * n_tiles].view(-1, 3)
+    assert int(tiles[:, 2].sum()) == T * k and n_tiles == int(((counts + 127) // 128).sum())
+    for e, row0, rows in tiles.tolist():
+        assert offsets[e] <= row0 and row0 + rows <= offsets[e + 1] and 0 < rows <= 128
+
+
+@pytest.mark.parametrize("T,h,f,E,k", [(700, 128, 32, 8, 2), (4096, 576, 144, 64, 5)])
+def test_moe_block_matches_specification(ops, T, h, f, E, k):
+    from types import SimpleNamespace
+    from q38.models import modeling, RouterStats
+    torch.manual_seed(10)
+    cfg = SimpleNamespace(num_experts=E, num_experts_per_tok=k, hidden_size=h, moe_intermediate_size=f, shared_expert_intermediate_size=f)
+    block = modeling.Qwen3_8MoeSparseMoeBlock(cfg).cuda().train()
+    with torch.no_grad():
+        for p in block.parameters():
+            p.normal_(0, 0.05)
+        block.gate.weight.normal_(0, 0.5)
+    x = torch.randn(1, T, h, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(1, T, h, device="cuda").to(torch.bfloat16)
+    backend = modeling.get_backend()
+
+    def run(fast):
+        modeling.set_backend(backend if fast else None)
+        try:
+            for p in block.parameters():
+                p.grad = None
+            xl = x.clone().requires_grad_()
+            block.stats_sink = RouterStats(E)
+            y = block(xl)
+            aux = block.stats_sink.loss()
+            block.stats_sink = None
+            (y.float() * dy.float()).sum().add(aux * 3.0).backward()
+            return y, aux, xl.grad, {n: p.grad.clone() for n, p in block.named_parameters()}
+        finally:
+            modeling.set_backend(backend)
+
+    ya, auxa, gxa, pa = run(True)
+    ops.check_errors()
+    yb, auxb, gxb, pb = run(False)
+    assert rel_err(ya, yb) < 3e-2 and abs(auxa.item() - auxb.item()) < 1e-2 * abs(auxb.item())
+    assert rel_err(gxa, gxb) < 5e-2
+    for name in pb:
+        assert rel_err(pa[name], pb[name]) < 5e-2, name
+
+
+def test_moe_weight_gradients_accumulate_in_place(ops):
+    from q38.ops.backend import _Experts
+    torch.manual_seed(11)
+    T, h, f, E, k = 900, 128, 32, 8, 2
+    wgu = torch.nn.Parameter(0.05 * torch.randn(E, 2 * f, h, device="cuda"))
+    wd = torch.nn.Parameter(0.05 * torch.randn(E, h, f, device="cuda"))
+    x = torch.randn(T, h, device="cuda").to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, k, device="cuda")
+    out = _Experts.apply(x, w, idx, wgu, wd)
+    out.float().sum().backward()
+    first = (wgu.grad.clone(), wd.grad.clone())
+    out = _Experts.apply(x, w, idx, wgu, wd)
+    out.float().sum().backward()                      # second pass accumulates into the existing buffers
+    ops.check_errors()
+    assert rel_err(wgu.grad, 2 * first[0]) < 1e-5 and rel_err(wd.grad, 2 * first[1]) < 1e-5
