@@ -15,6 +15,8 @@ TORCH_LIBRARY(q38, m) {
   m.def("gated_rmsnorm_bwd(Tensor dy, Tensor x, Tensor gate, Tensor w, float eps) -> Tensor[]");
   m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps) -> ()");
   m.def("sum_squares(Tensor x) -> Tensor");
+  m.def("gdn_scan_fwd(Tensor w, Tensor u, Tensor P, Tensor qg, Tensor kg, Tensor dch, int B, int H) -> Tensor[]");
+  m.def("gdn_scan_bwd(Tensor w, Tensor P, Tensor qg, Tensor kg, Tensor dch, Tensor vnew, Tensor states, Tensor dout, int B, int H) -> Tensor[]");
   m.def("moe_route_fwd(Tensor logits, int k) -> Tensor[]");
   m.def("moe_route_bwd(Tensor probs, Tensor top_idx, Tensor top_w, Tensor d_top_w, Tensor? d_prob_sum) -> Tensor");
   m.def("moe_sort(Tensor top_idx, int E) -> Tensor[]");
@@ -46,6 +48,8 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
     q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps);
   });
   m.impl("sum_squares", &q38::sum_squares);
+  m.impl("gdn_scan_fwd", &q38::gdn_scan_fwd);
+  m.impl("gdn_scan_bwd", &q38::gdn_scan_bwd);
   m.impl("moe_route_fwd", &q38::moe_route_fwd);
   m.impl("moe_route_bwd", [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, const at::Tensor& d, c10::optional<at::Tensor> e) {
     return q38::moe_route_bwd(a, b, c, d, e);

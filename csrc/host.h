@@ -53,4 +53,10 @@ void moe_grouped_swiglu(const at::Tensor& rows, const at::Tensor& weight, at::Te
 void moe_grouped_dswiglu(const at::Tensor& dy, const at::Tensor& w_down, const at::Tensor& gu, at::Tensor& dgu, const at::Tensor& sched, at::Tensor& err);
 void moe_grouped_wgrad(const at::Tensor& a, const at::Tensor& b, at::Tensor& grad, const at::Tensor& offsets, at::Tensor& err);
 
+// gdn.cu
+std::vector<at::Tensor> gdn_scan_fwd(const at::Tensor& w, const at::Tensor& u, const at::Tensor& P, const at::Tensor& qg, const at::Tensor& kg,
+                                     const at::Tensor& dch, int64_t B, int64_t H);
+std::vector<at::Tensor> gdn_scan_bwd(const at::Tensor& w, const at::Tensor& P, const at::Tensor& qg, const at::Tensor& kg, const at::Tensor& dch,
+                                     const at::Tensor& vnew, const at::Tensor& states, const at::Tensor& dout, int64_t B, int64_t H);
+
 }  // namespace q38

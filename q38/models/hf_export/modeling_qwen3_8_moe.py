@@ -135,15 +135,14 @@ def l2norm(x, eps=1e-6):
     return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
 
 
-def gated_delta_rule_chunked(q, k, v, g, beta, chunk=BLK):
-    """Chunked gated delta rule; the fp32 specification of the GDN kernels.
+def gdn_chunk_operands(q, k, v, g, beta, chunk=BLK):
+    """Per-chunk operands of the chunked delta rule, all ``[B,Hv,n,chunk,D]`` fp32 (``carry`` is ``[B,Hv,n]``).
 
-    q,k ``[B,S,Hk,D]``; v ``[B,S,Hv,D]``; g (log decay, <= 0) and beta ``[B,S,Hv]``.  Value head j
-    reads key head ``j // (Hv/Hk)``.  q and k are L2-normalised, q is scaled by ``D**-0.5``.
-    Per head and token: ``S <- exp(g) S;  S <- S + k (beta (v - S^T k))^T;  o = S^T q``.
-    The state starts at zero and is not reset at document boundaries.
+    With ``gc`` the cumulative log-decay inside a chunk and ``Gamma_ij = exp(gc_i - gc_j)``:
+    ``Tm = (I + tril(beta_i (k_i.k_j) Gamma_ij, -1))^-1``, ``w = Tm (beta e^gc k)``, ``u = Tm (beta v)``,
+    ``P = tril((q_i.k_j) Gamma_ij)``, ``qg = q e^gc``, ``kg = k e^(gc_last - gc)``, ``carry = e^gc_last``.
+    q and k are L2-normalised and q is scaled by ``D**-0.5``.  The sequence is right-padded to a multiple of the chunk.
     """
-    out_dtype = q.dtype
     B, S, Hk, D = k.shape
     Hv = v.shape[2]
     rep = Hv // Hk
@@ -156,7 +155,7 @@ def gated_delta_rule_chunked(q, k, v, g, beta, chunk=BLK):
     tr = lambda t: F.pad(t.float().transpose(1, 2), (0, 0, 0, pad) if t.dim() == 4 else (0, pad))
     q, k, v, g, beta = tr(q), tr(k), tr(v), tr(g), tr(beta)               # [B,H,Sp,(D)]
     n = (S + pad) // chunk
-    q, k, v = (t.reshape(B, Hv, n, chunk, D) for t in (q, k, v))
+    q, k, v = (t.reshape(B, Hv, n, chunk, -1) for t in (q, k, v))
     g, beta = g.reshape(B, Hv, n, chunk), beta.reshape(B, Hv, n, chunk)
     gc = g.cumsum(-1)                                                        # decay from chunk start
     diff = gc[..., :, None] - gc[..., None, :]
@@ -166,17 +165,29 @@ def gated_delta_rule_chunked(q, k, v, g, beta, chunk=BLK):
     system = (kb @ k.transpose(-1, -2)) * decay                             # unit lower-triangular system
     u = torch.linalg.solve_triangular(system, vb, upper=False, unitriangular=True)
     w = torch.linalg.solve_triangular(system, kb * gc.exp()[..., None], upper=False, unitriangular=True)
-    intra = (q @ k.transpose(-1, -2)) * decay
-    q_in = q * gc.exp()[..., None]
-    k_out = k * (gc[..., -1:] - gc).exp()[..., None]
-    carry = gc[..., -1].exp()[..., None, None]
-    state = q.new_zeros(B, Hv, D, v.shape[-1])
+    return dict(w=w, u=u, P=(q @ k.transpose(-1, -2)) * decay, qg=q * gc.exp()[..., None],
+                kg=k * (gc[..., -1:] - gc).exp()[..., None], carry=gc[..., -1].exp())
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, chunk=BLK):
+    """Chunked gated delta rule; the fp32 specification of the GDN kernels.
+
+    q,k ``[B,S,Hk,D]``; v ``[B,S,Hv,D]``; g (log decay, <= 0) and beta ``[B,S,Hv]``.  Value head j
+    reads key head ``j // (Hv/Hk)``.  Per head and token:
+    ``S <- exp(g) S;  S <- S + k (beta (v - S^T k))^T;  o = S^T q``.
+    The state starts at zero and is not reset at document boundaries.
+    """
+    out_dtype = q.dtype
+    B, S = k.shape[:2]
+    ops = gdn_chunk_operands(q, k, v, g, beta, chunk)
+    n = ops["w"].shape[2]
+    state = ops["w"].new_zeros(B, v.shape[2], k.shape[-1], v.shape[-1])
     outs = []
     for i in range(n):
-        v_new = u[:, :, i] - w[:, :, i] @ state
-        outs.append(q_in[:, :, i] @ state + intra[:, :, i] @ v_new)
-        state = state * carry[:, :, i] + k_out[:, :, i].transpose(-1, -2) @ v_new
-    o = torch.stack(outs, 2).reshape(B, Hv, n * chunk, -1)[:, :, :S]
+        v_new = ops["u"][:, :, i] - ops["w"][:, :, i] @ state
+        outs.append(ops["qg"][:, :, i] @ state + ops["P"][:, :, i] @ v_new)
+        state = state * ops["carry"][:, :, i, None, None] + ops["kg"][:, :, i].transpose(-1, -2) @ v_new
+    o = torch.stack(outs, 2).reshape(B, v.shape[2], n * chunk, -1)[:, :, :S]
     return o.transpose(1, 2).contiguous().to(out_dtype)
 
 
@@ -231,7 +242,9 @@ class Qwen3_8MoeGatedDeltaNet(nn.Module):
     def forward(self, x):
         fast = _hook("gated_deltanet", x)
         if fast is not None:
-            return fast(self, x)
+            out = fast(self, x)
+            if out is not None:
+                return out
         B, S, _ = x.shape
         qkv = causal_conv_silu(_linear(x, self.in_proj_qkv.weight), self.conv1d.weight)
         q, k, v = qkv.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)

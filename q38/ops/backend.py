@@ -158,6 +158,27 @@ class _MhcPost(torch.autograd.Function):
         return None, dy.view(B_, S, h), dcoef, None
 
 
+class _GdnScan(torch.autograd.Function):
+    """Sequential pass of the chunked delta rule over prepared chunk operands (see csrc/gdn.cu)."""
+
+    @staticmethod
+    def forward(ctx, w, u, P, qg, kg, carry, B, H):
+        w, u, P, qg, kg = (t.to(torch.bfloat16).contiguous() for t in (w, u, P, qg, kg))
+        carry = carry.float().contiguous()
+        o, vnew, states = load().gdn_scan_fwd(w, u, P, qg, kg, carry, B, H)
+        ctx.save_for_backward(w, P, qg, kg, carry, vnew, states)
+        ctx.dims = (B, H)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        w, P, qg, kg, carry, vnew, states = ctx.saved_tensors
+        B, H = ctx.dims
+        dw, du, dP, dqg, dkg, dd = load().gdn_scan_bwd(w, P, qg, kg, carry, vnew, states, do.to(torch.bfloat16).contiguous(), B, H)
+        shape = w.shape
+        return dw.view(shape), du.view(shape), dP.view(shape), dqg.view(shape), dkg.view(shape), dd.view(carry.shape), None, None
+
+
 class _Route(torch.autograd.Function):
     """bf16 router logits -> (top-k weights, indices, per-expert probability sums, per-expert assignment counts)."""
 
@@ -296,6 +317,30 @@ class Backend:
     def mhc_post(self, mhc, y, state):
         X, coef, link = state
         return _MhcPost.apply(X, y, coef, link)
+
+    def delta_rule(self, q, k, v, g, beta):
+        """q,k [B,S,Hk,64], v [B,S,Hv,64] bf16, g fp32 / beta [B,S,Hv] -> o [B,S,Hv,64] bf16 (S a multiple of 64)."""
+        from ..models import modeling
+        B, S, Hv = v.shape[0], v.shape[1], v.shape[2]
+        ops = modeling.gdn_chunk_operands(q, k, v, g, beta)
+        flat = lambda t: t.reshape(B * Hv, -1, 64, 64)
+        return _GdnScan.apply(flat(ops["w"]), flat(ops["u"]), flat(ops["P"]), flat(ops["qg"]), flat(ops["kg"]),
+                              ops["carry"].reshape(B * Hv, -1), B, Hv)
+
+    def gated_deltanet(self, m, x):
+        B, S, _ = x.shape
+        if x.dtype != torch.bfloat16 or S % 64 or m.head_k_dim != 64 or m.head_v_dim != 64:
+            return None
+        from ..models import modeling
+        F = torch.nn.functional
+        qkv = modeling.causal_conv_silu(self.linear(x, m.in_proj_qkv.weight), m.conv1d.weight)
+        q, k, v = qkv.split([m.key_dim, m.key_dim, m.value_dim], dim=-1)
+        z = self.linear(x, m.in_proj_z.weight)
+        beta = self.linear(x, m.in_proj_b.weight).sigmoid()
+        g = -m.A_log.float().exp() * F.softplus(self.linear(x, m.in_proj_a.weight).float() + m.dt_bias.float())
+        o = self.delta_rule(q.reshape(B, S, -1, 64), k.reshape(B, S, -1, 64), v.reshape(B, S, -1, 64), g, beta)
+        o = self.gated_rmsnorm(o.reshape(-1, 64), z.reshape(-1, 64), m.norm.weight, m.norm.variance_epsilon)
+        return self.linear(o.reshape(B, S, -1), m.out_proj.weight)
 
     def moe_block(self, block, x):
         experts = block.experts

@@ -260,3 +260,29 @@ def test_moe_weight_gradients_accumulate_in_place(ops):
     out.float().sum().backward()                      # second pass accumulates into the existing buffers
     ops.check_errors()
     assert rel_err(wgu.grad, 2 * first[0]) < 1e-5 and rel_err(wd.grad, 2 * first[1]) < 1e-5
+
+
+@pytest.mark.parametrize("B,S,Hk,Hv", [(1, 128, 1, 2), (2, 512, 2, 6)])
+def test_delta_rule_scan_matches_specification(ops, B, S, Hk, Hv):
+    from q38.models import modeling
+    backend = modeling.get_backend()
+    torch.manual_seed(12)
+    q = torch.randn(B, S, Hk, 64, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, 64, device="cuda").to(torch.bfloat16)
+    v = torch.randn(B, S, Hv, 64, device="cuda").to(torch.bfloat16)
+    g = -torch.rand(B, S, Hv, device="cuda") * 0.5
+    beta = torch.rand(B, S, Hv, device="cuda").to(torch.bfloat16)
+    do = torch.randn(B, S, Hv, 64, device="cuda").to(torch.bfloat16)
+
+    def run(fast):
+        leaves = [t.clone().requires_grad_() for t in (q, k, v, g, beta)]
+        o = backend.delta_rule(*leaves) if fast else modeling.gated_delta_rule_chunked(*leaves)
+        (o.float() * do.float()).sum().backward()
+        return o, [t.grad for t in leaves]
+
+    oa, ga = run(True)
+    ops.check_errors()
+    ob, gb = run(False)
+    assert rel_err(oa, ob) < 3e-2
+    for name, a, b in zip("q k v g beta".split(), ga, gb):
+        assert rel_err(a, b) < 6e-2, name
