@@ -15,6 +15,10 @@ TORCH_LIBRARY(q38, m) {
   m.def("gated_rmsnorm_bwd(Tensor dy, Tensor x, Tensor gate, Tensor w, float eps) -> Tensor[]");
   m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps) -> ()");
   m.def("sum_squares(Tensor x) -> Tensor");
+  m.def("conv_silu_fwd(Tensor x, Tensor w) -> Tensor");
+  m.def("conv_silu_bwd(Tensor x, Tensor w, Tensor dy) -> Tensor[]");
+  m.def("gdn_prep_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta) -> Tensor[]");
+  m.def("gdn_prep_bwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor Tm, Tensor dw, Tensor du, Tensor dP, Tensor dqg, Tensor dkg, Tensor dd) -> Tensor[]");
   m.def("gdn_scan_fwd(Tensor w, Tensor u, Tensor P, Tensor qg, Tensor kg, Tensor dch, int B, int H) -> Tensor[]");
   m.def("gdn_scan_bwd(Tensor w, Tensor P, Tensor qg, Tensor kg, Tensor dch, Tensor vnew, Tensor states, Tensor dout, int B, int H) -> Tensor[]");
   m.def("moe_route_fwd(Tensor logits, int k) -> Tensor[]");
@@ -48,6 +52,10 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
     q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps);
   });
   m.impl("sum_squares", &q38::sum_squares);
+  m.impl("conv_silu_fwd", &q38::conv_silu_fwd);
+  m.impl("conv_silu_bwd", &q38::conv_silu_bwd);
+  m.impl("gdn_prep_fwd", &q38::gdn_prep_fwd);
+  m.impl("gdn_prep_bwd", &q38::gdn_prep_bwd);
   m.impl("gdn_scan_fwd", &q38::gdn_scan_fwd);
   m.impl("gdn_scan_bwd", &q38::gdn_scan_bwd);
   m.impl("moe_route_fwd", &q38::moe_route_fwd);

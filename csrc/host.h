@@ -59,4 +59,12 @@ std::vector<at::Tensor> gdn_scan_fwd(const at::Tensor& w, const at::Tensor& u, c
 std::vector<at::Tensor> gdn_scan_bwd(const at::Tensor& w, const at::Tensor& P, const at::Tensor& qg, const at::Tensor& kg, const at::Tensor& dch,
                                      const at::Tensor& vnew, const at::Tensor& states, const at::Tensor& dout, int64_t B, int64_t H);
 
+std::vector<at::Tensor> gdn_prep_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g, const at::Tensor& beta);
+std::vector<at::Tensor> gdn_prep_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g, const at::Tensor& beta,
+                                     const at::Tensor& Tm, const at::Tensor& dw, const at::Tensor& du, const at::Tensor& dP, const at::Tensor& dqg,
+                                     const at::Tensor& dkg, const at::Tensor& dd);
+// conv.cu
+at::Tensor conv_silu_fwd(const at::Tensor& x, const at::Tensor& w);
+std::vector<at::Tensor> conv_silu_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy);
+
 }  // namespace q38

@@ -4,6 +4,8 @@ Each method is a `torch.autograd.Function` (or a composition of them) over the C
 A method that is absent makes the model use its PyTorch specification for that op; the set of present
 methods is reported by `describe()` so a run records exactly which paths were native.
 """
+import os
+
 import torch
 
 from . import error_flag, gemm, load
@@ -158,6 +160,23 @@ class _MhcPost(torch.autograd.Function):
         return None, dy.view(B_, S, h), dcoef, None
 
 
+class _ConvSilu(torch.autograd.Function):
+    """Depthwise causal conv (kernel 4) + SiLU on [B,S,C] bf16; weight is the fp32 master [C,1,4]."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        xc = x.contiguous()
+        w = weight.float().reshape(weight.shape[0], -1).contiguous()
+        ctx.save_for_backward(xc, weight)
+        return load().conv_silu_fwd(xc, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, weight = ctx.saved_tensors
+        dx, dw = load().conv_silu_bwd(xc, weight.float().reshape(weight.shape[0], -1).contiguous(), dy.contiguous())
+        return dx, dw.view(weight.shape).to(weight.dtype)
+
+
 class _GdnScan(torch.autograd.Function):
     """Sequential pass of the chunked delta rule over prepared chunk operands (see csrc/gdn.cu)."""
 
@@ -177,6 +196,30 @@ class _GdnScan(torch.autograd.Function):
         dw, du, dP, dqg, dkg, dd = load().gdn_scan_bwd(w, P, qg, kg, carry, vnew, states, do.to(torch.bfloat16).contiguous(), B, H)
         shape = w.shape
         return dw.view(shape), du.view(shape), dP.view(shape), dqg.view(shape), dkg.view(shape), dd.view(carry.shape), None, None
+
+
+class _DeltaRule(torch.autograd.Function):
+    """Chunked gated delta rule: per-chunk preparation kernel (parallel over chunks) + sequential scan kernel."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta):
+        ops = load()
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        g, beta = g.float().contiguous(), beta.to(torch.bfloat16).contiguous()
+        B, Hv = v.shape[0], v.shape[2]
+        w, u, P, qg, kg, Tm, carry, _gc = ops.gdn_prep_fwd(q, k, v, g, beta)
+        o, vnew, states = ops.gdn_scan_fwd(w, u, P, qg, kg, carry, B, Hv)
+        ctx.save_for_backward(q, k, v, g, beta, Tm, w, P, qg, kg, carry, vnew, states)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        ops = load()
+        q, k, v, g, beta, Tm, w, P, qg, kg, carry, vnew, states = ctx.saved_tensors
+        B, Hv = v.shape[0], v.shape[2]
+        dw, du, dP, dqg, dkg, dd = ops.gdn_scan_bwd(w, P, qg, kg, carry, vnew, states, do.to(torch.bfloat16).contiguous(), B, Hv)
+        dq, dk, dv, dg, dbeta = ops.gdn_prep_bwd(q, k, v, g, beta, Tm, dw, du, dP, dqg, dkg, dd)
+        return dq, dk, dv, dg, dbeta
 
 
 class _Route(torch.autograd.Function):
@@ -251,6 +294,8 @@ class Backend:
     def __init__(self, self_check=True):
         self.ops = load()
         self.layouts = dict(nt=True, nn=True, tn=True)       # which GEMM operand layouts passed the self-check
+        # True: chunk operands come from the PyTorch specification and only the scan runs in the CUDA kernel (debug aid)
+        self.hybrid_delta_rule = bool(int(os.environ.get("Q38_GDN_HYBRID", "0")))
         if self_check:
             self._self_check()
 
@@ -320,6 +365,8 @@ class Backend:
 
     def delta_rule(self, q, k, v, g, beta):
         """q,k [B,S,Hk,64], v [B,S,Hv,64] bf16, g fp32 / beta [B,S,Hv] -> o [B,S,Hv,64] bf16 (S a multiple of 64)."""
+        if not self.hybrid_delta_rule:
+            return _DeltaRule.apply(q, k, v, g, beta)
         from ..models import modeling
         B, S, Hv = v.shape[0], v.shape[1], v.shape[2]
         ops = modeling.gdn_chunk_operands(q, k, v, g, beta)
@@ -333,7 +380,7 @@ class Backend:
             return None
         from ..models import modeling
         F = torch.nn.functional
-        qkv = modeling.causal_conv_silu(self.linear(x, m.in_proj_qkv.weight), m.conv1d.weight)
+        qkv = _ConvSilu.apply(self.linear(x, m.in_proj_qkv.weight), m.conv1d.weight)
         q, k, v = qkv.split([m.key_dim, m.key_dim, m.value_dim], dim=-1)
         z = self.linear(x, m.in_proj_z.weight)
         beta = self.linear(x, m.in_proj_b.weight).sigmoid()

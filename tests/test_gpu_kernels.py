@@ -262,10 +262,12 @@ def test_moe_weight_gradients_accumulate_in_place(ops):
     assert rel_err(wgu.grad, 2 * first[0]) < 1e-5 and rel_err(wd.grad, 2 * first[1]) < 1e-5
 
 
+@pytest.mark.parametrize("hybrid", [True, False])
 @pytest.mark.parametrize("B,S,Hk,Hv", [(1, 128, 1, 2), (2, 512, 2, 6)])
-def test_delta_rule_scan_matches_specification(ops, B, S, Hk, Hv):
+def test_delta_rule_scan_matches_specification(ops, B, S, Hk, Hv, hybrid):
     from q38.models import modeling
     backend = modeling.get_backend()
+    backend.hybrid_delta_rule = hybrid
     torch.manual_seed(12)
     q = torch.randn(B, S, Hk, 64, device="cuda").to(torch.bfloat16)
     k = torch.randn(B, S, Hk, 64, device="cuda").to(torch.bfloat16)
@@ -280,9 +282,28 @@ def test_delta_rule_scan_matches_specification(ops, B, S, Hk, Hv):
         (o.float() * do.float()).sum().backward()
         return o, [t.grad for t in leaves]
 
-    oa, ga = run(True)
+    try:
+        oa, ga = run(True)
+    finally:
+        backend.hybrid_delta_rule = False
     ops.check_errors()
     ob, gb = run(False)
     assert rel_err(oa, ob) < 3e-2
     for name, a, b in zip("q k v g beta".split(), ga, gb):
         assert rel_err(a, b) < 6e-2, name
+
+
+def test_conv_silu(ops):
+    from q38.models import modeling
+    from q38.ops.backend import _ConvSilu
+    torch.manual_seed(13)
+    x = torch.randn(2, 200, 96, device="cuda").to(torch.bfloat16)
+    w = (0.5 * torch.randn(96, 1, 4, device="cuda"))
+    dy = torch.randn(2, 200, 96, device="cuda").to(torch.bfloat16)
+    xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+    ya = _ConvSilu.apply(xa, wa)
+    ya.backward(dy)
+    xb, wb = x.float().requires_grad_(), w.to(torch.bfloat16).float().requires_grad_()
+    yb = modeling.causal_conv_silu(xb, wb)
+    yb.backward(dy.float())
+    assert rel_err(ya, yb) < 2e-2 and rel_err(xa.grad, xb.grad) < 2e-2 and rel_err(wa.grad, wb.grad) < 2e-2
