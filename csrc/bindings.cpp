@@ -15,6 +15,11 @@ TORCH_LIBRARY(q38, m) {
   m.def("gated_rmsnorm_bwd(Tensor dy, Tensor x, Tensor gate, Tensor w, float eps) -> Tensor[]");
   m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps) -> ()");
   m.def("sum_squares(Tensor x) -> Tensor");
+  m.def("qsa_main_block_stats(Tensor q, Tensor k, float scale) -> Tensor");
+  m.def("qsa_indexer_fwd(Tensor qi, Tensor ki, Tensor wi, float scale) -> Tensor");
+  m.def("qsa_kl_combine(Tensor? stats, Tensor blse, int nq) -> Tensor[]");
+  m.def("qsa_select(Tensor lp_blk, int budget) -> Tensor[]");
+  m.def("qsa_indexer_bwd(Tensor qi, Tensor ki, Tensor wi, Tensor blse, Tensor dblse, float gscale, float scale) -> Tensor[]");
   m.def("conv_silu_fwd(Tensor x, Tensor w) -> Tensor");
   m.def("conv_silu_bwd(Tensor x, Tensor w, Tensor dy) -> Tensor[]");
   m.def("gdn_prep_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta) -> Tensor[]");
@@ -52,6 +57,11 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
     q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps);
   });
   m.impl("sum_squares", &q38::sum_squares);
+  m.impl("qsa_main_block_stats", &q38::qsa_main_block_stats);
+  m.impl("qsa_indexer_fwd", &q38::qsa_indexer_fwd);
+  m.impl("qsa_kl_combine", [](c10::optional<at::Tensor> stats, const at::Tensor& blse, int64_t nq) { return q38::qsa_kl_combine(stats, blse, nq); });
+  m.impl("qsa_select", &q38::qsa_select);
+  m.impl("qsa_indexer_bwd", &q38::qsa_indexer_bwd);
   m.impl("conv_silu_fwd", &q38::conv_silu_fwd);
   m.impl("conv_silu_bwd", &q38::conv_silu_bwd);
   m.impl("gdn_prep_fwd", &q38::gdn_prep_fwd);

@@ -63,6 +63,13 @@ std::vector<at::Tensor> gdn_prep_fwd(const at::Tensor& q, const at::Tensor& k, c
 std::vector<at::Tensor> gdn_prep_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g, const at::Tensor& beta,
                                      const at::Tensor& Tm, const at::Tensor& dw, const at::Tensor& du, const at::Tensor& dP, const at::Tensor& dqg,
                                      const at::Tensor& dkg, const at::Tensor& dd);
+// qsa_index.cu
+at::Tensor qsa_main_block_stats(const at::Tensor& q, const at::Tensor& k, double scale);
+at::Tensor qsa_indexer_fwd(const at::Tensor& qi, const at::Tensor& ki, const at::Tensor& wi, double scale);
+std::vector<at::Tensor> qsa_kl_combine(const c10::optional<at::Tensor>& stats, const at::Tensor& blse, int64_t nq);
+std::vector<at::Tensor> qsa_select(const at::Tensor& lp_blk, int64_t budget);
+std::vector<at::Tensor> qsa_indexer_bwd(const at::Tensor& qi, const at::Tensor& ki, const at::Tensor& wi, const at::Tensor& blse, const at::Tensor& dblse,
+                                        double gscale, double scale);
 // conv.cu
 at::Tensor conv_silu_fwd(const at::Tensor& x, const at::Tensor& w);
 std::vector<at::Tensor> conv_silu_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy);

@@ -1,0 +1,99 @@
+// 64x64x64 bf16 tile products on the warp-level tensor-core path (mma.sync m16n8k16, fp32 accumulation) for kernels
+// whose chains of small dependent products are latency bound: the delta-rule scan, the QSA indexer and the block-sparse
+// attention.  Four warps cooperate on one 64x64 output; warp w owns rows 16w..16w+15 and keeps them in registers.
+#pragma once
+#include "common.cuh"
+
+namespace q38 {
+
+constexpr int C64 = 64, LDS = 72;                 // 64x64 bf16 tiles padded to 72 columns (bank-conflict-free fragment loads)
+constexpr int TILE_ELEMS = C64 * LDS;
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ uint32_t pack2(bf16 a, bf16 b) {
+  return (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+}
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// acc[64x64] += A * B with four warps; warp w owns rows 16w..16w+15.
+//   A(i,k) = TA ? As[k*LDS + i] : As[i*LDS + k]          B(k,n) = TB ? Bs[n*LDS + k] : Bs[k*LDS + n]
+// Accumulator element acc[nt][e]: row = 16w + lane/4 + 8*(e>>1), col = 8nt + 2*(lane%4) + (e&1).
+template <bool TA, bool TB>
+__device__ __forceinline__ void mma64(const bf16* __restrict__ As, const bf16* __restrict__ Bs, float (&acc)[8][4], int warp, int lane) {
+  const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    const int k0 = 16 * ks + cq;
+    uint32_t a[4];
+    if (!TA) {
+      a[0] = *reinterpret_cast<const uint32_t*>(As + r * LDS + k0);
+      a[1] = *reinterpret_cast<const uint32_t*>(As + (r + 8) * LDS + k0);
+      a[2] = *reinterpret_cast<const uint32_t*>(As + r * LDS + k0 + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(As + (r + 8) * LDS + k0 + 8);
+    } else {
+      a[0] = pack2(As[k0 * LDS + r], As[(k0 + 1) * LDS + r]);
+      a[1] = pack2(As[k0 * LDS + r + 8], As[(k0 + 1) * LDS + r + 8]);
+      a[2] = pack2(As[(k0 + 8) * LDS + r], As[(k0 + 9) * LDS + r]);
+      a[3] = pack2(As[(k0 + 8) * LDS + r + 8], As[(k0 + 9) * LDS + r + 8]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int n = 8 * nt + (lane >> 2);
+      uint32_t b0, b1;
+      if (TB) {
+        b0 = *reinterpret_cast<const uint32_t*>(Bs + n * LDS + k0);
+        b1 = *reinterpret_cast<const uint32_t*>(Bs + n * LDS + k0 + 8);
+      } else {
+        b0 = pack2(Bs[k0 * LDS + n], Bs[(k0 + 1) * LDS + n]);
+        b1 = pack2(Bs[(k0 + 8) * LDS + n], Bs[(k0 + 9) * LDS + n]);
+      }
+      mma16816(acc[nt], a, b0, b1);
+    }
+  }
+}
+
+__device__ __forceinline__ void zero_acc(float (&acc)[8][4]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+}
+
+// Accumulator fragment -> padded bf16 tile in shared memory (row-major).
+__device__ __forceinline__ void acc_to_smem(const float (&acc)[8][4], bf16* __restrict__ dst, int warp, int lane) {
+  const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    *reinterpret_cast<__nv_bfloat162*>(dst + r * LDS + 8 * nt + cq) = __floats2bfloat162_rn(acc[nt][0], acc[nt][1]);
+    *reinterpret_cast<__nv_bfloat162*>(dst + (r + 8) * LDS + 8 * nt + cq) = __floats2bfloat162_rn(acc[nt][2], acc[nt][3]);
+  }
+}
+
+// Accumulator fragment -> dense [64,64] bf16 tile in global memory with row stride `ld` elements.
+__device__ __forceinline__ void acc_to_global(const float (&acc)[8][4], bf16* __restrict__ dst, long long ld, int warp, int lane, float scale = 1.f) {
+  const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    *reinterpret_cast<__nv_bfloat162*>(dst + (long long)r * ld + 8 * nt + cq) = __floats2bfloat162_rn(acc[nt][0] * scale, acc[nt][1] * scale);
+    *reinterpret_cast<__nv_bfloat162*>(dst + (long long)(r + 8) * ld + 8 * nt + cq) = __floats2bfloat162_rn(acc[nt][2] * scale, acc[nt][3] * scale);
+  }
+}
+
+// cp.async of a dense [64,64] bf16 tile (row stride `ld` elements, 16-byte aligned rows) into a padded shared tile.
+__device__ __forceinline__ void load_tile_async(bf16* __restrict__ dst, const bf16* __restrict__ src, long long ld, int tid) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int chunk = tid + 128 * i;                 // 512 chunks of 16 bytes
+    const int row = chunk >> 3, col = (chunk & 7) * 8;
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst + row * LDS + col));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + (long long)row * ld + col) : "memory");
+  }
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+
+}  // namespace q38

@@ -361,7 +361,9 @@ def qsa_attention(attn, x, cos, sin, indexer, budget, dense, want_kl):
     """
     fast = _hook("qsa_attention", x)
     if fast is not None:
-        return fast(attn, x, cos, sin, indexer, budget, dense, want_kl)
+        out = fast(attn, x, cos, sin, indexer, budget, dense, want_kl)
+        if out is not None:
+            return out
     B, S, _ = x.shape
     hd = attn.head_dim
     qg = _linear(x, attn.q_proj.weight).view(B, S, -1, 2 * hd)

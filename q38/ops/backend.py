@@ -222,6 +222,29 @@ class _DeltaRule(torch.autograd.Function):
         return dq, dk, dv, dg, dbeta
 
 
+class _IndexerKL(torch.autograd.Function):
+    """Indexer distillation: KL between the dense main attention's block mass (target, no gradient) and the indexer's
+    block distribution.  Returns (kl, lp_blk); only the indexer operands receive gradients."""
+
+    @staticmethod
+    def forward(ctx, qi, ki, wi, q_main, k_main, main_scale, idx_scale):
+        ops = load()
+        stats = ops.qsa_main_block_stats(q_main, k_main, main_scale)
+        blse = ops.qsa_indexer_fwd(qi, ki, wi, idx_scale)
+        P, lp_blk, kl_tok, dblse = ops.qsa_kl_combine(stats, blse, q_main.shape[1])
+        ctx.save_for_backward(qi, ki, wi, blse, dblse)
+        ctx.idx_scale = idx_scale
+        ctx.mark_non_differentiable(lp_blk)
+        return kl_tok.mean(), lp_blk
+
+    @staticmethod
+    def backward(ctx, dkl, _lp):
+        qi, ki, wi, blse, dblse = ctx.saved_tensors
+        tokens = qi.shape[0] * qi.shape[2]
+        dqi, dki, dwi = load().qsa_indexer_bwd(qi, ki, wi, blse, dblse, 1.0 / tokens, ctx.idx_scale)
+        return dqi * dkl.to(dqi.dtype), dki * dkl.to(dki.dtype), dwi * dkl, None, None, None, None
+
+
 class _Route(torch.autograd.Function):
     """bf16 router logits -> (top-k weights, indices, per-expert probability sums, per-expert assignment counts)."""
 
@@ -388,6 +411,48 @@ class Backend:
         o = self.delta_rule(q.reshape(B, S, -1, 64), k.reshape(B, S, -1, 64), v.reshape(B, S, -1, 64), g, beta)
         o = self.gated_rmsnorm(o.reshape(-1, 64), z.reshape(-1, 64), m.norm.weight, m.norm.variance_epsilon)
         return self.linear(o.reshape(B, S, -1), m.out_proj.weight)
+
+    def indexer_block_logprobs(self, indexer, x, cos, sin, q_main=None, k_main=None, main_scale=None):
+        """Indexer projections + score kernels.  With main q/k: (kl, lp_blk) for training; without: (None, lp_blk)."""
+        from ..models import modeling
+        B, S, _ = x.shape
+        NI, D = indexer.n_ih, indexer.d_ih
+        qi = modeling.apply_rope(self.linear(x, indexer.wq.weight).view(B, S, NI, D).transpose(1, 2), cos, sin).contiguous()
+        ki = modeling.apply_rope(self.linear(x, indexer.wk.weight).view(B, S, 1, D).transpose(1, 2), cos, sin)[:, 0].contiguous()
+        wi = (self.linear(x, indexer.ww.weight).float() * NI ** -0.5).contiguous()
+        if q_main is not None:
+            return _IndexerKL.apply(qi, ki, wi, q_main, k_main, main_scale, D ** -0.5)
+        ops = load()
+        blse = ops.qsa_indexer_fwd(qi.detach(), ki.detach(), wi.detach(), D ** -0.5)
+        return None, ops.qsa_kl_combine(None, blse, 1)[1]
+
+    def qsa_attention(self, attn, x, cos, sin, indexer, budget, dense, want_kl):
+        from ..models import modeling
+        F = torch.nn.functional
+        B, S, _ = x.shape
+        hd = attn.head_dim
+        if x.dtype != torch.bfloat16 or hd != 64 or S % 64 or S > 8192 or (indexer is not None and (indexer.d_ih != 64 or indexer.n_ih > 4)):
+            return None
+        qg = self.linear(x, attn.q_proj.weight).view(B, S, -1, 2 * hd)
+        q, gate = qg[..., :hd], qg[..., hd:].reshape(B, S, -1)
+        q = modeling.apply_rope(attn.q_norm(q).transpose(1, 2), cos, sin).contiguous()
+        k = modeling.apply_rope(attn.k_norm(self.linear(x, attn.k_proj.weight).view(B, S, -1, hd)).transpose(1, 2), cos, sin).contiguous()
+        v = self.linear(x, attn.v_proj.weight).view(B, S, -1, hd).transpose(1, 2)
+        kl = lp_blk = None
+        if indexer is not None and (want_kl or not dense):
+            if want_kl:
+                kl, lp_blk = self.indexer_block_logprobs(indexer, x.detach(), cos, sin, q.detach(), k.detach(), attn.scaling)
+            else:
+                with torch.no_grad():
+                    _, lp_blk = self.indexer_block_logprobs(indexer, x.detach(), cos, sin)
+        if dense or indexer is None:
+            o = F.scaled_dot_product_attention(q, k, v, scale=attn.scaling, is_causal=True, enable_gqa=True)
+        else:
+            count, index = load().qsa_select(lp_blk, budget)
+            mask = modeling.block_sparse_mask(count, index, S)
+            o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask[:, None], scale=attn.scaling, enable_gqa=True)
+        o = o.transpose(1, 2).reshape(B, S, -1) * torch.sigmoid(gate)
+        return self.linear(o, attn.o_proj.weight), kl
 
     def moe_block(self, block, x):
         experts = block.experts

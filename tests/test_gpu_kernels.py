@@ -307,3 +307,46 @@ def test_conv_silu(ops):
     yb = modeling.causal_conv_silu(xb, wb)
     yb.backward(dy.float())
     assert rel_err(ya, yb) < 2e-2 and rel_err(xa.grad, xb.grad) < 2e-2 and rel_err(wa.grad, wb.grad) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,nq,nkv", [(1, 256, 4, 2), (2, 512, 6, 2)])
+def test_indexer_kl_and_selection_match_specification(ops, B, S, nq, nkv):
+    from q38.models import modeling
+    backend = modeling.get_backend()
+    torch.manual_seed(14)
+    h = 128
+    indexer = modeling.Indexer(h, 4, 64).cuda()
+    x = torch.randn(B, S, h, device="cuda").to(torch.bfloat16)
+    q = torch.randn(B, nq, S, 64, device="cuda").to(torch.bfloat16)
+    k = torch.randn(B, nkv, S, 64, device="cuda").to(torch.bfloat16)
+    cos, sin = modeling.rope_tables(torch.arange(S, device="cuda")[None], 16, 1e7, torch.float32)
+    # specification (fp32 score pipeline of the model file)
+    for p in indexer.parameters():
+        p.grad = None
+    modeling.set_backend(None)
+    try:
+        score = indexer(x, cos, sin)
+        pos = torch.arange(S, device="cuda")
+        lp = score.masked_fill(pos[None, :] > pos[:, None], -1e9).log_softmax(-1)
+        lp_ref = lp.view(B, S, S // 64, 64).logsumexp(-1)
+        P = modeling.block_mass(q, k, 0.125)
+        kl_ref = torch.where(P > 0, P * (P.clamp(min=1e-12).log() - lp_ref), torch.zeros_like(P)).sum(-1).mean()
+        (kl_ref * 7.0).backward()
+        ref_grads = {n: p.grad.clone() for n, p in indexer.named_parameters()}
+    finally:
+        modeling.set_backend(backend)
+    for p in indexer.parameters():
+        p.grad = None
+    kl, lp_blk = backend.indexer_block_logprobs(indexer, x, cos, sin, q, k, 0.125)
+    (kl * 7.0).backward()
+    ops.check_errors()
+    assert abs(kl.item() - kl_ref.item()) < 2e-2 * abs(kl_ref.item()) + 1e-4, (kl.item(), kl_ref.item())
+    causal = (torch.arange(S // 64, device="cuda")[None, :] <= (pos // 64)[:, None])
+    assert (lp_blk - lp_ref)[:, causal].abs().max() < 5e-2
+    for name, g in indexer.named_parameters():
+        assert rel_err(g.grad, ref_grads[name]) < 8e-2, name
+    count, index = ops.load().qsa_select(lp_blk, 3)
+    c_ref, i_ref = modeling.select_blocks(lp_blk, 3)
+    assert torch.equal(count, c_ref)
+    slot = torch.arange(index.shape[-1], device="cuda")[None, None, :] < count[..., None]
+    assert torch.equal(torch.where(slot, index, -1).sort(-1).values, torch.where(slot, i_ref, -1).sort(-1).values)
