@@ -20,6 +20,8 @@ TORCH_LIBRARY(q38, m) {
   m.def("qsa_kl_combine(Tensor? stats, Tensor blse, int nq) -> Tensor[]");
   m.def("qsa_select(Tensor lp_blk, int budget) -> Tensor[]");
   m.def("qsa_indexer_bwd(Tensor qi, Tensor ki, Tensor wi, Tensor blse, Tensor dblse, float gscale, float scale) -> Tensor[]");
+  m.def("qsa_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor? count, Tensor? index, float scale) -> Tensor[]");
+  m.def("qsa_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor dout, Tensor lse, Tensor sel, float scale) -> Tensor[]");
   m.def("conv_silu_fwd(Tensor x, Tensor w) -> Tensor");
   m.def("conv_silu_bwd(Tensor x, Tensor w, Tensor dy) -> Tensor[]");
   m.def("gdn_prep_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta) -> Tensor[]");
@@ -62,6 +64,10 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
   m.impl("qsa_kl_combine", [](c10::optional<at::Tensor> stats, const at::Tensor& blse, int64_t nq) { return q38::qsa_kl_combine(stats, blse, nq); });
   m.impl("qsa_select", &q38::qsa_select);
   m.impl("qsa_indexer_bwd", &q38::qsa_indexer_bwd);
+  m.impl("qsa_attn_fwd", [](const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, c10::optional<at::Tensor> c, c10::optional<at::Tensor> i, double s) {
+    return q38::qsa_attn_fwd(q, k, v, c, i, s);
+  });
+  m.impl("qsa_attn_bwd", &q38::qsa_attn_bwd);
   m.impl("conv_silu_fwd", &q38::conv_silu_fwd);
   m.impl("conv_silu_bwd", &q38::conv_silu_bwd);
   m.impl("gdn_prep_fwd", &q38::gdn_prep_fwd);

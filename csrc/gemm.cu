@@ -21,7 +21,9 @@
 
 namespace q38 {
 
-constexpr int BM = 128, BK = 64, UMMA_K = 16, STAGES = 3, GEMM_THREADS = 192;
+constexpr int BM = 128, STAGES = 3, GEMM_THREADS = 192;
+// One pipeline stage holds 128 bytes of K per row: 64 bf16 or 32 fp32 (tf32) elements; one UMMA consumes 32 bytes of K.
+template <int EB> struct Elem { static constexpr int BK = 128 / EB, UMMA_K = 32 / EB, MN_BOX = 128 / EB; };
 
 struct GemmArgs {
   int M, N, K, batch;
@@ -32,15 +34,17 @@ struct GemmArgs {
 };
 
 template <int BN>
-constexpr int gemm_smem_bytes() { return STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 /*alignment slack*/ + 256 /*barriers*/; }
+constexpr int gemm_smem_bytes() { return STAGES * (BM * 128 + BN * 128) + 1024 /*alignment slack*/ + 256 /*barriers*/; }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
+template <int EB, int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
 __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmB, GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int BK = Elem<EB>::BK, UMMA_K = Elem<EB>::UMMA_K, MN_BOX = Elem<EB>::MN_BOX;
+  constexpr int MN_BOX_BYTES = BK * 128;                      // one MN-major TMA box: BK rows of 128 bytes
+  constexpr int A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_ready = empty + STAGES;
@@ -49,7 +53,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb = (p.K + Elem<EB>::BK - 1) / Elem<EB>::BK;
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tmA);
@@ -75,13 +79,13 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
         const int k0 = kb * BK;
         if (A_MN) {
 #pragma unroll
-          for (int i = 0; i < BM / 64; ++i) ptx::tma_load_3d(a_dst + i * 8192, &tmA, &full[s], m0 + 64 * i, k0, bz);
+          for (int i = 0; i < BM / MN_BOX; ++i) ptx::tma_load_3d(a_dst + i * MN_BOX_BYTES, &tmA, &full[s], m0 + MN_BOX * i, k0, bz);
         } else {
           ptx::tma_load_3d(a_dst, &tmA, &full[s], k0, m0, bz);
         }
         if (B_MN) {
 #pragma unroll
-          for (int i = 0; i < BN / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], n0 + 64 * i, k0, bz);
+          for (int i = 0; i < BN / MN_BOX; ++i) ptx::tma_load_3d(b_dst + i * MN_BOX_BYTES, &tmB, &full[s], n0 + MN_BOX * i, k0, bz);
         } else {
           ptx::tma_load_3d(b_dst, &tmB, &full[s], k0, n0, bz);
         }
@@ -89,7 +93,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
     }
   } else if (warp == 1) {
     if (ptx::elect_one()) {
-      constexpr uint32_t idesc = ptx::umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc = EB == 2 ? ptx::umma_idesc_bf16(BM, BN, A_MN, B_MN) : ptx::umma_idesc_tf32(BM, BN, A_MN, B_MN);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % STAGES, round = kb / STAGES;
@@ -98,13 +102,14 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
         const uint32_t a_base = ptx::smem_u32(smem + s * STAGE_BYTES), b_base = a_base + A_BYTES;
 #pragma unroll
         for (int j = 0; j < BK / UMMA_K; ++j) {
-          // K-major: 16 K-elements = 32 bytes inside the 128-byte swizzle row; 8-row groups are 1024 bytes apart.
-          // MN-major: 16 K-rows = 2048 bytes; 64-element MN chunks (one TMA box) are 8192 bytes apart.
-          const uint64_t a_desc = A_MN ? ptx::umma_smem_desc_sw128(a_base + j * 2048, 8192, 1024)
+          // K-major: one UMMA reads 32 bytes of K inside the 128-byte swizzle row; 8-row groups are 1024 bytes apart.
+          // MN-major: one UMMA reads UMMA_K rows of 128 bytes; 128-byte MN chunks (one TMA box each) are MN_BOX_BYTES apart.
+          const uint64_t a_desc = A_MN ? ptx::umma_smem_desc_sw128(a_base + j * UMMA_K * 128, MN_BOX_BYTES, 1024)
                                        : ptx::umma_smem_desc_sw128(a_base + j * 32, 0, 1024);
-          const uint64_t b_desc = B_MN ? ptx::umma_smem_desc_sw128(b_base + j * 2048, 8192, 1024)
+          const uint64_t b_desc = B_MN ? ptx::umma_smem_desc_sw128(b_base + j * UMMA_K * 128, MN_BOX_BYTES, 1024)
                                        : ptx::umma_smem_desc_sw128(b_base + j * 32, 0, 1024);
-          ptx::umma_f16(tmem_base, a_desc, b_desc, idesc, (kb | j) != 0);
+          if (EB == 2) ptx::umma_f16(tmem_base, a_desc, b_desc, idesc, (kb | j) != 0);
+          else ptx::umma_tf32(tmem_base, a_desc, b_desc, idesc, (kb | j) != 0);
         }
         ptx::umma_commit(&empty[s]);          // the stage may be refilled once these MMAs have read it
       }
@@ -186,27 +191,35 @@ static EncodeFn encode_fn() {
   return fn;
 }
 
-// 3-D bf16 tensor map {inner, rows, batch} with a 128-byte-swizzled {64, box_rows, 1} box; out-of-range elements read 0.
+// 3-D tensor map {inner, rows, batch} with a 128-byte-swizzled {128 bytes, box_rows, 1} box; out-of-range elements read 0.
+static CUtensorMap make_tmap(const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
+                             int64_t batch_stride_elems, int box_rows);
+
 CUtensorMap make_tmap_bf16(const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
                            int64_t batch_stride_elems, int box_rows) {
+  return make_tmap(base, 2, inner, rows, batch, row_stride_elems, batch_stride_elems, box_rows);
+}
+
+static CUtensorMap make_tmap(const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
+                             int64_t batch_stride_elems, int box_rows) {
   TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
-  TORCH_CHECK(row_stride_elems % 8 == 0 && (batch <= 1 || batch_stride_elems % 8 == 0), "TMA strides must be multiples of 16 bytes");
+  TORCH_CHECK((row_stride_elems * elem_bytes) % 16 == 0 && (batch <= 1 || (batch_stride_elems * elem_bytes) % 16 == 0), "TMA strides must be multiples of 16 bytes");
   TORCH_CHECK(box_rows >= 1 && box_rows <= 256, "TMA box rows out of range");
   CUtensorMap m;
   cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batch < 1 ? 1 : batch)};
-  cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * 2, (cuuint64_t)(batch <= 1 ? row_stride_elems * rows : batch_stride_elems) * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * elem_bytes, (cuuint64_t)(batch <= 1 ? row_stride_elems * rows : batch_stride_elems) * elem_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows, 1};
   cuuint32_t elem[3] = {1, 1, 1};
-  CUresult r = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+  CUresult r = encode_fn()(&m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
   return m;
 }
 
-template <int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
+template <int EB, int BN, bool A_MN, bool B_MN, typename OutT, bool ACCUM>
 static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& p, cudaStream_t stream) {
-  auto kernel = gemm_bf16_kernel<BN, A_MN, B_MN, OutT, ACCUM>;
+  auto kernel = gemm_bf16_kernel<EB, BN, A_MN, B_MN, OutT, ACCUM>;
   constexpr int smem = gemm_smem_bytes<BN>();
   static bool configured = false;
   if (!configured) {
@@ -219,18 +232,24 @@ static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs&
   count_launch();
 }
 
-template <bool A_MN, bool B_MN>
+template <int EB, bool A_MN, bool B_MN>
 static void dispatch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& p, bool out_fp32, bool accum, int bn,
                      cudaStream_t stream) {
   TORCH_CHECK(!accum || out_fp32, "accumulating epilogue requires an fp32 output");
+  if constexpr (EB == 4) {
+    TORCH_CHECK(out_fp32, "tf32 products write fp32");
+    if (bn == 64) { if (accum) launch<EB, 64, A_MN, B_MN, float, true>(ta, tb, p, stream); else launch<EB, 64, A_MN, B_MN, float, false>(ta, tb, p, stream); }
+    else { if (accum) launch<EB, 128, A_MN, B_MN, float, true>(ta, tb, p, stream); else launch<EB, 128, A_MN, B_MN, float, false>(ta, tb, p, stream); }
+    return;
+  }
   if (bn == 64) {
-    if (!out_fp32) launch<64, A_MN, B_MN, __nv_bfloat16, false>(ta, tb, p, stream);
-    else if (accum) launch<64, A_MN, B_MN, float, true>(ta, tb, p, stream);
-    else launch<64, A_MN, B_MN, float, false>(ta, tb, p, stream);
+    if (!out_fp32) launch<EB, 64, A_MN, B_MN, __nv_bfloat16, false>(ta, tb, p, stream);
+    else if (accum) launch<EB, 64, A_MN, B_MN, float, true>(ta, tb, p, stream);
+    else launch<EB, 64, A_MN, B_MN, float, false>(ta, tb, p, stream);
   } else {
-    if (!out_fp32) launch<128, A_MN, B_MN, __nv_bfloat16, false>(ta, tb, p, stream);
-    else if (accum) launch<128, A_MN, B_MN, float, true>(ta, tb, p, stream);
-    else launch<128, A_MN, B_MN, float, false>(ta, tb, p, stream);
+    if (!out_fp32) launch<EB, 128, A_MN, B_MN, __nv_bfloat16, false>(ta, tb, p, stream);
+    else if (accum) launch<EB, 128, A_MN, B_MN, float, true>(ta, tb, p, stream);
+    else launch<EB, 128, A_MN, B_MN, float, false>(ta, tb, p, stream);
   }
 }
 
@@ -238,7 +257,8 @@ static void dispatch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArg
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
                bool accumulate, at::Tensor& err) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda(), "gemm_bf16: CUDA tensors required");
-  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm_bf16: bf16 operands required");
+  const bool tf32 = a.scalar_type() == at::kFloat;
+  TORCH_CHECK((a.scalar_type() == at::kBFloat16 || tf32) && b.scalar_type() == a.scalar_type(), "gemm_bf16: operands must both be bf16 or both fp32 (tf32 math)");
   TORCH_CHECK(a.dim() == 3 && b.dim() == 3 && c.dim() == 3, "gemm_bf16: [batch, rows, cols] tensors required");
   TORCH_CHECK(a.stride(2) == 1 && b.stride(2) == 1 && c.stride(2) == 1, "gemm_bf16: innermost dimension must be contiguous");
   const c10::cuda::CUDAGuard guard(a.device());
@@ -249,16 +269,21 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_m
   const bool out_fp32 = c.scalar_type() == at::kFloat;
   TORCH_CHECK(out_fp32 || c.scalar_type() == at::kBFloat16, "gemm_bf16: output must be bf16 or fp32");
   const int bn = (N <= 64) ? 64 : 128;
-  CUtensorMap ta = make_tmap_bf16(a.data_ptr(), a.size(2), a.size(1), batch, a.stride(1), a.stride(0), a_mn_major ? 64 : BM);
-  CUtensorMap tb = make_tmap_bf16(b.data_ptr(), b.size(2), b.size(1), batch, b.stride(1), b.stride(0), b_mn_major ? 64 : bn);
+  const int eb = tf32 ? 4 : 2, bk = 128 / eb;
+  TORCH_CHECK(!tf32 || out_fp32, "gemm_bf16: tf32 products write fp32");
+  CUtensorMap ta = make_tmap(a.data_ptr(), eb, a.size(2), a.size(1), batch, a.stride(1), a.stride(0), a_mn_major ? bk : BM);
+  CUtensorMap tb = make_tmap(b.data_ptr(), eb, b.size(2), b.size(1), batch, b.stride(1), b.stride(0), b_mn_major ? bk : bn);
   GemmArgs p{M, N, K, batch, c.data_ptr(), c.stride(1), c.stride(0), (float)alpha, err.data_ptr<int>()};
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-  if (a_mn_major) {
-    if (b_mn_major) dispatch<true, true>(ta, tb, p, out_fp32, accumulate, bn, stream);
-    else dispatch<true, false>(ta, tb, p, out_fp32, accumulate, bn, stream);
+  if (tf32) {
+    TORCH_CHECK(!a_mn_major && !b_mn_major, "gemm_bf16: the tf32 path takes K-major operands only");
+    dispatch<4, false, false>(ta, tb, p, true, accumulate, bn, stream);
+  } else if (a_mn_major) {
+    if (b_mn_major) dispatch<2, true, true>(ta, tb, p, out_fp32, accumulate, bn, stream);
+    else dispatch<2, true, false>(ta, tb, p, out_fp32, accumulate, bn, stream);
   } else {
-    if (b_mn_major) dispatch<false, true>(ta, tb, p, out_fp32, accumulate, bn, stream);
-    else dispatch<false, false>(ta, tb, p, out_fp32, accumulate, bn, stream);
+    if (b_mn_major) dispatch<2, false, true>(ta, tb, p, out_fp32, accumulate, bn, stream);
+    else dispatch<2, false, false>(ta, tb, p, out_fp32, accumulate, bn, stream);
   }
 }
 

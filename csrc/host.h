@@ -70,6 +70,11 @@ std::vector<at::Tensor> qsa_kl_combine(const c10::optional<at::Tensor>& stats, c
 std::vector<at::Tensor> qsa_select(const at::Tensor& lp_blk, int64_t budget);
 std::vector<at::Tensor> qsa_indexer_bwd(const at::Tensor& qi, const at::Tensor& ki, const at::Tensor& wi, const at::Tensor& blse, const at::Tensor& dblse,
                                         double gscale, double scale);
+// qsa_attn.cu
+std::vector<at::Tensor> qsa_attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const c10::optional<at::Tensor>& count,
+                                     const c10::optional<at::Tensor>& index, double scale);
+std::vector<at::Tensor> qsa_attn_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o, const at::Tensor& dout,
+                                     const at::Tensor& lse, const at::Tensor& sel, double scale);
 // conv.cu
 at::Tensor conv_silu_fwd(const at::Tensor& x, const at::Tensor& w);
 std::vector<at::Tensor> conv_silu_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy);

@@ -96,4 +96,25 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 
+// Fragment of a dense [64,64] bf16 tile in global memory.
+__device__ __forceinline__ void frag_from_global(const bf16* __restrict__ src, float (&dst)[8][4], int warp, int lane) {
+  const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(src + r * 64 + 8 * nt + cq);
+    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(src + (r + 8) * 64 + 8 * nt + cq);
+    dst[nt][0] = __low2float(a); dst[nt][1] = __high2float(a); dst[nt][2] = __low2float(b2); dst[nt][3] = __high2float(b2);
+  }
+}
+__device__ __forceinline__ void frag_from_smem(const bf16* __restrict__ src, float (&dst)[8][4], int warp, int lane) {
+  const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(src + r * LDS + 8 * nt + cq);
+    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(src + (r + 8) * LDS + 8 * nt + cq);
+    dst[nt][0] = __low2float(a); dst[nt][1] = __high2float(a); dst[nt][2] = __low2float(b2); dst[nt][3] = __high2float(b2);
+  }
+}
+
+
 }  // namespace q38

@@ -88,6 +88,26 @@ class _GatedRMSNorm(torch.autograd.Function):
         return dx, dgate, dw.to(weight.dtype), None
 
 
+def _mm32(a, b, layout):
+    """Products of fp32 operands for the mHC low-rank path on the tensor cores.
+
+    'nt' a[M,K] b[N,K]^T and 'nn' a[M,K] b[K,N] run as tf32 (fp32 data read by TMA, 10-bit mantissa math, fp32 accumulate);
+    'nn' transposes the small operand so both are K-major.  'tn' a[K,M]^T b[K,N] (a weight gradient that reduces over the
+    tokens) runs on bf16 copies with MN-major operands and fp32 accumulation."""
+    a, b = a.float().contiguous(), b.float().contiguous()
+    if os.environ.get("Q38_MHC_FP32_GEMM"):
+        return a @ b.t() if layout == "nt" else (a @ b if layout == "nn" else a.t() @ b)
+    if layout == "tn":
+        if a.shape[1] % 8 or b.shape[1] % 8:
+            return a.t() @ b
+        return gemm(a.to(torch.bfloat16), b.to(torch.bfloat16), a_mn_major=True, b_mn_major=True, out_dtype=torch.float32)
+    if layout == "nn":
+        b = b.t().contiguous()
+    if a.shape[1] % 4 or a.data_ptr() % 16 or b.data_ptr() % 16:
+        return a @ b.t()
+    return gemm(a, b, out_dtype=torch.float32)
+
+
 class _MhcLink:
     """Carries the gradient of a sub-layer's output stream from `_MhcPost.backward` to `_MhcPreNorm.backward`, which
     writes the complete gradient of the input stream in one pass (the residual-mix term is folded in there)."""
@@ -106,7 +126,7 @@ class _MhcPreNorm(torch.autograd.Function):
         B_, S, n, h = X.shape
         Xc = X.contiguous()
         Xf = Xc.view(B_ * S, n * h)
-        Lraw = Xf @ A_w.float().t()                          # low-rank projection, fp32
+        Lraw = _mm32(Xf, A_w, 'nt')                           # low-rank projection: fp32 data, tf32 tensor-core math
         xout, coef, z, inv, rstd = ops.mhc_coef_fwd(Xc.view(B_ * S, n, h), Lraw, B_w.float().contiguous(), b_pre.float().contiguous(),
                                                     b_post.float().contiguous(), b_res.float().contiguous(), alphas.float().contiguous(),
                                                     norm_w.float().contiguous(), iters, eps, out_dtype == torch.bfloat16)
@@ -129,8 +149,8 @@ class _MhcPreNorm(torch.autograd.Function):
             b_post.float().contiguous(), b_res.float().contiguous(), alphas.float().contiguous(), norm_w.float().contiguous(),
             coef, z, inv, rstd, dcoef, ctx.iters)
         Xf = Xc.view(T, n * h)
-        dA = dLraw.t() @ Xf
-        dX = dLraw @ A_w.float()                              # G, completed in place below
+        dA = _mm32(dLraw, Xf, 'tn')
+        dX = _mm32(dLraw, A_w, 'nn')                          # G, completed in place below
         dXo = ctx.link.dXo if ctx.link.dXo is not None else torch.zeros_like(Xf)
         ctx.link.dXo = None
         ops.mhc_pre_bwd_c(dX.view(T, n, h), dXo.contiguous().view(T, n, h), Xc.view(T, n, h), dxin, coef, c1)
@@ -243,6 +263,25 @@ class _IndexerKL(torch.autograd.Function):
         tokens = qi.shape[0] * qi.shape[2]
         dqi, dki, dwi = load().qsa_indexer_bwd(qi, ki, wi, blse, dblse, 1.0 / tokens, ctx.idx_scale)
         return dqi * dkl.to(dqi.dtype), dki * dkl.to(dki.dtype), dwi * dkl, None, None, None, None
+
+
+class _BlockAttention(torch.autograd.Function):
+    """GQA attention over the selected 64-token key blocks (or all causal blocks when `count` is None).
+    q [B,nq,S,64], k/v [B,nkv,S,64] -> o [B,S,nq,64]."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, count, index, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse, sel = load().qsa_attn_fwd(q, k, v, count, index, scale)
+        ctx.save_for_backward(q, k, v, o, lse, sel)
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, sel = ctx.saved_tensors
+        dq, dk, dv = load().qsa_attn_bwd(q, k, v, o, do.to(torch.bfloat16).contiguous(), lse, sel, ctx.scale)
+        return dq, dk, dv, None, None, None
 
 
 class _Route(torch.autograd.Function):
@@ -446,12 +485,11 @@ class Backend:
                 with torch.no_grad():
                     _, lp_blk = self.indexer_block_logprobs(indexer, x.detach(), cos, sin)
         if dense or indexer is None:
-            o = F.scaled_dot_product_attention(q, k, v, scale=attn.scaling, is_causal=True, enable_gqa=True)
+            o = _BlockAttention.apply(q, k, v, None, None, attn.scaling)
         else:
             count, index = load().qsa_select(lp_blk, budget)
-            mask = modeling.block_sparse_mask(count, index, S)
-            o = F.scaled_dot_product_attention(q, k, v, attn_mask=mask[:, None], scale=attn.scaling, enable_gqa=True)
-        o = o.transpose(1, 2).reshape(B, S, -1) * torch.sigmoid(gate)
+            o = _BlockAttention.apply(q, k, v, count, index, attn.scaling)
+        o = o.reshape(B, S, -1) * torch.sigmoid(gate)
         return self.linear(o, attn.o_proj.weight), kl
 
     def moe_block(self, block, x):

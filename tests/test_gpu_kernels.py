@@ -180,7 +180,7 @@ def test_mhc_sublayer_matches_specification(ops, h, iters, dtype):
 
     xa, oa, ga, pa = run(True)
     xb, ob, gb, pb = run(False)
-    tol = 2e-2 if dtype == torch.bfloat16 else 2e-4
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-3          # the low-rank projection runs in tf32 (10-bit mantissa)
     assert rel_err(xa, xb) < tol and rel_err(oa, ob) < tol
     assert rel_err(ga, gb) < tol
     for name in pb:
@@ -350,3 +350,13 @@ def test_indexer_kl_and_selection_match_specification(ops, B, S, nq, nkv):
     assert torch.equal(count, c_ref)
     slot = torch.arange(index.shape[-1], device="cuda")[None, None, :] < count[..., None]
     assert torch.equal(torch.where(slot, index, -1).sort(-1).values, torch.where(slot, i_ref, -1).sort(-1).values)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 72, 2304), (256, 2304, 72), (72, 512, 4096)])
+def test_gemm_tf32(ops, M, N, K):
+    """fp32 operands consumed as tf32 by the tensor cores (K-major operands)."""
+    torch.manual_seed(15)
+    a, b = torch.randn(M, K, device="cuda"), torch.randn(N, K, device="cuda")
+    got = ops.gemm(a, b, out_dtype=torch.float32)
+    ops.check_errors()
+    assert rel_err(got, a @ b.t()) < 3e-3            # 10-bit mantissa operands, fp32 accumulation
