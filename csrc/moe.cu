@@ -17,6 +17,7 @@
 
 #include "ptx.cuh"
 #include "host.h"
+#include "q38_noalloc.h"
 
 namespace q38 {
 
@@ -679,3 +680,45 @@ at::Tensor moe_unpermute_sum(const at::Tensor& dx_sorted, const at::Tensor& inv_
 }
 
 }  // namespace q38
+
+// =====================================================================================================================
+// Allocation-free entry point (see q38_noalloc.h): same kernels as moe_sort, scratch in a static device array.
+// =====================================================================================================================
+static __device__ __align__(256) int g_sort_static_scratch[Q38_SORT_STATIC_MAX_BLOCKS * 64];
+
+namespace {
+constexpr int kMaxDevices = 64;
+int* g_sort_static_ptr[kMaxDevices] = {nullptr};
+
+// The array's name is only a host-side handle; kernels need its device address, which differs per GPU.
+int* sort_static_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (g_sort_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_sort_static_scratch) != cudaSuccess) return nullptr;
+    g_sort_static_ptr[dev] = static_cast<int*>(ptr);
+  }
+  return g_sort_static_ptr[dev];
+}
+}  // namespace
+
+extern "C" int q38_moe_sort_static(const int* expert_of_pair, int P, int experts, int* perm, int* inv_perm, int* offsets, int* sched,
+                                   int max_tiles, cudaStream_t stream) {
+  using namespace q38;
+  if (!expert_of_pair || !perm || !inv_perm || !offsets || !sched || P <= 0 || experts <= 0) return Q38_NOALLOC_BAD_ARGUMENT;
+  if (experts > 64 || P > Q38_SORT_STATIC_MAX_PAIRS) return Q38_NOALLOC_TOO_LARGE;
+  if (max_tiles < (P + G_BM - 1) / G_BM + experts) return Q38_NOALLOC_BAD_ARGUMENT;
+  const int nblocks = (P + SORT_CHUNK - 1) / SORT_CHUNK;
+  if (nblocks > Q38_SORT_STATIC_MAX_BLOCKS) return Q38_NOALLOC_TOO_LARGE;
+  int* scratch = sort_static_scratch_for_current_device();
+  if (scratch == nullptr) return Q38_NOALLOC_CUDA_ERROR;
+  // Every word of the scratch that the scan and scatter kernels read is written by the histogram kernel first.
+  moe_hist_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(expert_of_pair, P, experts, scratch);
+  moe_scan_kernel<<<1, 64, 0, stream>>>(scratch, nblocks, experts, offsets, sched, max_tiles, G_BM);
+  moe_scatter_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(expert_of_pair, P, experts, scratch, perm, inv_perm);
+  if (cudaGetLastError() != cudaSuccess) return Q38_NOALLOC_CUDA_ERROR;
+  count_launch(3);
+  return Q38_NOALLOC_OK;
+}
+
