@@ -122,7 +122,7 @@ def main():
     def timed(batches_pool, read_back):
         barrier()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0 = ops.launch_count()
+        launches0 = ops.launch_count() + trainer.replayed_launches
         start.record()
         last = run(a.steps, batches_pool, read_back)
         stop.record()
@@ -130,7 +130,7 @@ def main():
         ms = torch.tensor(start.elapsed_time(stop), device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return ms.item(), ops.launch_count() - launches0, last
+        return ms.item(), ops.launch_count() + trainer.replayed_launches - launches0, last
 
     with ClockSampler(local_rank) as clocks:
         wall0 = time.time()

@@ -421,8 +421,19 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
           ptx::tmem_ld_32x32b_x16(lane_addr + c0, r);
           ptx::tmem_ld_wait();
           if (row < p.M) {
+            if (n0 + c0 + 16 <= p.N && p.ld0 % 4 == 0) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) if (n0 + c0 + e < p.N) c_row[n0 + c0 + e] += __uint_as_float(r[e]);
+              for (int v = 0; v < 4; ++v) {
+                float4* dst = reinterpret_cast<float4*>(c_row + n0 + c0 + 4 * v);
+                float4 cur = *dst;
+                cur.x += __uint_as_float(r[4 * v]); cur.y += __uint_as_float(r[4 * v + 1]);
+                cur.z += __uint_as_float(r[4 * v + 2]); cur.w += __uint_as_float(r[4 * v + 3]);
+                *dst = cur;
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) if (n0 + c0 + e < p.N) c_row[n0 + c0 + e] += __uint_as_float(r[e]);
+            }
           }
         }
       } else {
@@ -466,15 +477,36 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
               } else {   // EPI_DSWIGLU: accumulator = d(hmid) for columns n0+c0.. of f = p.N
                 const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(p.out1) + row * p.ld1;
                 __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(p.out0) + row * p.ld0;
+                const int c = n0 + c0;
+                if (c + 16 <= p.N && p.N % 8 == 0) {
+                  // 16 gate and 16 up values as four 16-byte loads
+                  uint4 graw[2], uraw[2];
+                  graw[0] = reinterpret_cast<const uint4*>(gu + c)[0]; graw[1] = reinterpret_cast<const uint4*>(gu + c)[1];
+                  uraw[0] = reinterpret_cast<const uint4*>(gu + p.N + c)[0]; uraw[1] = reinterpret_cast<const uint4*>(gu + p.N + c)[1];
+                  const __nv_bfloat16* gp = reinterpret_cast<const __nv_bfloat16*>(graw);
+                  const __nv_bfloat16* up = reinterpret_cast<const __nv_bfloat16*>(uraw);
+                  float dg[16], du_[16];
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                  const int c = n0 + c0 + e;
-                  if (c < p.N) {
+                  for (int e = 0; e < 16; ++e) {
                     const float dh = bf16_round(__uint_as_float(r[e]));
-                    const float g = __bfloat162float(gu[c]), uu = __bfloat162float(gu[p.N + c]);
+                    const float g = __bfloat162float(gp[e]), uu = __bfloat162float(up[e]);
                     const float sg = sigmoidf_(g);
-                    dgu[c] = __float2bfloat16_rn(dh * uu * sg * (1.f + g * (1.f - sg)));
-                    dgu[p.N + c] = __float2bfloat16_rn(dh * g * sg);
+                    dg[e] = dh * uu * sg * (1.f + g * (1.f - sg));
+                    du_[e] = dh * g * sg;
+                  }
+                  store16_bf16(dgu + c, dg);
+                  store16_bf16(dgu + p.N + c, du_);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 16; ++e) {
+                    const int cc = c + e;
+                    if (cc < p.N) {
+                      const float dh = bf16_round(__uint_as_float(r[e]));
+                      const float g = __bfloat162float(gu[cc]), uu = __bfloat162float(gu[p.N + cc]);
+                      const float sg = sigmoidf_(g);
+                      dgu[cc] = __float2bfloat16_rn(dh * uu * sg * (1.f + g * (1.f - sg)));
+                      dgu[p.N + cc] = __float2bfloat16_rn(dh * g * sg);
+                    }
                   }
                 }
               }

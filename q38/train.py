@@ -51,7 +51,7 @@ TRAIN_DEFAULTS = dict(
     eval_sampling="random", eval_offset=0, final_eval_tokens=0, final_eval_offset=0, require_ready_pool=0,
     auto_micro_bs=0, probe_mem_frac=0.92, mtp_coef=0.3, kl_coef=0.05, muon=1, dense_warmup=1, grad_ckpt=0)
 # Options of this framework that the reference trainer does not have (never part of the resume contract).
-ENGINE_DEFAULTS = dict(grad_sync="auto", fp8_ffn=0, expert_parallel=0, export_hf=1, device="auto")
+ENGINE_DEFAULTS = dict(grad_sync="auto", fp8_ffn=0, expert_parallel=0, export_hf=1, device="auto", cuda_graphs=1)
 
 # Everything that shapes the model, the data stream or the schedule must be unchanged on resume.
 RESUME_KEYS = (
@@ -324,6 +324,11 @@ class Trainer:
                                  lr=a.lr, weight_decay=a.wd, muon=bool(a.muon))
         self.opt = self.engine.optimizer
         self.model.train()
+        # One CUDA graph per (micro-batch shape, accumulation count, attention phase) replays forward + backward of a
+        # micro-step without any per-kernel host work; the optimizer step stays eager.
+        self.use_graphs = bool(getattr(a, "cuda_graphs", 1)) and dev.type == "cuda" and not getattr(a, "grad_ckpt", 0)
+        self._graphs = {}
+        self.replayed_launches = 0            # kernels of this library executed through graph replays
 
     def coefficients(self):
         return self.a.aux_coef, self.a.mtp_coef, self.a.kl_coef
@@ -334,17 +339,58 @@ class Trainer:
         return (ce + aux_c * aux + mtp_c * mtp + kl_c * kl) / accum, torch.stack(
             [ce.detach().float(), aux.detach().float(), mtp.detach().float(), kl.detach().float()])
 
+    def _captured_micro_step(self, x, y, accum, dense):
+        """Forward + backward of one micro-step through a CUDA graph (captured on first use of this configuration).
+        Returns the 4 loss terms, or None when capture is unavailable and the caller should run eagerly."""
+        key = (tuple(x.shape), accum, bool(dense))
+        entry = self._graphs.get(key)
+        if entry is None:
+            try:
+                sx, sy = torch.zeros_like(x), torch.zeros_like(y)
+                sx.copy_(x)
+                sy.copy_(y)
+                saved = self.engine.arena.grads.clone()
+                side = torch.cuda.Stream(self.dev)
+                side.wait_stream(torch.cuda.current_stream(self.dev))
+                with torch.cuda.stream(side):
+                    for _ in range(2):                       # warm-up: lazy initialisation must not happen inside the capture
+                        loss, _ = self.micro_loss(sx, sy, accum)
+                        loss.backward()
+                torch.cuda.current_stream(self.dev).wait_stream(side)
+                from . import ops
+                graph = torch.cuda.CUDAGraph()
+                before = ops.launch_count()
+                with torch.cuda.graph(graph):
+                    loss, parts = self.micro_loss(sx, sy, accum)
+                    loss.backward()
+                self.engine.arena.grads.copy_(saved)         # warm-up and capture passes must not leak into the gradients
+                entry = (graph, sx, sy, parts, ops.launch_count() - before)
+            except Exception as exc:                         # pragma: no cover - depends on the driver
+                print(f"[q38.train] CUDA graph capture failed ({type(exc).__name__}: {exc}); running eagerly", flush=True)
+                self.use_graphs = False
+                torch.cuda.synchronize(self.dev)
+                return None
+            self._graphs[key] = entry
+        graph, sx, sy, parts, launches = entry
+        sx.copy_(x, non_blocking=True)
+        sy.copy_(y, non_blocking=True)
+        graph.replay()
+        self.replayed_launches += launches
+        return parts
+
     def train_step(self, batches, lr=None, dense=False):
         accum = len(batches)
         self.model.model.qsa_dense = bool(dense)
         if lr is not None:
             self.engine.set_lr(lr)
         totals = torch.zeros(4, dtype=torch.float32, device=self.dev)
-        staged = [(x.to(self.dev, non_blocking=True), y.to(self.dev, non_blocking=True)) for x, y in batches]
-        for i, (x, y) in enumerate(staged):
+        for i, (x, y) in enumerate(batches):
             self.engine.begin_micro_step(last=i == accum - 1)
-            loss, parts = self.micro_loss(x, y, accum)
-            loss.backward()
+            parts = self._captured_micro_step(x, y, accum, dense) if self.use_graphs else None
+            if parts is None:
+                xd, yd = x.to(self.dev, non_blocking=True), y.to(self.dev, non_blocking=True)
+                loss, parts = self.micro_loss(xd, yd, accum)
+                loss.backward()
             totals += parts / accum
         grad_norm = self.engine.finish_step(self.a.clip)
         return self.engine.average_metrics(torch.cat([totals, grad_norm.detach().reshape(1).float()]))
