@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(128) gdn_prep_fwd_kernel(const bf16* __restric
                                                            const float* __restrict__ g, const bf16* __restrict__ beta, bf16* __restrict__ w_out,
                                                            bf16* __restrict__ u_out, bf16* __restrict__ P_out, bf16* __restrict__ qg_out,
                                                            bf16* __restrict__ kg_out, bf16* __restrict__ Tm_out, float* __restrict__ carry,
-                                                           float* __restrict__ gc_out, int S, int Hk, int Hv) {
+                                                           float* __restrict__ gc_out, int S, int Hk, int Hv, long long qk_ld, long long v_ld) {
   extern __shared__ __align__(16) uint8_t smem_bytes[];
   bf16* sm = reinterpret_cast<bf16*>(smem_bytes);
   PrepSmem s;
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(128) gdn_prep_fwd_kernel(const bf16* __restric
   const int NT = gridDim.x;
   const long long tok0 = (long long)b * S + (long long)c * 64;
   const long long tile_off = ((long long)bh * NT + c) * 4096;
-  prep_load_qk(s, q + (tok0 * Hk + hk) * 64, k + (tok0 * Hk + hk) * 64, (long long)Hk * 64, tid);
+  prep_load_qk(s, q + tok0 * qk_ld + hk * 64, k + tok0 * qk_ld + hk * 64, qk_ld, tid);
   prep_load_gates(s, g + tok0 * Hv + hv, beta + tok0 * Hv + hv, Hv, tid);
   __syncthreads();
   {
@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(128) gdn_prep_fwd_kernel(const bf16* __restric
     }
     store_half_row_global(kg_out + tile_off, tid, row, __expf(gl - gct));
     store_half_row_smem(s.KBG, tid, row, bt * __expf(gct));
-    load_half_row(v + (tok0 * Hv + hv) * 64, (long long)Hv * 64, tid, row);
+    load_half_row(v + tok0 * v_ld + hv * 64, v_ld, tid, row);
     store_half_row_smem(s.VB, tid, row, bt);
     if (tid == 0) carry[(long long)bh * NT + c] = __expf(gl);
     if (tid < 64) gc_out[((long long)bh * NT + c) * 64 + tid] = s.gc[tid];
@@ -445,7 +445,8 @@ __global__ void __launch_bounds__(128) gdn_prep_bwd_kernel(const bf16* __restric
                                                            const bf16* __restrict__ dw, const bf16* __restrict__ du, const bf16* __restrict__ dP,
                                                            const bf16* __restrict__ dqg, const bf16* __restrict__ dkg, const float* __restrict__ dd,
                                                            bf16* __restrict__ dq, bf16* __restrict__ dk, bf16* __restrict__ dv,
-                                                           float* __restrict__ dg, float* __restrict__ dbeta, int S, int Hk, int Hv) {
+                                                           float* __restrict__ dg, float* __restrict__ dbeta, int S, int Hk, int Hv,
+                                                           long long qk_ld, long long v_ld, long long dqk_ld, long long dv_ld) {
   extern __shared__ __align__(16) uint8_t smem_bytes[];
   bf16* sm = reinterpret_cast<bf16*>(smem_bytes);
   PrepSmem s;
@@ -463,7 +464,7 @@ __global__ void __launch_bounds__(128) gdn_prep_bwd_kernel(const bf16* __restric
   const int c = blockIdx.x, NT = gridDim.x, rep = Hv / Hk;
   const int b = blockIdx.y / Hk, hk = blockIdx.y % Hk;
   const long long tok0 = (long long)b * S + (long long)c * 64;
-  prep_load_qk(s, q + (tok0 * Hk + hk) * 64, k + (tok0 * Hk + hk) * 64, (long long)Hk * 64, tid);
+  prep_load_qk(s, q + tok0 * qk_ld + hk * 64, k + tok0 * qk_ld + hk * 64, qk_ld, tid);
   float dQn[8][4], dKn[8][4];
   zero_acc(dQn);
   zero_acc(dKn);
@@ -489,7 +490,7 @@ __global__ void __launch_bounds__(128) gdn_prep_bwd_kernel(const bf16* __restric
         row[2 * i] = __low2float(h); row[2 * i + 1] = __high2float(h);
       }
       store_half_row_smem(s.KBG, tid, row, bt * __expf(gct));
-      load_half_row(v + (tok0 * Hv + hv) * 64, (long long)Hv * 64, tid, row);
+      load_half_row(v + tok0 * v_ld + hv * 64, v_ld, tid, row);
       store_half_row_smem(s.VB, tid, row, bt);
     }
     cp_async_wait<0>();
@@ -516,19 +517,19 @@ __global__ void __launch_bounds__(128) gdn_prep_bwd_kernel(const bf16* __restric
     mma64<true, false>(s.Tm, dUs, acc, warp, lane);
     {
       float tb[8][4];
-      const bf16* vsrc = v + (tok0 * Hv + hv) * 64;
-      bf16* dvdst = dv + (tok0 * Hv + hv) * 64;
+      const bf16* vsrc = v + tok0 * v_ld + hv * 64;
+      bf16* dvdst = dv + tok0 * dv_ld + hv * 64;
       const int r0 = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
         for (int hrow = 0; hrow < 2; ++hrow) {
           const int row = r0 + 8 * hrow;
-          const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(vsrc + (long long)row * Hv * 64 + 8 * nt + cq);
+          const __nv_bfloat162 vv = *reinterpret_cast<const __nv_bfloat162*>(vsrc + (long long)row * v_ld + 8 * nt + cq);
           const float a0 = acc[nt][2 * hrow], a1 = acc[nt][2 * hrow + 1];
           tb[nt][2 * hrow] = a0 * __low2float(vv);
           tb[nt][2 * hrow + 1] = a1 * __high2float(vv);
-          *reinterpret_cast<__nv_bfloat162*>(dvdst + (long long)row * Hv * 64 + 8 * nt + cq) = __floats2bfloat162_rn(a0 * s.beta[row], a1 * s.beta[row]);
+          *reinterpret_cast<__nv_bfloat162*>(dvdst + (long long)row * dv_ld + 8 * nt + cq) = __floats2bfloat162_rn(a0 * s.beta[row], a1 * s.beta[row]);
         }
       }
       frag_row_add(tb, dbt, warp, lane);
@@ -628,11 +629,11 @@ __global__ void __launch_bounds__(128) gdn_prep_bwd_kernel(const bf16* __restric
   }
   // ---- L2-norm backward: qn = 0.125 rq q, kn = rk k ----
   {
-    const bf16* qsrc = q + (tok0 * Hk + hk) * 64;
-    const bf16* ksrc = k + (tok0 * Hk + hk) * 64;
-    bf16* dqdst = dq + (tok0 * Hk + hk) * 64;
-    bf16* dkdst = dk + (tok0 * Hk + hk) * 64;
-    const long long ld = (long long)Hk * 64;
+    const bf16* qsrc = q + tok0 * qk_ld + hk * 64;
+    const bf16* ksrc = k + tok0 * qk_ld + hk * 64;
+    bf16* dqdst = dq + tok0 * dqk_ld + hk * 64;
+    bf16* dkdst = dk + tok0 * dqk_ld + hk * 64;
+    const long long ld = qk_ld, dld = dqk_ld;
     const int r0 = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
 #pragma unroll
     for (int hrow = 0; hrow < 2; ++hrow) {
@@ -652,9 +653,9 @@ __global__ void __launch_bounds__(128) gdn_prep_bwd_kernel(const bf16* __restric
       dotk += __shfl_xor_sync(0xffffffffu, dotk, 1); dotk += __shfl_xor_sync(0xffffffffu, dotk, 2);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
-        *reinterpret_cast<__nv_bfloat162*>(dqdst + row * ld + 8 * nt + cq) =
+        *reinterpret_cast<__nv_bfloat162*>(dqdst + row * dld + 8 * nt + cq) =
             __floats2bfloat162_rn(rq * (0.125f * dQn[nt][2 * hrow] - qh[2 * nt] * dotq), rq * (0.125f * dQn[nt][2 * hrow + 1] - qh[2 * nt + 1] * dotq));
-        *reinterpret_cast<__nv_bfloat162*>(dkdst + row * ld + 8 * nt + cq) =
+        *reinterpret_cast<__nv_bfloat162*>(dkdst + row * dld + 8 * nt + cq) =
             __floats2bfloat162_rn(rk * (dKn[nt][2 * hrow] - kh[2 * nt] * dotk), rk * (dKn[nt][2 * hrow + 1] - kh[2 * nt + 1] * dotk));
       }
     }
@@ -664,8 +665,12 @@ __global__ void __launch_bounds__(128) gdn_prep_bwd_kernel(const bf16* __restric
 // ---- host ----------------------------------------------------------------------------------------------------------------
 // Returns {w, u, P, qg, kg, Tm (bf16 tiles [B*Hv,NT,64,64]), carry [B*Hv,NT] fp32, gc [B*Hv,NT,64] fp32}
 std::vector<at::Tensor> gdn_prep_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g, const at::Tensor& beta) {
-  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && q.size(3) == 64 && v.size(3) == 64,
-              "gdn_prep_fwd: contiguous bf16 [B,S,H,64] tensors required");
+  auto token_major = [](const at::Tensor& t) {
+    return t.dim() == 4 && t.size(3) == 64 && t.stride(3) == 1 && t.stride(2) == 64 && t.stride(0) == t.size(1) * t.stride(1) && t.stride(1) % 8 == 0 &&
+           (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0;
+  };
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && token_major(q) && token_major(k) && token_major(v) && q.stride(1) == k.stride(1),
+              "gdn_prep_fwd: bf16 [B,S,H,64] tensors with contiguous heads and a common token stride required (views of a packed qkv tensor are fine)");
   TORCH_CHECK(g.scalar_type() == at::kFloat && g.is_contiguous() && beta.scalar_type() == at::kBFloat16 && beta.is_contiguous(), "gdn_prep_fwd: g fp32 / beta bf16 [B,S,Hv]");
   const c10::cuda::CUDAGuard guard(q.device());
   const int64_t B = q.size(0), S = q.size(1), Hk = q.size(2), Hv = v.size(2);
@@ -682,13 +687,13 @@ std::vector<at::Tensor> gdn_prep_fwd(const at::Tensor& q, const at::Tensor& k, c
   gdn_prep_fwd_kernel<<<dim3((int)NT, (int)BH), 128, smem, at::cuda::getCurrentCUDAStream()>>>(
       (const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(), (const bf16*)v.data_ptr(), g.data_ptr<float>(), (const bf16*)beta.data_ptr(),
       (bf16*)out[0].data_ptr(), (bf16*)out[1].data_ptr(), (bf16*)out[2].data_ptr(), (bf16*)out[3].data_ptr(), (bf16*)out[4].data_ptr(),
-      (bf16*)out[5].data_ptr(), out[6].data_ptr<float>(), out[7].data_ptr<float>(), (int)S, (int)Hk, (int)Hv);
+      (bf16*)out[5].data_ptr(), out[6].data_ptr<float>(), out[7].data_ptr<float>(), (int)S, (int)Hk, (int)Hv, (long long)q.stride(1), (long long)v.stride(1));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
   return out;
 }
 
-// Returns {dq, dk (bf16 [B,S,Hk,64]), dv (bf16 [B,S,Hv,64]), dg, dbeta (fp32 [B,S,Hv])}
+// Returns {dqkv packed bf16 [B,S,(2 Hk + Hv) 64] holding dq | dk | dv per token, dg, dbeta (fp32 [B,S,Hv])}
 std::vector<at::Tensor> gdn_prep_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& g, const at::Tensor& beta,
                                      const at::Tensor& Tm, const at::Tensor& dw, const at::Tensor& du, const at::Tensor& dP, const at::Tensor& dqg,
                                      const at::Tensor& dkg, const at::Tensor& dd) {
@@ -697,7 +702,11 @@ std::vector<at::Tensor> gdn_prep_bwd(const at::Tensor& q, const at::Tensor& k, c
   check_tiles(Tm, BH, NT, "Tm"); check_tiles(dw, BH, NT, "dw"); check_tiles(du, BH, NT, "du"); check_tiles(dP, BH, NT, "dP");
   check_tiles(dqg, BH, NT, "dqg"); check_tiles(dkg, BH, NT, "dkg");
   TORCH_CHECK(dd.scalar_type() == at::kFloat && dd.is_contiguous() && dd.numel() == BH * NT, "gdn_prep_bwd: dd must be fp32 [BH,NT]");
-  auto dq = at::empty_like(q), dk = at::empty_like(k), dv = at::empty_like(v);
+  const int64_t packed = (2 * Hk + Hv) * 64;
+  auto dqkv = at::empty({B, S, packed}, q.options());
+  bf16* dq_ptr = (bf16*)dqkv.data_ptr();
+  bf16* dk_ptr = dq_ptr + Hk * 64;
+  bf16* dv_ptr = dq_ptr + 2 * Hk * 64;
   auto dg = at::empty({B, S, Hv}, q.options().dtype(at::kFloat)), dbeta = at::empty({B, S, Hv}, q.options().dtype(at::kFloat));
   const int smem = 9 * TILE_ELEMS * 2 + 400 * 4;
   static bool configured = false;
@@ -705,11 +714,11 @@ std::vector<at::Tensor> gdn_prep_bwd(const at::Tensor& q, const at::Tensor& k, c
   gdn_prep_bwd_kernel<<<dim3((int)NT, (int)(B * Hk)), 128, smem, at::cuda::getCurrentCUDAStream()>>>(
       (const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(), (const bf16*)v.data_ptr(), g.data_ptr<float>(), (const bf16*)beta.data_ptr(),
       (const bf16*)Tm.data_ptr(), (const bf16*)dw.data_ptr(), (const bf16*)du.data_ptr(), (const bf16*)dP.data_ptr(), (const bf16*)dqg.data_ptr(),
-      (const bf16*)dkg.data_ptr(), dd.data_ptr<float>(), (bf16*)dq.data_ptr(), (bf16*)dk.data_ptr(), (bf16*)dv.data_ptr(), dg.data_ptr<float>(),
-      dbeta.data_ptr<float>(), (int)S, (int)Hk, (int)Hv);
+      (const bf16*)dkg.data_ptr(), dd.data_ptr<float>(), dq_ptr, dk_ptr, dv_ptr, dg.data_ptr<float>(),
+      dbeta.data_ptr<float>(), (int)S, (int)Hk, (int)Hv, (long long)q.stride(1), (long long)v.stride(1), (long long)packed, (long long)packed);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
-  return {dq, dk, dv, dg, dbeta};
+  return {dqkv, dg, dbeta};
 }
 
 }  // namespace q38

@@ -27,6 +27,7 @@ template <int EB> struct Elem { static constexpr int BK = 128 / EB, UMMA_K = 32 
 
 struct GemmArgs {
   int M, N, K, batch;
+  int splits, kb_per_split;     // split-K: blockIdx.z = batch * splits + split; partial sums are added atomically
   void* C;
   long long ldc, c_batch_stride;
   float alpha;
@@ -52,8 +53,10 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
   constexpr uint32_t TMEM_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z;
-  const int num_kb = (p.K + Elem<EB>::BK - 1) / Elem<EB>::BK;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, bz = blockIdx.z / p.splits, split = blockIdx.z % p.splits;
+  const int total_kb = (p.K + Elem<EB>::BK - 1) / Elem<EB>::BK;
+  const int kb_begin = split * p.kb_per_split;
+  const int num_kb = min(p.kb_per_split, total_kb - kb_begin);
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tmA);
@@ -76,7 +79,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
         uint8_t* a_dst = smem + s * STAGE_BYTES;
         uint8_t* b_dst = a_dst + A_BYTES;
         ptx::mbar_expect_tx(&full[s], STAGE_BYTES);
-        const int k0 = kb * BK;
+        const int k0 = (kb_begin + kb) * BK;
         if (A_MN) {
 #pragma unroll
           for (int i = 0; i < BM / MN_BOX; ++i) ptx::tma_load_3d(a_dst + i * MN_BOX_BYTES, &tmA, &full[s], m0 + MN_BOX * i, k0, bz);
@@ -150,8 +153,13 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
                 float4* dst = reinterpret_cast<float4*>(c_row + col0 + v * 4);
                 float4 o = make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha,
                                        __uint_as_float(r[v * 4 + 2]) * p.alpha, __uint_as_float(r[v * 4 + 3]) * p.alpha);
-                if (ACCUM) { float4 c = *dst; o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w; }
-                *dst = o;
+                if (ACCUM && p.splits > 1) {
+                  float* d = reinterpret_cast<float*>(dst);
+                  atomicAdd(d, o.x); atomicAdd(d + 1, o.y); atomicAdd(d + 2, o.z); atomicAdd(d + 3, o.w);
+                } else {
+                  if (ACCUM) { float4 c = *dst; o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w; }
+                  *dst = o;
+                }
               }
             }
           } else {
@@ -159,6 +167,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_kernel(const __grid_co
             for (int e = 0; e < 32; ++e) {
               if (col0 + e < p.N) {
                 float v = __uint_as_float(r[e]) * p.alpha;
+                if constexpr (ACCUM && sizeof(OutT) == 4) {
+                  if (p.splits > 1) { atomicAdd(reinterpret_cast<float*>(c_row) + col0 + e, v); continue; }
+                }
                 if (ACCUM) v += to_float<OutT>(c_row[col0 + e]);
                 c_row[col0 + e] = from_float<OutT>(v);
               }
@@ -226,7 +237,7 @@ static void launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs&
     C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, p.batch);
+  dim3 grid((p.N + BN - 1) / BN, (p.M + BM - 1) / BM, p.batch * p.splits);
   kernel<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
@@ -255,7 +266,7 @@ static void dispatch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArg
 
 // a: K-major [batch, M, K] or MN-major [batch, K, M]; b likewise with N; c: [batch, M, N] bf16 or fp32 (last dim contiguous).
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
-               bool accumulate, at::Tensor& err) {
+               bool accumulate, at::Tensor& err, int64_t splits) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && c.is_cuda(), "gemm_bf16: CUDA tensors required");
   const bool tf32 = a.scalar_type() == at::kFloat;
   TORCH_CHECK((a.scalar_type() == at::kBFloat16 || tf32) && b.scalar_type() == a.scalar_type(), "gemm_bf16: operands must both be bf16 or both fp32 (tf32 math)");
@@ -273,7 +284,19 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_m
   TORCH_CHECK(!tf32 || out_fp32, "gemm_bf16: tf32 products write fp32");
   CUtensorMap ta = make_tmap(a.data_ptr(), eb, a.size(2), a.size(1), batch, a.stride(1), a.stride(0), a_mn_major ? bk : BM);
   CUtensorMap tb = make_tmap(b.data_ptr(), eb, b.size(2), b.size(1), batch, b.stride(1), b.stride(0), b_mn_major ? bk : bn);
-  GemmArgs p{M, N, K, batch, c.data_ptr(), c.stride(1), c.stride(0), (float)alpha, err.data_ptr<int>()};
+  const int total_kb = (K + bk - 1) / bk;
+  int nsplit = 1;
+  if (accumulate && out_fp32) {
+    if (splits > 0) nsplit = (int)splits;
+    else if (splits == 0) {
+      // automatic: enough CTAs for two per SM, at least eight K blocks per split
+      const int tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM) * batch;
+      nsplit = std::max(1, std::min({(2 * kNumSMs + tiles - 1) / tiles, total_kb / 8, 32}));
+    }
+  }
+  const int kb_per_split = (total_kb + nsplit - 1) / nsplit;
+  nsplit = (total_kb + kb_per_split - 1) / kb_per_split;
+  GemmArgs p{M, N, K, batch, nsplit, kb_per_split, c.data_ptr(), c.stride(1), c.stride(0), (float)alpha, err.data_ptr<int>()};
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   if (tf32) {
     TORCH_CHECK(!a_mn_major && !b_mn_major, "gemm_bf16: the tf32 path takes K-major operands only");

@@ -16,7 +16,7 @@ CUtensorMap make_tmap_bf16(const void* base, int64_t inner, int64_t rows, int64_
 
 // gemm.cu
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
-               bool accumulate, at::Tensor& err);
+               bool accumulate, at::Tensor& err, int64_t splits);
 
 // elementwise.cu
 std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps, bool out_bf16);

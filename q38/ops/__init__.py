@@ -65,10 +65,12 @@ def install(self_check=True):
 
 
 # ---- thin wrappers used outside the model ------------------------------------------------------------------
-def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumulate=False, out_dtype=torch.bfloat16):
+def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumulate=False, out_dtype=torch.bfloat16, splits=-1):
     """``out[b] (+)= alpha * A[b] @ B[b]^T`` on the tcgen05 tensor cores.
 
-    a: ``[batch, M, K]`` (K-major) or ``[batch, K, M]`` (``a_mn_major``); b likewise with N.  2-D inputs are treated as batch 1."""
+    a: ``[batch, M, K]`` (K-major) or ``[batch, K, M]`` (``a_mn_major``); b likewise with N.  2-D inputs are treated as batch 1.
+    ``splits`` (only with ``accumulate`` into fp32): -1 no split-K, 0 automatic, n > 0 that many K slices whose partial
+    sums are added atomically (the summation order, hence the last bits, then vary from run to run)."""
     ops = load()
     squeeze = a.dim() == 2
     if squeeze:
@@ -79,7 +81,7 @@ def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumula
         out3 = torch.empty(a.shape[0], M, N, dtype=out_dtype, device=a.device)
     else:
         out3 = out.unsqueeze(0) if out.dim() == 2 else out
-    ops.gemm_bf16(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device))
+    ops.gemm_bf16(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
     return out3[0] if squeeze else out3
 
 

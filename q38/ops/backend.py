@@ -50,7 +50,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = backend.mm_nn(dy2, _bf16_weight(weight)).view(ctx.in_shape).to(ctx.in_dtype)
         if ctx.needs_input_grad[1]:
-            dw = backend.mm_tn(dy2, x2).to(weight.dtype)
+            dw = backend.weight_grad(dy2, x2, weight)
         return dx, dw, None
 
 
@@ -108,6 +108,17 @@ def _mm32(a, b, layout):
     return gemm(a, b, out_dtype=torch.float32)
 
 
+def _mhc_weight_grad(dL, Xf, A_w):
+    """dA = dL^T Xf (reduction over tokens): bf16 operands, MN-major, split-K accumulated into A's gradient buffer."""
+    grad = A_w.grad
+    if (grad is not None and grad.dtype == torch.float32 and grad.is_contiguous() and dL.shape[1] % 8 == 0 and Xf.shape[1] % 8 == 0
+            and not os.environ.get("Q38_MHC_FP32_GEMM")):
+        gemm(dL.to(torch.bfloat16), Xf.to(torch.bfloat16), out=grad, a_mn_major=True, b_mn_major=True, accumulate=True,
+             splits=-1 if os.environ.get("Q38_DETERMINISTIC") == "1" else 0)
+        return None
+    return _mm32(dL, Xf, 'tn').to(A_w.dtype)
+
+
 class _MhcLink:
     """Carries the gradient of a sub-layer's output stream from `_MhcPost.backward` to `_MhcPreNorm.backward`, which
     writes the complete gradient of the input stream in one pass (the residual-mix term is folded in there)."""
@@ -149,12 +160,12 @@ class _MhcPreNorm(torch.autograd.Function):
             b_post.float().contiguous(), b_res.float().contiguous(), alphas.float().contiguous(), norm_w.float().contiguous(),
             coef, z, inv, rstd, dcoef, ctx.iters)
         Xf = Xc.view(T, n * h)
-        dA = _mm32(dLraw, Xf, 'tn')
+        dA = _mhc_weight_grad(dLraw, Xf, A_w)
         dX = _mm32(dLraw, A_w, 'nn')                          # G, completed in place below
         dXo = ctx.link.dXo if ctx.link.dXo is not None else torch.zeros_like(Xf)
         ctx.link.dXo = None
         ops.mhc_pre_bwd_c(dX.view(T, n, h), dXo.contiguous().view(T, n, h), Xc.view(T, n, h), dxin, coef, c1)
-        return (dX.view(B_, S, n, h), dA.to(A_w.dtype), dBw.to(B_w.dtype), dbias[0:4].to(b_pre.dtype), dbias[4:8].to(b_post.dtype),
+        return (dX.view(B_, S, n, h), dA, dBw.to(B_w.dtype), dbias[0:4].to(b_pre.dtype), dbias[4:8].to(b_post.dtype),
                 dbias[8:24].view(4, 4).to(b_res.dtype), dbias[24:27].to(alphas.dtype), dnw.to(norm_w.dtype), None, None, None, None)
 
 
@@ -219,27 +230,37 @@ class _GdnScan(torch.autograd.Function):
 
 
 class _DeltaRule(torch.autograd.Function):
-    """Chunked gated delta rule: per-chunk preparation kernel (parallel over chunks) + sequential scan kernel."""
+    """Chunked gated delta rule on a packed ``qkv [B,S,(2 Hk + Hv) 64]`` tensor (q | k | v per token, as the causal conv
+    produces it): per-chunk preparation kernel (parallel over chunks) + sequential scan kernel.  The kernels read the
+    three parts through strided views and write their gradients into one packed tensor, so no split/concat copies run."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta):
+    def forward(ctx, qkv, g, beta, Hk, Hv):
         ops = load()
-        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        qkv = qkv.contiguous()
+        B, S, _ = qkv.shape
+        q = qkv[..., :Hk * 64].unflatten(-1, (Hk, 64))
+        k = qkv[..., Hk * 64:2 * Hk * 64].unflatten(-1, (Hk, 64))
+        v = qkv[..., 2 * Hk * 64:].unflatten(-1, (Hv, 64))
         g, beta = g.float().contiguous(), beta.to(torch.bfloat16).contiguous()
-        B, Hv = v.shape[0], v.shape[2]
         w, u, P, qg, kg, Tm, carry, _gc = ops.gdn_prep_fwd(q, k, v, g, beta)
         o, vnew, states = ops.gdn_scan_fwd(w, u, P, qg, kg, carry, B, Hv)
-        ctx.save_for_backward(q, k, v, g, beta, Tm, w, P, qg, kg, carry, vnew, states)
+        ctx.save_for_backward(qkv, g, beta, Tm, w, P, qg, kg, carry, vnew, states)
+        ctx.heads = (Hk, Hv)
         return o
 
     @staticmethod
     def backward(ctx, do):
         ops = load()
-        q, k, v, g, beta, Tm, w, P, qg, kg, carry, vnew, states = ctx.saved_tensors
-        B, Hv = v.shape[0], v.shape[2]
+        qkv, g, beta, Tm, w, P, qg, kg, carry, vnew, states = ctx.saved_tensors
+        Hk, Hv = ctx.heads
+        B = qkv.shape[0]
+        q = qkv[..., :Hk * 64].unflatten(-1, (Hk, 64))
+        k = qkv[..., Hk * 64:2 * Hk * 64].unflatten(-1, (Hk, 64))
+        v = qkv[..., 2 * Hk * 64:].unflatten(-1, (Hv, 64))
         dw, du, dP, dqg, dkg, dd = ops.gdn_scan_bwd(w, P, qg, kg, carry, vnew, states, do.to(torch.bfloat16).contiguous(), B, Hv)
-        dq, dk, dv, dg, dbeta = ops.gdn_prep_bwd(q, k, v, g, beta, Tm, dw, du, dP, dqg, dkg, dd)
-        return dq, dk, dv, dg, dbeta
+        dqkv, dg, dbeta = ops.gdn_prep_bwd(q, k, v, g, beta, Tm, dw, du, dP, dqg, dkg, dd)
+        return dqkv, dg, dbeta, None, None
 
 
 class _IndexerKL(torch.autograd.Function):
@@ -358,6 +379,8 @@ class Backend:
         self.layouts = dict(nt=True, nn=True, tn=True)       # which GEMM operand layouts passed the self-check
         # True: chunk operands come from the PyTorch specification and only the scan runs in the CUDA kernel (debug aid)
         self.hybrid_delta_rule = bool(int(os.environ.get("Q38_GDN_HYBRID", "0")))
+        # True: no atomically accumulated split-K; weight gradients are then bitwise reproducible from run to run
+        self.deterministic = bool(int(os.environ.get("Q38_DETERMINISTIC", "0")))
         if self_check:
             self._self_check()
 
@@ -379,6 +402,16 @@ class Backend:
         if a.shape[1] % 8 or b.shape[1] % 8 or not self.layouts["tn"]:
             return (a.t() @ b).to(out_dtype)
         return gemm(a, b, a_mn_major=True, b_mn_major=True, out_dtype=out_dtype)
+
+    def weight_grad(self, dy, x, weight):
+        """dW = dy^T x.  When the parameter already has an fp32 gradient buffer (the trainer's arena) the product is
+        accumulated straight into it with split-K and nothing is returned to autograd; otherwise a fresh tensor is returned."""
+        grad = weight.grad
+        fast = self.layouts["tn"] and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0
+        if fast and grad is not None and grad.dtype == torch.float32 and grad.is_contiguous() and grad.dim() == 2:
+            gemm(dy, x, out=grad, a_mn_major=True, b_mn_major=True, accumulate=True, splits=-1 if self.deterministic else 0)
+            return None
+        return self.mm_tn(dy, x).to(weight.dtype)
 
     def _self_check(self):
         """Compare each operand layout of the tensor-core GEMM with a PyTorch matmul on a small problem.  A layout that
@@ -428,7 +461,8 @@ class Backend:
     def delta_rule(self, q, k, v, g, beta):
         """q,k [B,S,Hk,64], v [B,S,Hv,64] bf16, g fp32 / beta [B,S,Hv] -> o [B,S,Hv,64] bf16 (S a multiple of 64)."""
         if not self.hybrid_delta_rule:
-            return _DeltaRule.apply(q, k, v, g, beta)
+            Hk, Hv = k.shape[2], v.shape[2]
+            return _DeltaRule.apply(torch.cat([q.flatten(2), k.flatten(2), v.flatten(2)], dim=-1), g, beta, Hk, Hv)
         from ..models import modeling
         B, S, Hv = v.shape[0], v.shape[1], v.shape[2]
         ops = modeling.gdn_chunk_operands(q, k, v, g, beta)
@@ -443,11 +477,14 @@ class Backend:
         from ..models import modeling
         F = torch.nn.functional
         qkv = _ConvSilu.apply(self.linear(x, m.in_proj_qkv.weight), m.conv1d.weight)
-        q, k, v = qkv.split([m.key_dim, m.key_dim, m.value_dim], dim=-1)
         z = self.linear(x, m.in_proj_z.weight)
         beta = self.linear(x, m.in_proj_b.weight).sigmoid()
         g = -m.A_log.float().exp() * F.softplus(self.linear(x, m.in_proj_a.weight).float() + m.dt_bias.float())
-        o = self.delta_rule(q.reshape(B, S, -1, 64), k.reshape(B, S, -1, 64), v.reshape(B, S, -1, 64), g, beta)
+        if self.hybrid_delta_rule:
+            q, k, v = qkv.split([m.key_dim, m.key_dim, m.value_dim], dim=-1)
+            o = self.delta_rule(q.reshape(B, S, -1, 64), k.reshape(B, S, -1, 64), v.reshape(B, S, -1, 64), g, beta)
+        else:
+            o = _DeltaRule.apply(qkv, g, beta, m.num_k_heads, m.num_v_heads)
         o = self.gated_rmsnorm(o.reshape(-1, 64), z.reshape(-1, 64), m.norm.weight, m.norm.variance_epsilon)
         return self.linear(o.reshape(B, S, -1), m.out_proj.weight)
 

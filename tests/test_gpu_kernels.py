@@ -360,3 +360,15 @@ def test_gemm_tf32(ops, M, N, K):
     got = ops.gemm(a, b, out_dtype=torch.float32)
     ops.check_errors()
     assert rel_err(got, a @ b.t()) < 3e-3            # 10-bit mantissa operands, fp32 accumulation
+
+
+@pytest.mark.parametrize("splits", [0, 3, 7])
+def test_gemm_split_k_accumulates(ops, splits):
+    torch.manual_seed(17)
+    a = torch.randn(4096, 64, device="cuda").to(torch.bfloat16)       # [K, M]: reduction over 4096 rows
+    b = torch.randn(4096, 576, device="cuda").to(torch.bfloat16)
+    c = torch.randn(64, 576, device="cuda")
+    ref = c + a.float().t() @ b.float()
+    ops.gemm(a, b, out=c, a_mn_major=True, b_mn_major=True, accumulate=True, splits=splits)
+    ops.check_errors()
+    assert rel_err(c, ref) < 1e-3
