@@ -22,6 +22,20 @@ TORCH_LIBRARY(q38, m) {
   m.def("qsa_indexer_bwd(Tensor qi, Tensor ki, Tensor wi, Tensor blse, Tensor dblse, float gscale, float scale) -> Tensor[]");
   m.def("qsa_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor? count, Tensor? index, float scale) -> Tensor[]");
   m.def("qsa_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor dout, Tensor lse, Tensor sel, float scale) -> Tensor[]");
+  m.def("p2p_alloc(int nbytes, int device) -> Tensor", &q38::p2p_alloc);
+  m.def("p2p_get_handle(Tensor t) -> Tensor", &q38::p2p_get_handle);
+  m.def("p2p_open_handle(Tensor handle, int device) -> int", &q38::p2p_open_handle);
+  m.def("p2p_close_handle(int ptr, int device) -> ()", &q38::p2p_close_handle);
+  m.def("p2p_barrier(Tensor(a!) own_flags, int[] peer_flags, int rank, int epoch, float wait_seconds, Tensor(b!) err) -> ()",
+        [](at::Tensor& f, std::vector<int64_t> peers, int64_t rank, int64_t epoch, double wait, at::Tensor& err) { q38::p2p_barrier(f, peers, rank, epoch, wait, err); });
+  m.def("p2p_reduce_scatter(int[] grads, int rank, int start, int count, float scale, int device) -> ()",
+        [](std::vector<int64_t> g, int64_t rank, int64_t start, int64_t count, double scale, int64_t dev) { q38::p2p_reduce_scatter(g, rank, start, count, scale, dev); });
+  m.def("p2p_all_gather(Tensor params, Tensor? shadow, int[] peer_params, int[] peer_shadow, int rank, int start, int count) -> ()",
+        [](const at::Tensor& p, c10::optional<at::Tensor> sh, std::vector<int64_t> pp, std::vector<int64_t> ps, int64_t rank, int64_t start, int64_t count) {
+          q38::p2p_all_gather(p, sh, pp, ps, rank, start, count);
+        });
+  m.def("p2p_publish_scalar(Tensor value, int[] peer_slots, int rank) -> ()",
+        [](const at::Tensor& v, std::vector<int64_t> slots, int64_t rank) { q38::p2p_publish_scalar(v, slots, rank); });
   m.def("conv_silu_fwd(Tensor x, Tensor w) -> Tensor");
   m.def("conv_silu_bwd(Tensor x, Tensor w, Tensor dy) -> Tensor[]");
   m.def("gdn_prep_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta) -> Tensor[]");

@@ -1,0 +1,176 @@
+// Peer-memory collectives for the data-parallel gradient path: every rank maps the other ranks' gradient / parameter
+// arenas (cudaMalloc + CUDA IPC handles over NVLink) and the kernels below read and write them directly.
+//
+//   p2p_barrier          flag barrier across GPUs: rank r stores `epoch` into slot r of every peer's flag array (after a
+//                        system-scope fence) and waits until all slots of its own array reached `epoch`.
+//   p2p_reduce_scatter   rank r replaces segment r of its gradient arena by scale * sum_p grads_p[segment r]; the cast /
+//                        mean scaling is fused into the reduction and the summation order is the same on every rank.
+//   p2p_all_gather       rank r stores its updated fp32 parameters and bf16 shadow of segment r into every peer's arenas.
+//   p2p_publish_scalar   writes one double into slot r of every peer's scalar array (global gradient norm).
+//
+// Every wait is bounded by a clock budget; on expiry the kernel records ERR_PEER_WAIT and returns, the context stays
+// usable and the host raises.  Loads from peers are plain (no TMA, no multicast); NVLS multimem is not used.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace q38 {
+
+constexpr int MAX_PEERS = 16;
+
+struct PeerPtrs { void* p[MAX_PEERS]; };
+
+__device__ __forceinline__ long long ld_volatile_ll(const long long* p) {
+  long long v;
+  asm volatile("ld.volatile.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// One CTA of 32 threads.  wait_cycles bounds the spin (about a second at 2 GHz by default).
+__global__ void p2p_barrier_kernel(long long* __restrict__ own_flags, PeerPtrs peers, int rank, int world, long long epoch,
+                                   long long wait_cycles, int* __restrict__ err) {
+  const int t = threadIdx.x;
+  __threadfence_system();                                  // everything this GPU wrote before the barrier is visible first
+  if (t < world) {
+    long long* dst = reinterpret_cast<long long*>(peers.p[t]) + rank;
+    asm volatile("st.volatile.global.s64 [%0], %1;" ::"l"(dst), "l"(epoch) : "memory");
+  }
+  if (t < world) {
+    const long long start = clock64();
+    bool ok = false;
+    while (clock64() - start < wait_cycles) {
+      if (ld_volatile_ll(own_flags + t) >= epoch) { ok = true; break; }
+      __nanosleep(200);
+    }
+    if (!ok) report_error(err, ERR_PEER_WAIT);
+  }
+  __threadfence_system();
+}
+
+// own[i] = scale * sum_p grads_p[i] for i in [start, start + count); 16-byte loads; count and start multiples of 4.
+__global__ void __launch_bounds__(256) p2p_reduce_scatter_kernel(PeerPtrs grads, int rank, int world, long long start, long long count, float scale) {
+  const float4* src[MAX_PEERS];
+#pragma unroll
+  for (int p = 0; p < MAX_PEERS; ++p) src[p] = p < world ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + start) : nullptr;
+  float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[rank]) + start);
+  const long long n4 = count / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < MAX_PEERS; ++p) {
+      if (p < world) { const float4 v = src[p][i]; acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+    }
+    dst[i] = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+  }
+}
+
+// Push segment [start, start + count) of the local fp32 parameters (and bf16 shadow) into every peer's arenas.
+__global__ void __launch_bounds__(256) p2p_all_gather_kernel(const float* __restrict__ params, const __nv_bfloat16* __restrict__ shadow, PeerPtrs peer_params,
+                                                             PeerPtrs peer_shadow, int rank, int world, long long start, long long count) {
+  const long long n4 = count / 4;
+  const float4* src = reinterpret_cast<const float4*>(params + start);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = src[i];
+    uint2 packed;
+    {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      packed.x = *reinterpret_cast<uint32_t*>(&lo); packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    }
+#pragma unroll
+    for (int p = 0; p < MAX_PEERS; ++p) {
+      if (p < world && p != rank) {
+        reinterpret_cast<float4*>(reinterpret_cast<float*>(peer_params.p[p]) + start)[i] = v;
+        if (shadow != nullptr) reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(peer_shadow.p[p]) + start)[i] = packed;
+      }
+    }
+  }
+}
+
+__global__ void p2p_publish_scalar_kernel(const double* __restrict__ value, PeerPtrs slots, int rank, int world) {
+  const int t = threadIdx.x;
+  if (t < world) reinterpret_cast<double*>(slots.p[t])[rank] = *value;
+}
+
+// ---- host: allocation and IPC ------------------------------------------------------------------------------------------------
+at::Tensor p2p_alloc(int64_t nbytes, int64_t device) {
+  const c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+  void* ptr = nullptr;
+  C10_CUDA_CHECK(cudaMalloc(&ptr, (size_t)nbytes));
+  C10_CUDA_CHECK(cudaMemset(ptr, 0, (size_t)nbytes));
+  return at::from_blob(ptr, {nbytes}, [](void* p) { cudaFree(p); }, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, (c10::DeviceIndex)device));
+}
+
+at::Tensor p2p_get_handle(const at::Tensor& t) {
+  cudaIpcMemHandle_t h;
+  C10_CUDA_CHECK(cudaIpcGetMemHandle(&h, t.data_ptr()));
+  auto out = at::empty({(int64_t)sizeof(h)}, at::TensorOptions().dtype(at::kByte));
+  std::memcpy(out.data_ptr(), &h, sizeof(h));
+  return out;
+}
+
+int64_t p2p_open_handle(const at::Tensor& handle, int64_t device) {
+  const c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+  TORCH_CHECK(handle.numel() == (int64_t)sizeof(cudaIpcMemHandle_t), "p2p_open_handle: bad handle size");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle.data_ptr(), sizeof(h));
+  void* ptr = nullptr;
+  C10_CUDA_CHECK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return reinterpret_cast<int64_t>(ptr);
+}
+
+void p2p_close_handle(int64_t ptr, int64_t device) {
+  const c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+  cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr));
+}
+
+static PeerPtrs to_ptrs(const std::vector<int64_t>& v) {
+  TORCH_CHECK((int)v.size() <= MAX_PEERS, "at most 16 peers");
+  PeerPtrs p{};
+  for (size_t i = 0; i < v.size(); ++i) p.p[i] = reinterpret_cast<void*>(v[i]);
+  return p;
+}
+
+void p2p_barrier(at::Tensor& own_flags, std::vector<int64_t> peer_flags, int64_t rank, int64_t epoch, double wait_seconds, at::Tensor& err) {
+  const c10::cuda::CUDAGuard guard(own_flags.device());
+  const long long cycles = (long long)(wait_seconds * 1.9e9);
+  p2p_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<long long*>(own_flags.data_ptr()), to_ptrs(peer_flags), (int)rank,
+                                                                     (int)peer_flags.size(), (long long)epoch, cycles, err.data_ptr<int>());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start, int64_t count, double scale, int64_t device) {
+  const c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
+  TORCH_CHECK(start % 4 == 0 && count % 4 == 0, "p2p_reduce_scatter: segment must be 16-byte aligned");
+  if (count == 0) return;
+  const int grid = (int)std::min<int64_t>((count / 4 + 255) / 256, kNumSMs * 8);
+  p2p_reduce_scatter_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(to_ptrs(grads), (int)rank, (int)grads.size(), start, count, (float)scale);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void p2p_all_gather(const at::Tensor& params, const c10::optional<at::Tensor>& shadow, std::vector<int64_t> peer_params, std::vector<int64_t> peer_shadow,
+                    int64_t rank, int64_t start, int64_t count) {
+  const c10::cuda::CUDAGuard guard(params.device());
+  TORCH_CHECK(start % 4 == 0 && count % 4 == 0, "p2p_all_gather: segment must be 16-byte aligned");
+  if (count == 0) return;
+  const int grid = (int)std::min<int64_t>((count / 4 + 255) / 256, kNumSMs * 8);
+  p2p_all_gather_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(params.data_ptr<float>(),
+      shadow.has_value() ? (const __nv_bfloat16*)shadow->data_ptr() : nullptr, to_ptrs(peer_params), to_ptrs(peer_shadow), (int)rank,
+      (int)peer_params.size(), start, count);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void p2p_publish_scalar(const at::Tensor& value, std::vector<int64_t> peer_slots, int64_t rank) {
+  const c10::cuda::CUDAGuard guard(value.device());
+  TORCH_CHECK(value.scalar_type() == at::kDouble && value.numel() == 1, "p2p_publish_scalar: one double required");
+  p2p_publish_scalar_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(value.data_ptr<double>(), to_ptrs(peer_slots), (int)rank, (int)peer_slots.size());
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+}  // namespace q38

@@ -75,6 +75,16 @@ std::vector<at::Tensor> qsa_attn_fwd(const at::Tensor& q, const at::Tensor& k, c
                                      const c10::optional<at::Tensor>& index, double scale);
 std::vector<at::Tensor> qsa_attn_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o, const at::Tensor& dout,
                                      const at::Tensor& lse, const at::Tensor& sel, double scale);
+// comm.cu
+at::Tensor p2p_alloc(int64_t nbytes, int64_t device);
+at::Tensor p2p_get_handle(const at::Tensor& t);
+int64_t p2p_open_handle(const at::Tensor& handle, int64_t device);
+void p2p_close_handle(int64_t ptr, int64_t device);
+void p2p_barrier(at::Tensor& own_flags, std::vector<int64_t> peer_flags, int64_t rank, int64_t epoch, double wait_seconds, at::Tensor& err);
+void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start, int64_t count, double scale, int64_t device);
+void p2p_all_gather(const at::Tensor& params, const c10::optional<at::Tensor>& shadow, std::vector<int64_t> peer_params, std::vector<int64_t> peer_shadow,
+                    int64_t rank, int64_t start, int64_t count);
+void p2p_publish_scalar(const at::Tensor& value, std::vector<int64_t> peer_slots, int64_t rank);
 // conv.cu
 at::Tensor conv_silu_fwd(const at::Tensor& x, const at::Tensor& w);
 std::vector<at::Tensor> conv_silu_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy);

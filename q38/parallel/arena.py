@@ -102,7 +102,7 @@ class ParamArena:
         self.exp_avg = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
         self.exp_avg_sq = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
         self.muon_buf = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
-        self.shadow = torch.zeros(self.numel, dtype=torch.bfloat16, device=self.device) if self.device.type == "cuda" else None
+        self.shadow = allocate(self.numel, torch.bfloat16) if self.device.type == "cuda" else None
         with torch.no_grad():
             for unit in self.units:
                 p = unit.param

@@ -77,6 +77,7 @@ class GradEngine:
             self.arena.refresh_shadow()
             return
         if self.transport is not None:
+            self.arena.refresh_shadow(self.rank)
             self.transport.all_gather_params()
             return
         for owner, (s, e) in enumerate(self.arena.segments):
@@ -88,8 +89,11 @@ class GradEngine:
         s, e = self.arena.segments[self.rank]
         sq = self.arena.grads[s:e].double().pow(2).sum() if self.device.type == "cpu" else self._sumsq(s, e)
         if self.world > 1:
-            sq = sq.clone()
-            dist.all_reduce(sq)
+            if self.transport is not None:
+                sq = self.transport.allreduce_sum_scalar(sq)
+            else:
+                sq = sq.clone()
+                dist.all_reduce(sq)
         return sq.sqrt().float()
 
     def _sumsq(self, s, e):
