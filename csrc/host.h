@@ -85,6 +85,8 @@ void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start,
 void p2p_all_gather(const at::Tensor& params, const c10::optional<at::Tensor>& shadow, std::vector<int64_t> peer_params, std::vector<int64_t> peer_shadow,
                     int64_t rank, int64_t start, int64_t count);
 void p2p_publish_scalar(const at::Tensor& value, std::vector<int64_t> peer_slots, int64_t rank);
+// ce.cu
+at::Tensor ce_inplace(at::Tensor& logits, const at::Tensor& target);
 // conv.cu
 at::Tensor conv_silu_fwd(const at::Tensor& x, const at::Tensor& w);
 std::vector<at::Tensor> conv_silu_bwd(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dy);

@@ -556,7 +556,58 @@ class Backend:
         return dict(native=native, gemm_layouts=self.layouts)
 
 
+class _LinearCE(torch.autograd.Function):
+    """Sum of token cross-entropies of ``hidden @ weight^T`` (ignore index -100) without fp32 logits.
+
+    Forward, per chunk of rows: vocabulary GEMM (bf16 logits) -> in-place CE kernel that leaves softmax - onehot in the
+    logits buffer.  The gradient buffers are kept (bf16) and the backward is two GEMMs: d(hidden) = dlogits W and
+    d(W) += dlogits^T hidden (split-K, accumulated into the tied embedding's gradient), both scaled by the upstream gradient."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, target, backend, rows):
+        ops = load()
+        h2 = hidden.reshape(-1, hidden.shape[-1]).to(torch.bfloat16).contiguous()
+        w = _bf16_weight(weight)
+        total = torch.zeros((), dtype=torch.float32, device=hidden.device)
+        grads = []
+        for o in range(0, h2.shape[0], rows):
+            logits = backend.mm_nt(h2[o:o + rows], w)
+            total = total + ops.ce_inplace(logits, target[o:o + rows].contiguous()).sum()
+            grads.append(logits)
+        ctx.save_for_backward(h2, weight, *grads)
+        ctx.backend, ctx.rows, ctx.shape, ctx.dtype = backend, rows, hidden.shape, hidden.dtype
+        return total
+
+    @staticmethod
+    def backward(ctx, g):
+        h2, weight, *grads = ctx.saved_tensors
+        backend, rows = ctx.backend, ctx.rows
+        w = _bf16_weight(weight)
+        gs = g.to(torch.bfloat16)
+        dh = torch.empty_like(h2)
+        need_w = ctx.needs_input_grad[1]
+        dw_total = None
+        for i, dl in enumerate(grads):
+            o = i * rows
+            dh[o:o + rows] = backend.mm_nn(dl, w)
+            if need_w:
+                part = backend.weight_grad(dl, (h2[o:o + rows] * gs), weight)
+                if part is not None:
+                    dw_total = part if dw_total is None else dw_total + part
+        return (dh * gs).view(ctx.shape).to(ctx.dtype), dw_total, None, None, None
+
+
 def _chunked_linear_ce(backend, weight, hidden, target, reduction, rows=8192):
+    V = weight.shape[0]
+    if hidden.shape[-1] % 8 == 0 and V % 8 == 0 and V <= 16384:
+        total = _LinearCE.apply(hidden, weight, target, backend, rows)
+        if reduction == "sum":
+            return total
+        return total / (target != -100).sum().clamp_min(1)
+    return _chunked_linear_ce_reference(backend, weight, hidden, target, reduction, rows)
+
+
+def _chunked_linear_ce_reference(backend, weight, hidden, target, reduction, rows=8192):
     total = hidden.new_zeros((), dtype=torch.float32)
     count = (target != -100).sum()
     for o in range(0, hidden.shape[0], rows):

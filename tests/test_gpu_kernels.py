@@ -372,3 +372,24 @@ def test_gemm_split_k_accumulates(ops, splits):
     ops.gemm(a, b, out=c, a_mn_major=True, b_mn_major=True, accumulate=True, splits=splits)
     ops.check_errors()
     assert rel_err(c, ref) < 1e-3
+
+
+def test_fused_linear_cross_entropy(ops):
+    from q38.models import modeling
+    backend = modeling.get_backend()
+    torch.manual_seed(18)
+    T, h, V = 3000, 128, 10112
+    hid = torch.randn(T, h, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (0.1 * torch.randn(V, h, device="cuda")).requires_grad_()
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    tgt[::7] = -100
+    for reduction in ("mean", "sum"):
+        hid.grad = w.grad = None
+        loss = backend.linear_cross_entropy(w, hid, tgt, reduction)
+        (loss * 0.37).backward()
+        ops.check_errors()
+        hr, wr = hid.detach().float().requires_grad_(), w.detach().to(torch.bfloat16).float().requires_grad_()
+        ref = torch.nn.functional.cross_entropy(hr @ wr.t(), tgt, ignore_index=-100, reduction=reduction)
+        (ref * 0.37).backward()
+        assert abs(loss.item() - ref.item()) < 5e-3 * abs(ref.item())
+        assert rel_err(hid.grad, hr.grad) < 3e-2 and rel_err(w.grad, wr.grad) < 3e-2
