@@ -40,6 +40,8 @@ def parse():
     ap.add_argument("--grad_sync", default="auto", choices=("auto", "p2p", "collective"))
     ap.add_argument("--zipf", type=float, default=0.0, help="Zipf exponent of the token distribution (0 = uniform)")
     ap.add_argument("--grad_ckpt", type=int, default=-1)
+    ap.add_argument("--expert_parallel", type=int, default=0, help="1: split the experts over the GPUs (needs --gpus > 1)")
+    ap.add_argument("--ep_capacity", type=float, default=4.0)
     return ap.parse_args()
 
 
@@ -82,7 +84,8 @@ def main():
     vocab, eos = 10112, 53
     cfg = model_config(preset["model"], vocab, a.seq, bos_token_id=1, eos_token_id=eos, pad_token_id=0)
     fc = count(cfg.to_dict(), a.seq)
-    args = SimpleNamespace(**{**train, "aux_coef": preset["model"]["aux_coef"], "grad_sync": a.grad_sync,
+    args = SimpleNamespace(**{**train, "aux_coef": preset["model"]["aux_coef"], "grad_sync": a.grad_sync, "micro_bs": micro_bs, "seq": a.seq,
+                              "expert_parallel": a.expert_parallel, "ep_capacity": a.ep_capacity,
                               "grad_ckpt": train.get("grad_ckpt", 0) if a.grad_ckpt < 0 else a.grad_ckpt})
     torch.manual_seed(0)
     trainer = Trainer(cfg, args, dev, rank, world)
@@ -156,7 +159,7 @@ def main():
             "vs_baseline": published, "dtype": "bf16", "data": "synthetic packed stream (uniform ids, EOS at geometric(1024) boundaries), random-init weights",
             "impl": "ours",
             "config": {"model": a.preset, "global_batch": batch_tokens // a.seq, "seq_len": a.seq, "micro_bs": micro_bs,
-                       "accum": accum, "parallelism": f"dp{world}", "phase": a.phase, "grad_sync": trainer.engine.mode,
+                       "accum": accum, "parallelism": f"dp{world}" + (f"+ep{world}" if a.expert_parallel and world > 1 else ""), "phase": a.phase, "grad_sync": trainer.engine.mode,
                        "grad_ckpt": int(args.grad_ckpt), "zipf": a.zipf,
                        "l2": "no flush: one step streams >10 GB of activations and 1.3 GB of fp32 weights, far above the 126 MB L2",
                        "train_flops_per_token": fc["train_flops_per_token"]},
@@ -165,7 +168,7 @@ def main():
             "gpu_launches": launches, "clocks": clocks.summary(), "losses_last_step": last, "losses_last_step_e2e": last_host,
             "backend": backend, "timed_wall_s": wall,
         }), flush=True)
-    trainer.engine.close()
+    trainer.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -22,6 +22,17 @@ TORCH_LIBRARY(q38, m) {
   m.def("qsa_indexer_bwd(Tensor qi, Tensor ki, Tensor wi, Tensor blse, Tensor dblse, float gscale, float scale) -> Tensor[]");
   m.def("qsa_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor? count, Tensor? index, float scale) -> Tensor[]");
   m.def("qsa_attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor dout, Tensor lse, Tensor sel, float scale) -> Tensor[]");
+  m.def("ep_publish_counts(Tensor offsets, int rank, int[] peer_counts) -> ()",
+        [](const at::Tensor& o, int64_t rank, std::vector<int64_t> peers) { q38::ep_publish_counts(o, rank, peers); });
+  m.def("ep_plan(Tensor counts_all, int rank, int world, int capacity, Tensor(a!) err) -> Tensor[]",
+        [](const at::Tensor& c, int64_t rank, int64_t world, int64_t cap, at::Tensor& err) { return q38::ep_plan(c, rank, world, cap, err); });
+  m.def("ep_dispatch(Tensor src, Tensor perm, Tensor expert_of_pair, Tensor offsets, Tensor send_base, int K, int E_loc, int capacity, bool gather, int rank, int[] recv_rows, int[] ret_rank, int[] ret_row) -> ()",
+        [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, const at::Tensor& d, const at::Tensor& e, int64_t K, int64_t El, int64_t cap, bool g, int64_t rank,
+           std::vector<int64_t> r0, std::vector<int64_t> r1, std::vector<int64_t> r2) { q38::ep_dispatch(a, b, c, d, e, K, El, cap, g, rank, r0, r1, r2); });
+  m.def("moe_grouped_gemm_return(Tensor rows, Tensor weight, Tensor out, Tensor sched, bool b_mn_major, Tensor(a!) err, Tensor ret_rank, Tensor ret_row, int[] peer_out) -> ()",
+        [](const at::Tensor& r, const at::Tensor& w, at::Tensor o, const at::Tensor& s, bool mn, at::Tensor& err, const at::Tensor& rr, const at::Tensor& rw, std::vector<int64_t> po) {
+          q38::moe_grouped_gemm_return(r, w, o, s, mn, err, rr, rw, po);
+        });
   m.def("p2p_alloc(int nbytes, int device) -> Tensor", &q38::p2p_alloc);
   m.def("p2p_get_handle(Tensor t) -> Tensor", &q38::p2p_get_handle);
   m.def("p2p_open_handle(Tensor handle, int device) -> int", &q38::p2p_open_handle);

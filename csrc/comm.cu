@@ -30,9 +30,17 @@ __device__ __forceinline__ long long ld_volatile_ll(const long long* p) {
 }
 
 // One CTA of 32 threads.  wait_cycles bounds the spin (about a second at 2 GHz by default).
+// epoch < 0: take the next value of the device-side counter own_flags[MAX_PEERS] (all ranks execute the same sequence
+// of barriers, so the counters stay in lockstep; this form can be captured in a CUDA graph and replayed).
 __global__ void p2p_barrier_kernel(long long* __restrict__ own_flags, PeerPtrs peers, int rank, int world, long long epoch,
                                    long long wait_cycles, int* __restrict__ err) {
   const int t = threadIdx.x;
+  __shared__ long long next;
+  if (epoch < 0) {
+    if (t == 0) { next = own_flags[MAX_PEERS] + 1; own_flags[MAX_PEERS] = next; }
+    __syncthreads();
+    epoch = next;
+  }
   __threadfence_system();                                  // everything this GPU wrote before the barrier is visible first
   if (t < world) {
     long long* dst = reinterpret_cast<long long*>(peers.p[t]) + rank;

@@ -75,6 +75,14 @@ std::vector<at::Tensor> qsa_attn_fwd(const at::Tensor& q, const at::Tensor& k, c
                                      const c10::optional<at::Tensor>& index, double scale);
 std::vector<at::Tensor> qsa_attn_bwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& o, const at::Tensor& dout,
                                      const at::Tensor& lse, const at::Tensor& sel, double scale);
+// ep.cu
+void ep_publish_counts(const at::Tensor& offsets, int64_t rank, std::vector<int64_t> peer_counts);
+std::vector<at::Tensor> ep_plan(const at::Tensor& counts_all, int64_t rank, int64_t world, int64_t capacity, at::Tensor& err);
+void ep_dispatch(const at::Tensor& src, const at::Tensor& perm, const at::Tensor& expert_of_pair, const at::Tensor& offsets, const at::Tensor& send_base,
+                 int64_t K, int64_t E_loc, int64_t capacity, bool gather, int64_t rank, std::vector<int64_t> recv_rows, std::vector<int64_t> ret_rank,
+                 std::vector<int64_t> ret_row);
+void moe_grouped_gemm_return(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err,
+                             const at::Tensor& ret_rank, const at::Tensor& ret_row, std::vector<int64_t> peer_out);
 // comm.cu
 at::Tensor p2p_alloc(int64_t nbytes, int64_t device);
 at::Tensor p2p_get_handle(const at::Tensor& t);

@@ -290,6 +290,9 @@ struct GroupedArgs {
   long long c_expert_stride;        // WGRAD: elements between experts in C
   int M;                            // WGRAD: rows of C per expert
   int* err;
+  // Expert parallelism (EPI_STORE only): output row `row` is stored into rank ret_rank[row]'s buffer at row ret_row[row].
+  const int* ret_rank; const int* ret_row;
+  void* peer_out[16];
 };
 
 template <int EPI, bool A_MN, bool B_MN>
@@ -379,7 +382,9 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
         const int valid = rows_valid - kb * G_BK;          // rows of this K block that belong to the expert
         if (valid < G_BK) {
           // MN-major box = 64 K-rows of 128 bytes: rows >= valid hold another expert's data and are cleared
-          for (int i = lane; i < (G_BK - valid) * 8 * (G_BM / 64); i += 32) {
+          // both operands: rows past the expert's range may be another expert's rows or never-written buffer space
+          const int boxes = G_BM / 64 + p.bn / 64;               // the B boxes follow the A boxes in the stage
+          for (int i = lane; i < (G_BK - valid) * 8 * boxes; i += 32) {
             const int box = i / ((G_BK - valid) * 8), rem = i % ((G_BK - valid) * 8);
             *reinterpret_cast<uint4*>(a_tile + box * 8192 + (valid + rem / 8) * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
           }
@@ -464,7 +469,8 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
             ptx::tmem_ld_wait();
             if (live) {
               if (EPI == EPI_STORE) {
-                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out0) + row * p.ld0;
+                __nv_bfloat16* o = p.ret_rank ? reinterpret_cast<__nv_bfloat16*>(p.peer_out[p.ret_rank[row]]) + (long long)p.ret_row[row] * p.ld0
+                                              : reinterpret_cast<__nv_bfloat16*>(p.out0) + row * p.ld0;
                 if (n0 + c0 + 16 <= p.N && p.ld0 % 8 == 0) {
                   float v[16];
 #pragma unroll
@@ -546,13 +552,29 @@ static void check_bf16_2d(const at::Tensor& t, const char* name) {
 }
 
 // rows: sorted activations [P, K]; weight: [E, N, K] (K-major) or [E, K, N] (b_mn_major) bf16; out [P, N] bf16
+void moe_grouped_gemm_impl(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err,
+                           const int* ret_rank, const int* ret_row, const std::vector<int64_t>& peer_out);
+
 void moe_grouped_gemm(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err) {
+  moe_grouped_gemm_impl(rows, weight, out, sched, b_mn_major, err, nullptr, nullptr, {});
+}
+
+// Same product, but every output row is stored into the buffer of the rank it came from (peer_out[ret_rank[row]] at row
+// ret_row[row]); `out` only provides the row width and dtype of those buffers.
+void moe_grouped_gemm_return(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err,
+                             const at::Tensor& ret_rank, const at::Tensor& ret_row, std::vector<int64_t> peer_out) {
+  TORCH_CHECK(ret_rank.scalar_type() == at::kInt && ret_row.scalar_type() == at::kInt && peer_out.size() <= 16, "moe_grouped_gemm_return: bad return map");
+  moe_grouped_gemm_impl(rows, weight, out, sched, b_mn_major, err, ret_rank.data_ptr<int>(), ret_row.data_ptr<int>(), peer_out);
+}
+
+void moe_grouped_gemm_impl(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err,
+                           const int* ret_rank, const int* ret_row, const std::vector<int64_t>& peer_out) {
   check_bf16_2d(rows, "moe_grouped_gemm rows"); check_bf16_2d(out, "moe_grouped_gemm out");
   TORCH_CHECK(weight.dim() == 3 && weight.is_contiguous() && weight.scalar_type() == at::kBFloat16, "moe_grouped_gemm: weight must be contiguous bf16 [E,*,*]");
   const c10::cuda::CUDAGuard guard(rows.device());
   const int P = rows.size(0), K = rows.size(1), E = weight.size(0);
   const int N = b_mn_major ? weight.size(2) : weight.size(1);
-  TORCH_CHECK((b_mn_major ? weight.size(1) : weight.size(2)) == K && out.size(0) == P && out.size(1) == N, "moe_grouped_gemm: shape mismatch");
+  TORCH_CHECK((b_mn_major ? weight.size(1) : weight.size(2)) == K && (ret_rank || out.size(0) == P) && out.size(1) == N, "moe_grouped_gemm: shape mismatch");
   const int bn = N <= 64 ? 64 : 128;
   const int max_tiles = (sched.numel() - 1) / 3;
   CUtensorMap ta = make_tmap_bf16(rows.data_ptr(), K, P, 1, K, 0, G_BM);
@@ -561,6 +583,8 @@ void moe_grouped_gemm(const at::Tensor& rows, const at::Tensor& weight, at::Tens
   GroupedArgs p{};
   p.sched = sched.data_ptr<int>(); p.bn = bn; p.K = K; p.N = N; p.b_rows_per_expert = b_mn_major ? K : N;
   p.out0 = out.data_ptr(); p.ld0 = N; p.err = err.data_ptr<int>();
+  p.ret_rank = ret_rank; p.ret_row = ret_row;
+  for (size_t i = 0; i < peer_out.size(); ++i) p.peer_out[i] = reinterpret_cast<void*>(peer_out[i]);
   dim3 grid(max_tiles, (N + bn - 1) / bn, 1);
   auto stream = at::cuda::getCurrentCUDAStream();
   if (b_mn_major) launch_grouped<EPI_STORE, false, true>(ta, tb, p, grid, 1, stream);

@@ -381,6 +381,7 @@ class Backend:
         self.hybrid_delta_rule = bool(int(os.environ.get("Q38_GDN_HYBRID", "0")))
         # True: no atomically accumulated split-K; weight gradients are then bitwise reproducible from run to run
         self.deterministic = bool(int(os.environ.get("Q38_DETERMINISTIC", "0")))
+        self.ep = None            # an `ExpertParallel` context when the experts are split over ranks
         if self_check:
             self._self_check()
 
@@ -540,7 +541,11 @@ class Backend:
         top_w, top_idx, prob_sum, counts = _Route.apply(logits, block.gate.top_k)
         if block._recording():
             block.stats_sink.add(counts, prob_sum, x2.shape[0])
-        routed = _Experts.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj)
+        if self.ep is not None:
+            from ..parallel.ep import _ExpertsEP
+            routed = _ExpertsEP.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj, self.ep, self.ep.layer_index(block))
+        else:
+            routed = _Experts.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj)
         shared_gate = torch.sigmoid(self.linear(x2, block.shared_expert_gate.weight))
         shared = block.shared_expert
         mid = torch.nn.functional.silu(self.linear(x2, shared.gate_proj.weight)) * self.linear(x2, shared.up_proj.weight)

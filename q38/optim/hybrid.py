@@ -111,7 +111,12 @@ class HybridOptimizer:
                             group["lr"], group["weight_decay"], grad_scale)
         if self.muon:
             owned = [u.param for u in a.owned(self.rank, "muon")]
-            self.muon.step(params=owned, grad_scale=grad_scale)
+            slices = {}
+            for unit in a.local_units():                     # expert-parallel tensors: this rank updates its own experts only
+                owned.append(unit.param)
+                n = unit.param.shape[0] // a.world
+                slices[id(unit.param)] = slice(self.rank * n, (self.rank + 1) * n)
+            self.muon.step(params=owned, grad_scale=grad_scale, slices=slices)
 
     def zero_grad(self, set_to_none=True):
         if self.arena is not None:

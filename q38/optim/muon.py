@@ -55,13 +55,15 @@ class Muon(torch.optim.Optimizer):
         return state["buf"]
 
     @torch.no_grad()
-    def step(self, closure=None, params=None, grad_scale=None):
+    def step(self, closure=None, params=None, grad_scale=None, slices=None):
         """`params`: optional subset (the units this rank owns).  `grad_scale`: optional scalar tensor the
-        gradients are multiplied with before use (the clip coefficient), without modifying `.grad`."""
+        gradients are multiplied with before use (the clip coefficient), without modifying `.grad`.
+        `slices`: ``{id(param): slice}`` restricts a stacked parameter (experts ``[E, a, b]``) to a range of its matrices."""
         keep = None if params is None else {id(p) for p in params}
+        slices = slices or {}
         on_gpu = any(p.is_cuda for g in self.param_groups for p in g["params"])
         if not on_gpu or os.environ.get("Q38_MUON_BASELINE"):
-            return self._reference_step(keep, grad_scale)
+            return self._reference_step(keep, grad_scale, slices)
         from ..ops import muon_batched_step
         for group in self.param_groups:
             by_shape = {}
@@ -73,22 +75,28 @@ class Muon(torch.optim.Optimizer):
                 views = []
                 for p in plist:
                     buf = self._buffer(p)
-                    views.append((p.view(-1, rows, cols), p.grad.view(-1, rows, cols), buf.view(-1, rows, cols)))
+                    sl = slices.get(id(p), slice(None))
+                    views.append((p.view(-1, rows, cols)[sl], p.grad.view(-1, rows, cols)[sl], buf.view(-1, rows, cols)[sl]))
                 muon_batched_step(views, per_call, lr=group["lr"], momentum=group["momentum"],
                                   weight_decay=group["weight_decay"], ns_steps=group["ns_steps"],
                                   scale=update_scale((rows, cols), group["rms_scale"]), grad_scale=grad_scale)
 
     @torch.no_grad()
-    def _reference_step(self, keep=None, grad_scale=None):
+    def _reference_step(self, keep=None, grad_scale=None, slices=None):
+        slices = slices or {}
         for group in self.param_groups:
             for p in group["params"]:
                 if p.grad is None or (keep is not None and id(p) not in keep):
                     continue
-                grad = p.grad if grad_scale is None else p.grad * grad_scale
-                buf = self._buffer(p)
+                sl = slices.get(id(p))
+                target, grad, buf = p, p.grad, self._buffer(p)
+                if sl is not None:
+                    target, grad, buf = p[sl], grad[sl], buf[sl]
+                if grad_scale is not None:
+                    grad = grad * grad_scale
                 buf.mul_(group["momentum"]).add_(grad)
                 update = grad.add(buf, alpha=group["momentum"])
                 ortho = newton_schulz(update, group["ns_steps"]).float()
                 if group["weight_decay"]:
-                    p.mul_(1 - group["lr"] * group["weight_decay"])
-                p.add_(ortho, alpha=-group["lr"] * update_scale(p.shape, group["rms_scale"]))
+                    target.mul_(1 - group["lr"] * group["weight_decay"])
+                target.add_(ortho, alpha=-group["lr"] * update_scale(p.shape, group["rms_scale"]))

@@ -36,6 +36,7 @@ class Unit:
     index: int          # registration order
     owner: int = 0
     offset: int = 0
+    local: bool = False   # expert-parallel tensor: every rank owns its own slice, never reduced or gathered
 
     @property
     def numel(self):
@@ -73,15 +74,19 @@ def _align(x, a):
 
 
 class ParamArena:
-    def __init__(self, model, device, world=1, muon=True, allocate=None):
-        """`allocate(numel, dtype)` returns a zero-filled flat tensor (peer-mapped memory for the p2p engine)."""
+    def __init__(self, model, device, world=1, muon=True, allocate=None, local_filter=None):
+        """`allocate(numel, dtype)` returns a zero-filled flat tensor (peer-mapped memory for the p2p engine).
+        `local_filter(name)` marks expert-parallel tensors: they live after all owner segments (`local_range`) and take no part
+        in the gradient reduce-scatter or the parameter all-gather."""
         self.device, self.world = torch.device(device), world
         allocate = allocate or (lambda numel, dtype: torch.zeros(numel, dtype=dtype, device=self.device))
         matrices, decay, no_decay = split_parameters(model, muon)
         order = {name: i for i, (name, _) in enumerate(model.named_parameters())}
         self.units = [Unit(n, p, g, order[n]) for g, items in zip(GROUPS, (matrices, decay, no_decay)) for n, p in items]
-        self.load = assign_owners(self.units, world)
-        self.units.sort(key=lambda u: (u.owner, GROUPS.index(u.group), u.index))
+        for unit in self.units:
+            unit.local = bool(local_filter and local_filter(unit.name))
+        self.load = assign_owners([u for u in self.units if not u.local], world)
+        self.units.sort(key=lambda u: (u.local, u.owner, GROUPS.index(u.group), u.index))
         # layout
         self.segments = []                       # per owner: (start, end)
         self.group_ranges = {}                   # (owner, group) -> (start, end)
@@ -90,12 +95,18 @@ class ParamArena:
             start = cursor
             for group in GROUPS:
                 g0 = cursor
-                for unit in (u for u in self.units if u.owner == owner and u.group == group):
+                for unit in (u for u in self.units if u.owner == owner and u.group == group and not u.local):
                     unit.offset = cursor
                     cursor = _align(cursor + unit.numel, UNIT_ALIGN)
                 self.group_ranges[(owner, group)] = (g0, cursor)
             cursor = _align(cursor, SEGMENT_ALIGN)
             self.segments.append((start, cursor))
+        local_start = cursor
+        for unit in (u for u in self.units if u.local):
+            unit.offset = cursor
+            cursor = _align(cursor + unit.numel, UNIT_ALIGN)
+        cursor = _align(cursor, SEGMENT_ALIGN)
+        self.local_range = (local_start, cursor)
         self.numel = cursor
         self.params = allocate(self.numel, torch.float32)
         self.grads = allocate(self.numel, torch.float32)
@@ -119,7 +130,10 @@ class ParamArena:
         return flat[unit.offset:unit.offset + unit.numel].view(unit.param.shape)
 
     def owned(self, rank, group=None):
-        return [u for u in self.units if u.owner == rank and (group is None or u.group == group)]
+        return [u for u in self.units if not u.local and u.owner == rank and (group is None or u.group == group)]
+
+    def local_units(self):
+        return [u for u in self.units if u.local]
 
     def refresh_shadow(self, rank=None):
         """Re-derive the bf16 shadow from the fp32 parameters (all of it, or one owner's segment)."""
@@ -127,6 +141,9 @@ class ParamArena:
             return
         s, e = (0, self.numel) if rank is None else self.segments[rank]
         self.shadow[s:e].copy_(self.params[s:e])
+        if rank is not None and self.local_range[1] > self.local_range[0]:
+            ls, le = self.local_range
+            self.shadow[ls:le].copy_(self.params[ls:le])
 
     def zero_grad(self):
         self.grads.zero_()

@@ -28,13 +28,18 @@ from .arena import ParamArena
 
 
 class GradEngine:
-    def __init__(self, model, device, rank=0, world=1, mode="auto", lr=1e-3, weight_decay=0.1, muon=True):
+    def __init__(self, model, device, rank=0, world=1, mode="auto", lr=1e-3, weight_decay=0.1, muon=True, expert_parallel=False):
         self.model, self.device, self.rank, self.world = model, torch.device(device), rank, world
+        self.expert_parallel = bool(expert_parallel) and world > 1
+        if self.expert_parallel and not muon:
+            raise ValueError("expert parallelism keeps the experts in the Muon group; run it with --muon 1")
         if mode == "auto":
             mode = "p2p" if (world > 1 and self.device.type == "cuda") else "collective"
         self.mode = mode
         self.transport = None
         allocate = None
+        if self.expert_parallel and mode != "p2p":
+            raise ValueError("expert parallelism needs the peer-memory transport (--grad_sync p2p on GPUs)")
         if world > 1 and mode == "p2p":
             from .p2p import PeerTransport
             self.transport = PeerTransport(self.device, rank, world)
@@ -43,7 +48,8 @@ class GradEngine:
             # rank 0's initial weights win, as with DDP's construction-time broadcast
             for p in model.parameters():
                 dist.broadcast(p.data, 0)
-        self.arena = ParamArena(model, self.device, world, muon=muon, allocate=allocate)
+        local_filter = (lambda name: ".mlp.experts." in name) if self.expert_parallel else None
+        self.arena = ParamArena(model, self.device, world, muon=muon, allocate=allocate, local_filter=local_filter)
         self.optimizer = HybridOptimizer(model, lr=lr, weight_decay=weight_decay, muon=muon, arena=self.arena, rank=rank)
         if self.transport is not None:
             self.transport.bind(self.arena)
@@ -85,9 +91,20 @@ class GradEngine:
                 dist.broadcast(self.arena.params[s:e], src=owner)
         self.arena.refresh_shadow()
 
+    def _local_grad_slices(self):
+        """This rank's slices of the expert-parallel gradient tensors."""
+        out = []
+        for unit in self.arena.local_units():
+            n = unit.param.shape[0] // self.world
+            out.append(unit.param.grad[self.rank * n:(self.rank + 1) * n])
+        return out
+
     def grad_norm(self):
         s, e = self.arena.segments[self.rank]
         sq = self.arena.grads[s:e].double().pow(2).sum() if self.device.type == "cpu" else self._sumsq(s, e)
+        for g in self._local_grad_slices():
+            g.mul_(1.0 / self.world)                      # tokens of all ranks are already summed in: scale to the data-parallel mean
+            sq = sq + g.double().pow(2).sum()
         if self.world > 1:
             if self.transport is not None:
                 sq = self.transport.allreduce_sum_scalar(sq)
@@ -131,6 +148,14 @@ class GradEngine:
                 for owner, (s, e) in enumerate(self.arena.segments):
                     if e > s:
                         dist.broadcast(flat[s:e], src=owner)
+            for unit in self.arena.local_units():             # assemble the full expert tensors from the ranks' slices
+                n = unit.param.shape[0] // self.world
+                for flat in (self.arena.params, self.arena.muon_buf):
+                    full = self.arena.view(flat, unit)
+                    for owner in range(self.world):
+                        dist.broadcast(full[owner * n:(owner + 1) * n], src=owner)
+            if self.arena.local_units():
+                self.arena.refresh_shadow()
         return self.model.state_dict(), self.optimizer.state_dict()
 
     def load_checkpoint(self, model_state, opt_state):

@@ -30,7 +30,7 @@ class PeerTransport:
         self.epoch = 0
         self.arena = None
         self._named = 0
-        self.flags = self._alloc_raw("flags", 8 * max(world, 16)).view(torch.int64)
+        self.flags = self._alloc_raw("flags", 8 * 32).view(torch.int64)          # 16 peer slots + the device-side epoch counter
         self.scalars = self._alloc_raw("scalars", 8 * max(world, 16)).view(torch.float64)
 
     def _alloc_raw(self, name, nbytes):
@@ -46,10 +46,20 @@ class PeerTransport:
         size = torch.empty((), dtype=dtype).element_size()
         return self._alloc_raw(name, numel * size)[:numel * size].view(dtype)
 
+    def allocate_named(self, name, numel, dtype):
+        size = torch.empty((), dtype=dtype).element_size()
+        return self._alloc_raw(name, numel * size)[:numel * size].view(dtype)
+
     def bind(self, arena):
         """Exchange IPC handles of every local buffer and map the peers' buffers."""
         self.arena = arena
-        names = sorted(self.local)
+        self.exchange()
+
+    def exchange(self):
+        """Publish the handles of buffers allocated since the last exchange and map the peers' counterparts (collective)."""
+        names = sorted(n for n in self.local if n not in self.peers)
+        if not names:
+            return
         mine = {n: bytes(self.ops.p2p_get_handle(self.local[n]).numpy().tobytes()) for n in names}
         gathered = [None] * self.world
         dist.all_gather_object(gathered, mine)
@@ -65,8 +75,9 @@ class PeerTransport:
         dist.barrier()
 
     def barrier(self):
-        self.epoch += 1
-        self.ops.p2p_barrier(self.flags, self.peers["flags"], self.rank, self.epoch, self.wait_seconds, ops.error_flag(self.device))
+        """Cross-GPU barrier on the current stream.  The epoch lives in device memory, so the same launch can be captured in a
+        CUDA graph and replayed; every rank must issue the same sequence of barriers."""
+        self.ops.p2p_barrier(self.flags, self.peers["flags"], self.rank, -1, self.wait_seconds, ops.error_flag(self.device))
 
     def reduce_scatter_mean(self):
         self.barrier()

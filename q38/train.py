@@ -51,7 +51,7 @@ TRAIN_DEFAULTS = dict(
     eval_sampling="random", eval_offset=0, final_eval_tokens=0, final_eval_offset=0, require_ready_pool=0,
     auto_micro_bs=0, probe_mem_frac=0.92, mtp_coef=0.3, kl_coef=0.05, muon=1, dense_warmup=1, grad_ckpt=0)
 # Options of this framework that the reference trainer does not have (never part of the resume contract).
-ENGINE_DEFAULTS = dict(grad_sync="auto", fp8_ffn=0, expert_parallel=0, export_hf=1, device="auto", cuda_graphs=1)
+ENGINE_DEFAULTS = dict(grad_sync="auto", fp8_ffn=0, expert_parallel=0, ep_capacity=4.0, export_hf=1, device="auto", cuda_graphs=1)
 
 # Everything that shapes the model, the data stream or the schedule must be unchanged on resume.
 RESUME_KEYS = (
@@ -321,14 +321,30 @@ class Trainer:
         self.loss_model = LossModel(self.model, cfg.num_experts, cfg.num_experts_per_tok)
         from .parallel import GradEngine
         self.engine = GradEngine(self.model, dev, rank, world, mode=getattr(a, "grad_sync", "auto"),
-                                 lr=a.lr, weight_decay=a.wd, muon=bool(a.muon))
+                                 lr=a.lr, weight_decay=a.wd, muon=bool(a.muon), expert_parallel=getattr(a, "expert_parallel", 0))
         self.opt = self.engine.optimizer
+        if self.engine.expert_parallel:
+            from .models import modeling
+            from .parallel.ep import ExpertParallel
+            layers = cfg.num_hidden_layers + (1 if cfg.mtp else 0)
+            modeling.get_backend().ep = ExpertParallel(
+                self.engine.transport, rank, world, cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts, cfg.num_experts_per_tok,
+                tokens=a.micro_bs * a.seq, layers=layers, capacity_factor=float(getattr(a, "ep_capacity", 4.0)))
         self.model.train()
         # One CUDA graph per (micro-batch shape, accumulation count, attention phase) replays forward + backward of a
         # micro-step without any per-kernel host work; the optimizer step stays eager.
         self.use_graphs = bool(getattr(a, "cuda_graphs", 1)) and dev.type == "cuda" and not getattr(a, "grad_ckpt", 0)
         self._graphs = {}
         self.replayed_launches = 0            # kernels of this library executed through graph replays
+
+    def close(self):
+        """Release peer mappings and detach the expert-parallel context from the kernel backend."""
+        from .models import modeling
+        backend = modeling.get_backend()
+        if backend is not None and getattr(backend, "ep", None) is not None:
+            backend.ep = None
+        self._graphs = {}
+        self.engine.close()
 
     def coefficients(self):
         return self.a.aux_coef, self.a.mtp_coef, self.a.kl_coef
@@ -346,7 +362,8 @@ class Trainer:
         entry = self._graphs.get(key)
         if entry is None:
             try:
-                sx, sy = torch.zeros_like(x), torch.zeros_like(y)
+                sx = torch.zeros(x.shape, dtype=x.dtype, device=self.dev)
+                sy = torch.zeros(y.shape, dtype=y.dtype, device=self.dev)
                 sx.copy_(x)
                 sy.copy_(y)
                 saved = self.engine.arena.grads.clone()
@@ -665,7 +682,7 @@ def main(argv=None):
         with open(f"{a.run_dir}/flops.json", "w") as f:
             json.dump({**fc, "train_tokens": tok_seen, "train_flops": flops_per_token * tok_seen}, f, indent=2)
         print("DONE", f"{a.run_dir}/hf" if a.export_hf else a.run_dir, flush=True)
-    trainer.engine.close()
+    trainer.close()
     if ddp:
         dist.barrier()
         dist.destroy_process_group()

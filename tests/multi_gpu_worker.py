@@ -26,31 +26,47 @@ def main():
                  ngram_rows=1024, mhc_iters=5, qsa_blocks=2)
     cfg = model_config(shape, 512, 256, eos_token_id=7, pad_token_id=0)
     results = {}
-    for mode in ("p2p", "collective"):
+    for mode in ("p2p", "collective", "ep", "ep_graph"):
         torch.manual_seed(0)
-        args = SimpleNamespace(**{**TRAIN_DEFAULTS, "aux_coef": 0.001, "lr": 3e-3, "grad_sync": mode, "cuda_graphs": 0})
+        args = SimpleNamespace(**{**TRAIN_DEFAULTS, "aux_coef": 0.001, "lr": 3e-3, "grad_sync": "collective" if mode == "collective" else "p2p",
+                                  "cuda_graphs": int(mode == "ep_graph"), "expert_parallel": int(mode.startswith("ep")), "micro_bs": 2, "seq": 256})
         trainer = Trainer(cfg, args, dev, rank, world)
-        assert trainer.engine.mode == mode
+        assert trainer.engine.mode == args.grad_sync
         gen = torch.Generator().manual_seed(100 + rank)
         x = torch.randint(1, 512, (2, 256), generator=gen).pin_memory()
         y = x.roll(-1, 1).pin_memory()
         losses = [trainer.train_step([(x, y)], lr=3e-3, dense=(i == 0)).tolist() for i in range(5)]
         ops.check_errors()
-        params = trainer.engine.arena.params.clone()
+        state, _ = trainer.engine.checkpoint_state()           # assembles expert slices when the experts are split over ranks
+        params = torch.cat([v.detach().float().reshape(-1) for k, v in sorted(state.items())])
         gathered = [torch.empty_like(params) for _ in range(world)]
         dist.all_gather(gathered, params)
         for other in gathered:
-            assert torch.equal(other, params), f"{mode}: replicas differ"
-        assert torch.equal(trainer.engine.arena.shadow, params.to(torch.bfloat16)), f"{mode}: bf16 shadow out of sync"
+            if not torch.equal(other, params):
+                offset, bad = 0, []
+                for key, value in sorted(state.items()):
+                    n = value.numel()
+                    if not torch.equal(other[offset:offset + n], params[offset:offset + n]):
+                        bad.append((key, (other[offset:offset + n] - params[offset:offset + n]).abs().max().item()))
+                    offset += n
+                raise AssertionError(f"{mode}: replicas differ in {bad[:8]} ({len(bad)} tensors)")
+        arena = trainer.engine.arena
+        assert torch.equal(arena.shadow, arena.params.to(torch.bfloat16)), f"{mode}: bf16 shadow out of sync"
         assert losses[-1][0] < losses[0][0], (mode, losses)
         results[mode] = (params, losses)
-        trainer.engine.close()
+        trainer.close()
     a, b = results["p2p"][0], results["collective"][0]
     rel = ((a - b).norm() / b.norm()).item()
     first = abs(results["p2p"][1][0][0] - results["collective"][1][0][0])
     assert first < 1e-4, f"first-step losses differ: {first}"                 # same weights, same data, before any update
     # later steps differ by bf16 / atomic-accumulation noise amplified through Newton-Schulz; a transport bug would be O(1)
     assert rel < 1e-2, f"p2p and collective transports disagree: {rel}"
+    for mode in ("ep", "ep_graph"):
+        c = results[mode][0]
+        rel_ep = ((c - b).norm() / b.norm()).item()
+        first_ep = abs(results[mode][1][0][0] - results["collective"][1][0][0])
+        assert first_ep < 1e-4, f"{mode}: first-step loss differs from the replicated-expert run: {first_ep}"
+        assert rel_ep < 1e-2, f"{mode}: expert-parallel run disagrees with the replicated-expert run: {rel_ep}"
     if rank == 0:
         print(f"MULTI_GPU_OK world={world} rel={rel:.2e} loss {results['p2p'][1][0][0]:.4f} -> {results['p2p'][1][-1][0]:.4f}", flush=True)
     dist.barrier()
