@@ -9,6 +9,10 @@ namespace q38 { std::atomic<long long> g_launches{0}; }
 TORCH_LIBRARY(q38, m) {
   m.def("launch_count() -> int", []() -> int64_t { return (int64_t)q38::g_launches.load(); });
   m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, bool a_mn_major, bool b_mn_major, float alpha, bool accumulate, Tensor(b!) err, int splits) -> ()");
+  m.def("gemm_bf16_persistent(Tensor a, Tensor b, Tensor(a!) c, bool a_mn_major, bool b_mn_major, float alpha, bool accumulate, Tensor(b!) err, int splits) -> ()",
+        [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool amn, bool bmn, double alpha, bool acc, at::Tensor& err, int64_t splits) {
+          q38::gemm_bf16_persistent(a, b, c, amn, bmn, alpha, acc, err, splits);
+        });
   m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps, bool out_bf16) -> Tensor[]");
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) -> Tensor[]");
   m.def("gated_rmsnorm_fwd(Tensor x, Tensor gate, Tensor w, float eps) -> Tensor");

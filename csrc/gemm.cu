@@ -16,6 +16,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <mutex>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "ptx.cuh"
 #include "host.h"
 
@@ -204,27 +207,52 @@ static EncodeFn encode_fn() {
 
 // 3-D tensor map {inner, rows, batch} with a 128-byte-swizzled {128 bytes, box_rows, 1} box; out-of-range elements read 0.
 static CUtensorMap make_tmap(const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
-                             int64_t batch_stride_elems, int box_rows);
+                             int64_t batch_stride_elems, int box_rows, int box_inner_bytes = 128);
 
 CUtensorMap make_tmap_bf16(const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
                            int64_t batch_stride_elems, int box_rows) {
   return make_tmap(base, 2, inner, rows, batch, row_stride_elems, batch_stride_elems, box_rows);
 }
 
+// Box of `box_rows` rows x `box_inner_bytes` (128 with the 128-byte swizzle, 64 with the 64-byte swizzle).
+CUtensorMap make_tmap_box(const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
+                          int64_t batch_stride_elems, int box_rows, int box_inner_bytes) {
+  return make_tmap(base, elem_bytes, inner, rows, batch, row_stride_elems, batch_stride_elems, box_rows, box_inner_bytes);
+}
+
 static CUtensorMap make_tmap(const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
-                             int64_t batch_stride_elems, int box_rows) {
+                             int64_t batch_stride_elems, int box_rows, int box_inner_bytes) {
+  TORCH_CHECK(box_inner_bytes == 128 || box_inner_bytes == 64, "TMA box must be 64 or 128 bytes wide");
   TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
   TORCH_CHECK((row_stride_elems * elem_bytes) % 16 == 0 && (batch <= 1 || (batch_stride_elems * elem_bytes) % 16 == 0), "TMA strides must be multiples of 16 bytes");
   TORCH_CHECK(box_rows >= 1 && box_rows <= 256, "TMA box rows out of range");
   CUtensorMap m;
   cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batch < 1 ? 1 : batch)};
   cuuint64_t strides[2] = {(cuuint64_t)row_stride_elems * elem_bytes, (cuuint64_t)(batch <= 1 ? row_stride_elems * rows : batch_stride_elems) * elem_bytes};
-  cuuint32_t box[3] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows, 1};
+  cuuint32_t box[3] = {(cuuint32_t)(box_inner_bytes / elem_bytes), (cuuint32_t)box_rows, 1};
   cuuint32_t elem[3] = {1, 1, 1};
-  CUresult r = encode_fn()(&m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  auto encode = [&] {
+    return encode_fn()(&m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, box_inner_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // A thread that has issued no runtime call yet (an autograd worker whose first op is this one) has no current context:
+    // bind the device's primary context and encode again.
+    int dev = 0;
+    C10_CUDA_CHECK(cudaGetDevice(&dev));
+    C10_CUDA_CHECK(cudaSetDevice(dev));
+    C10_CUDA_CHECK(cudaFree(nullptr));
+    r = encode();
+  }
+  if (r != CUDA_SUCCESS) {
+    char msg[384];
+    std::snprintf(msg, sizeof msg, "cuTensorMapEncodeTiled failed with code %d (base %p, dims %llu x %llu x %llu, strides %llu / %llu bytes, box %u x %u, map at %p)", (int)r, base,
+                  (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2], (unsigned long long)strides[0], (unsigned long long)strides[1], box[0], box[1], (void*)&m);
+    if (std::getenv("Q38_GEMM_TRACE")) { std::fprintf(stderr, "%s\n", msg); std::fflush(stderr); }
+    TORCH_CHECK(false, msg);
+  }
   return m;
 }
 

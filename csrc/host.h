@@ -13,10 +13,15 @@ inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_
 
 CUtensorMap make_tmap_bf16(const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
                            int64_t batch_stride_elems, int box_rows);
+CUtensorMap make_tmap_box(const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t batch, int64_t row_stride_elems,
+                          int64_t batch_stride_elems, int box_rows, int box_inner_bytes);
 
 // gemm.cu
 void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
                bool accumulate, at::Tensor& err, int64_t splits);
+
+void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
+                          bool accumulate, at::Tensor& err, int64_t splits);
 
 // elementwise.cu
 std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps, bool out_bf16);

@@ -6,11 +6,15 @@ file.  It raises when the extension is missing or the device is not a CUDA devic
 PyTorch fallback for a GPU run.  The individual wrappers below are what the optimizer and the gradient
 engine call directly.
 """
+import os
 from pathlib import Path
 
 import torch
 
 _LIB = Path(__file__).resolve().parent / "_C.so"
+# bf16 products go to the persistent kernel (one CTA per SM, epilogue overlapped with the next tile's MMAs);
+# Q38_GEMM_PERSISTENT=0 selects the one-tile-per-CTA kernel.
+PERSISTENT_GEMM = os.environ.get("Q38_GEMM_PERSISTENT", "1") != "0"
 _loaded = False
 _error_flags = {}
 
@@ -81,7 +85,10 @@ def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumula
         out3 = torch.empty(a.shape[0], M, N, dtype=out_dtype, device=a.device)
     else:
         out3 = out.unsqueeze(0) if out.dim() == 2 else out
-    ops.gemm_bf16(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
+    if PERSISTENT_GEMM and a.dtype == torch.bfloat16:
+        ops.gemm_bf16_persistent(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
+    else:
+        ops.gemm_bf16(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
     return out3[0] if squeeze else out3
 
 

@@ -393,3 +393,23 @@ def test_fused_linear_cross_entropy(ops):
         (ref * 0.37).backward()
         assert abs(loss.item() - ref.item()) < 5e-3 * abs(ref.item())
         assert rel_err(hid.grad, hr.grad) < 3e-2 and rel_err(w.grad, wr.grad) < 3e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(16384, 2240, 576), (4096, 10112, 576), (20000, 80, 200)])
+def test_gemm_persistent_many_tiles_per_cta(ops, M, N, K, monkeypatch):
+    """More tiles than SMs: the smem ring and the two TMEM accumulators wrap around several times per CTA."""
+    torch.manual_seed(11)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    monkeypatch.setattr(ops, "PERSISTENT_GEMM", True)
+    persistent = ops.gemm(a, b, out_dtype=torch.bfloat16)
+    # weight-gradient shape: both operands MN-major views with a row stride, reduction over M, split-K into a zeroed fp32 buffer
+    wgrad = torch.zeros(64, 72, device="cuda")
+    ops.gemm(a[:, :64], a[:, :72], out=wgrad, a_mn_major=True, b_mn_major=True, accumulate=True, splits=0)
+    monkeypatch.setattr(ops, "PERSISTENT_GEMM", False)
+    single = ops.gemm(a, b, out_dtype=torch.bfloat16)
+    ops.check_errors()
+    ref = a.float() @ b.float().t()
+    assert rel_err(persistent, ref) < 1e-2
+    assert torch.equal(persistent, single)
+    assert rel_err(wgrad, a[:, :64].float().t() @ a[:, :72].float()) < 1e-3
