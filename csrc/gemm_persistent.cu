@@ -34,7 +34,8 @@ struct PGemmArgs {
 // conflict free) and hands the box to the TMA unit, which writes full lines and clips rows >= M and columns >= N; with ACCUM the
 // box is added to global memory by the TMA unit (one reduction per element, so split-K partial sums need no atomics loop).
 // Two staging buffers per warp.
-template <bool A_MN, bool B_MN, typename OutT, bool ACCUM, bool TMA_OUT>
+// TF32: fp32 operands (K-major only) read by TMA and multiplied as tf32; a stage then holds 32 elements of K per row.
+template <bool A_MN, bool B_MN, typename OutT, bool ACCUM, bool TMA_OUT, bool TF32 = false>
 __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                                     const __grid_constant__ CUtensorMap tmC, PGemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           uint8_t* b_dst = a_dst + A_BYTES;
           ptx::mbar_expect_tx(&full[s], STAGE_BYTES);
-          const int k0 = (kb_begin + kb) * P_BK;
+          const int k0 = (kb_begin + kb) * (TF32 ? P_BK / 2 : P_BK);
           if (A_MN) {
 #pragma unroll
             for (int i = 0; i < P_BM / 64; ++i) ptx::tma_load_3d(a_dst + i * 8192, &tmA, &full[s], m0 + 64 * i, k0, bz);
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
     }
   } else if (warp == 1) {
     if (ptx::elect_one()) {
-      const uint32_t idesc = ptx::umma_idesc_bf16(P_BM, p.bn, A_MN, B_MN);
+      const uint32_t idesc = TF32 ? ptx::umma_idesc_tf32(P_BM, p.bn, false, false) : ptx::umma_idesc_bf16(P_BM, p.bn, A_MN, B_MN);
       uint32_t it = 0, tile = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < p.work_items && ok; w += gridDim.x, ++tile) {
@@ -123,7 +124,8 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
           for (int j = 0; j < P_BK / 16; ++j) {
             const uint64_t a_desc = A_MN ? ptx::umma_smem_desc_sw128(a_base + j * 2048, 8192, 1024) : ptx::umma_smem_desc_sw128(a_base + j * 32, 0, 1024);
             const uint64_t b_desc = B_MN ? ptx::umma_smem_desc_sw128(b_base + j * 2048, 8192, 1024) : ptx::umma_smem_desc_sw128(b_base + j * 32, 0, 1024);
-            ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0);
+            if (TF32) ptx::umma_tf32(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0);
+            else ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0);
           }
           ptx::umma_commit(&empty[s]);
         }
@@ -268,17 +270,20 @@ static int pick_splits(int tiles, int total_kb) {
   return best;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool TF32 = false>
 static void launch_p(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, bool tma_out, const PGemmArgs& p, bool out_fp32, bool accum,
                      cudaStream_t stream) {
   const int smem = P_STAGES * (P_BM * 128 + p.bn * 128) + 1024 /* alignment */ + 1024 /* barriers */ + 4 * 2 * 4096 /* output staging */;
   const int grid = std::min(p.work_items, kNumSMs);
   Q38_TRACE("[gemm_p] launch grid=%d smem=%d bn=%d items=%d splits=%d kb=%d tma_out=%d fp32=%d acc=%d amn=%d bmn=%d\n", grid, smem, p.bn, p.work_items, p.splits,
             p.total_kb, (int)tma_out, (int)out_fp32, (int)accum, (int)A_MN, (int)B_MN);
-#define Q38_LAUNCH(OutT, ACC, TMAO) { auto k = gemm_persistent_kernel<A_MN, B_MN, OutT, ACC, TMAO>; static bool cfg = false; \
+#define Q38_LAUNCH(OutT, ACC, TMAO) { auto k = gemm_persistent_kernel<A_MN, B_MN, OutT, ACC, TMAO, TF32>; static bool cfg = false; \
     if (!cfg) { C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); cfg = true; } \
     k<<<grid, P_THREADS, smem, stream>>>(ta, tb, tc, p); }
-  if (tma_out) {
+  if constexpr (TF32) {
+    if (tma_out) { if (accum) Q38_LAUNCH(float, true, true) else Q38_LAUNCH(float, false, true) }
+    else { if (accum) Q38_LAUNCH(float, true, false) else Q38_LAUNCH(float, false, false) }
+  } else if (tma_out) {
     if (!out_fp32) Q38_LAUNCH(__nv_bfloat16, false, true)
     else if (accum) Q38_LAUNCH(float, true, true)
     else Q38_LAUNCH(float, false, true)
@@ -299,8 +304,11 @@ static void launch_p(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 // Same contract as gemm_bf16 (bf16 operands only).
 void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
                           bool accumulate, at::Tensor& err, int64_t splits) {
-  TORCH_CHECK(a.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.dim() == 3 && b.dim() == 3 && c.dim() == 3,
-              "gemm_bf16_persistent: bf16 [batch, rows, cols] operands required");
+  const bool tf32 = a.scalar_type() == at::kFloat;
+  TORCH_CHECK(a.is_cuda() && (tf32 || a.scalar_type() == at::kBFloat16) && b.scalar_type() == a.scalar_type() && a.dim() == 3 && b.dim() == 3 && c.dim() == 3,
+              "gemm_bf16_persistent: bf16 (or fp32 for tf32 math) [batch, rows, cols] operands required");
+  TORCH_CHECK(!tf32 || (!a_mn_major && !b_mn_major && c.scalar_type() == at::kFloat), "gemm_bf16_persistent: the tf32 path takes K-major operands and writes fp32");
+  const int eb = tf32 ? 4 : 2, bk = 128 / eb;
   TORCH_CHECK(a.stride(2) == 1 && b.stride(2) == 1 && c.stride(2) == 1, "gemm_bf16_persistent: innermost dimension must be contiguous");
   const c10::cuda::CUDAGuard guard(a.device());
   const int batch = a.size(0);
@@ -320,7 +328,7 @@ void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& 
   PGemmArgs p{};
   p.M = M; p.N = N; p.K = K; p.batch = batch; p.bn = bn;
   p.tiles_m = (M + P_BM - 1) / P_BM; p.tiles_n = (N + bn - 1) / bn;
-  p.total_kb = (K + P_BK - 1) / P_BK;
+  p.total_kb = (K + bk - 1) / bk;
   int nsplit = 1;
   if (accumulate && out_fp32) {
     if (splits > 0) nsplit = (int)splits;
@@ -335,13 +343,15 @@ void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& 
   p.C = c.data_ptr(); p.ldc = c.stride(1); p.c_batch_stride = c.stride(0); p.alpha = (float)alpha; p.err = err.data_ptr<int>();
   CUtensorMap ta, tb;
   Q38_TRACE("[gemm_p] args bn=%d tiles=%dx%d splits=%d items=%d\n", bn, p.tiles_m, p.tiles_n, p.splits, p.work_items);
-  ta = make_tmap_bf16(a.data_ptr(), a.size(2), a.size(1), batch, a.stride(1), a.stride(0), a_mn_major ? 64 : P_BM);
+  ta = make_tmap_box(a.data_ptr(), eb, a.size(2), a.size(1), batch, a.stride(1), a.stride(0), a_mn_major ? 64 : P_BM, 128);
   Q38_TRACE("[gemm_p] map A encoded\n");
-  tb = make_tmap_bf16(b.data_ptr(), b.size(2), b.size(1), batch, b.stride(1), b.stride(0), b_mn_major ? 64 : bn);
+  tb = make_tmap_box(b.data_ptr(), eb, b.size(2), b.size(1), batch, b.stride(1), b.stride(0), b_mn_major ? 64 : bn, 128);
   Q38_TRACE("[gemm_p] operand maps encoded\n");
   CUtensorMap tc = tma_out ? make_tmap_box(c.data_ptr(), c_eb, N, M, batch, c.stride(1), c.stride(0), 32, 32 * c_eb) : ta;
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
-  if (a_mn_major) {
+  if (tf32) {
+    launch_p<false, false, true>(ta, tb, tc, tma_out, p, out_fp32, accumulate, stream);
+  } else if (a_mn_major) {
     if (b_mn_major) launch_p<true, true>(ta, tb, tc, tma_out, p, out_fp32, accumulate, stream);
     else launch_p<true, false>(ta, tb, tc, tma_out, p, out_fp32, accumulate, stream);
   } else {

@@ -312,6 +312,259 @@ __global__ void __launch_bounds__(256) mhc_pre_bwd_c_kernel(float* __restrict__ 
   }
 }
 
+
+// ---- row-in-registers variants ---------------------------------------------------------------------------------------
+// One warp per token, looping over tokens.  A lane owns the float4 columns q = lane + 32 jj (jj < NQ) of all four branches,
+// so the token's 4 x h row is loaded once with 4 NQ independent 16-byte loads per lane and every later use (mean square,
+// branch mix, gradient dot products) comes from registers.  B is kept in shared memory with a padded row (r + 1 words) so
+// that lane j reading row j is conflict free.  Used when h / 4 <= 32 NQ and r <= 96.
+constexpr int RW = 4;      // warps per CTA
+
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+template <> __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+__device__ __forceinline__ float dot4(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+
+template <int NQ>
+__device__ __forceinline__ void load_row(const float* __restrict__ Xt, int h, int h4, int lane, float4 (&x)[NB][NQ]) {
+#pragma unroll
+  for (int jj = 0; jj < NQ; ++jj) {
+    const int q = lane + 32 * jj;
+#pragma unroll
+    for (int n = 0; n < NB; ++n) x[n][jj] = q < h4 ? __ldcs(reinterpret_cast<const float4*>(Xt + n * h) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// value of element i (< 96) of a vector spread as l0 = v[lane], l1 = v[lane + 32], l2 = v[lane + 64]
+__device__ __forceinline__ float spread_get(float l0, float l1, float l2, int i) {
+  return __shfl_sync(0xffffffffu, i < 32 ? l0 : (i < 64 ? l1 : l2), i & 31);
+}
+
+template <typename OutT, int NQ>
+__global__ void __launch_bounds__(32 * RW, 4) mhc_coef_fwd_rows_kernel(const float* __restrict__ X, const float* __restrict__ Lraw, MhcParams P,
+                                                                       const float* __restrict__ norm_w, OutT* __restrict__ xout,
+                                                                       float* __restrict__ coef, float* __restrict__ zsave,
+                                                                       float* __restrict__ inv_save, float* __restrict__ rstd_save, int T, int h,
+                                                                       int r, int iters, float norm_eps) {
+  extern __shared__ float sm[];
+  const int RP = r + 1;
+  float* Bs = sm;                               // [24][r + 1]
+  for (int i = threadIdx.x; i < NCOEF * r; i += blockDim.x) Bs[(i / r) * RP + i % r] = P.Bw[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, h4 = h >> 2;
+  const float* Brow = Bs + min(lane, NCOEF - 1) * RP;
+  for (int t = blockIdx.x * RW + warp; t < T; t += gridDim.x * RW) {
+    const float* Xt = X + (size_t)t * NB * h;
+    float4 x[NB][NQ];
+    load_row<NQ>(Xt, h, h4, lane, x);
+    const float* Lt = Lraw + (size_t)t * r;
+    const float l0 = lane < r ? Lt[lane] : 0.f, l1 = lane + 32 < r ? Lt[lane + 32] : 0.f, l2 = lane + 64 < r ? Lt[lane + 64] : 0.f;
+    float ss = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < NQ; ++jj)
+#pragma unroll
+      for (int n = 0; n < NB; ++n) ss += dot4(x[n][jj], x[n][jj]);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (NB * h) + 1e-6f);
+    float acc = 0.f;
+    for (int i = 0; i < r; ++i) acc += Brow[i] * spread_get(l0, l1, l2, i);
+    float z = 0.f;
+    if (lane < NCOEF) {
+      z = tanhf(acc * inv);
+      zsave[(size_t)t * NCOEF + lane] = z;
+    }
+    float c = 0.f;
+    if (lane < 4) c = sigmoidf_(P.b_pre[lane] + P.alphas[0] * z);
+    else if (lane < 8) c = 2.f * sigmoidf_(P.b_post[lane - 4] + P.alphas[1] * z);
+    const float zr = __shfl_sync(0xffffffffu, z, (lane & 15) + 8);
+    float res = 0.f;
+    if (lane < 16) res = sinkhorn_fwd(P.b_res[lane] + P.alphas[2] * zr, iters, nullptr, nullptr, false);
+    if (lane < 8) coef[(size_t)t * NCOEF + lane] = c;
+    if (lane < 16) coef[(size_t)t * NCOEF + 8 + lane] = res;
+    const float p0 = __shfl_sync(0xffffffffu, c, 0), p1 = __shfl_sync(0xffffffffu, c, 1), p2 = __shfl_sync(0xffffffffu, c, 2),
+                p3 = __shfl_sync(0xffffffffu, c, 3);
+    float4 v[NQ];
+    float ss2 = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < NQ; ++jj) {
+      v[jj] = make_float4(p0 * x[0][jj].x + p1 * x[1][jj].x + p2 * x[2][jj].x + p3 * x[3][jj].x,
+                          p0 * x[0][jj].y + p1 * x[1][jj].y + p2 * x[2][jj].y + p3 * x[3][jj].y,
+                          p0 * x[0][jj].z + p1 * x[1][jj].z + p2 * x[2][jj].z + p3 * x[3][jj].z,
+                          p0 * x[0][jj].w + p1 * x[1][jj].w + p2 * x[2][jj].w + p3 * x[3][jj].w);
+      ss2 += dot4(v[jj], v[jj]);
+    }
+    ss2 = warp_sum(ss2);
+    const float rstd = rsqrtf(ss2 / h + norm_eps);
+    if (lane == 0) { inv_save[t] = inv; rstd_save[t] = rstd; }
+    OutT* xo = xout + (size_t)t * h;
+#pragma unroll
+    for (int jj = 0; jj < NQ; ++jj) {
+      const int q = lane + 32 * jj;
+      if (q < h4) {
+        const float4 nw = load4<float>(norm_w + 4 * q);
+        store4(xo + 4 * q, make_float4(v[jj].x * rstd * (1.f + nw.x), v[jj].y * rstd * (1.f + nw.y), v[jj].z * rstd * (1.f + nw.z), v[jj].w * rstd * (1.f + nw.w)));
+      }
+    }
+  }
+}
+
+// Part A of the pre backward on register rows.  Instead of accumulating dB in shared memory it writes dlin [T,24]; dB is the
+// product dlin^T (inv L_raw), formed by mhc_dB_kernel.  d(norm weight) is accumulated per lane across the warp's tokens.
+template <typename GT, int NQ>
+__global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_a_rows_kernel(const GT* __restrict__ dxout, const float* __restrict__ X,
+                                                                        const float* __restrict__ Lraw, MhcParams P, const float* __restrict__ norm_w,
+                                                                        const float* __restrict__ coef, const float* __restrict__ zsave,
+                                                                        const float* __restrict__ inv_save, const float* __restrict__ rstd_save,
+                                                                        float* __restrict__ dcoef, float* __restrict__ dLraw, float* __restrict__ c1_out,
+                                                                        float* __restrict__ dxin_out, float* __restrict__ dlin_out,
+                                                                        float* __restrict__ dbias, float* __restrict__ dnorm_w, int T, int h, int r, int iters) {
+  extern __shared__ float sm[];
+  const int RP = r + 1;
+  float* Bs = sm;                      // [24][r + 1]
+  float* dnw_s = Bs + NCOEF * RP;      // [h]
+  float* dbias_s = dnw_s + h;          // [32]
+  for (int i = threadIdx.x; i < NCOEF * r; i += blockDim.x) Bs[(i / r) * RP + i % r] = P.Bw[i];
+  for (int i = threadIdx.x; i < h; i += blockDim.x) dnw_s[i] = 0.f;
+  if (threadIdx.x < 32) dbias_s[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, h4 = h >> 2;
+  float4 dnw[NQ];
+#pragma unroll
+  for (int jj = 0; jj < NQ; ++jj) dnw[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+  float db = 0.f, da = 0.f;
+  const float alpha = lane < 4 ? P.alphas[0] : lane < 8 ? P.alphas[1] : P.alphas[2];
+  for (int t = blockIdx.x * RW + warp; t < T; t += gridDim.x * RW) {
+    const float* Xt = X + (size_t)t * NB * h;
+    float4 x[NB][NQ];
+    load_row<NQ>(Xt, h, h4, lane, x);
+    const float cv = lane < NCOEF ? coef[(size_t)t * NCOEF + lane] : 0.f;
+    const float p0 = __shfl_sync(0xffffffffu, cv, 0), p1 = __shfl_sync(0xffffffffu, cv, 1), p2 = __shfl_sync(0xffffffffu, cv, 2),
+                p3 = __shfl_sync(0xffffffffu, cv, 3);
+    const float rstd = rstd_save[t], inv = inv_save[t];
+    const GT* gt = dxout + (size_t)t * h;
+    float4 g[NQ];          // dxout (1 + w)
+    float dot = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < NQ; ++jj) {
+      const int q = lane + 32 * jj;
+      g[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (q < h4) {
+        const float4 gv = load4<GT>(gt + 4 * q), nw = load4<float>(norm_w + 4 * q);
+        const float4 xh = make_float4(rstd * (p0 * x[0][jj].x + p1 * x[1][jj].x + p2 * x[2][jj].x + p3 * x[3][jj].x),
+                                      rstd * (p0 * x[0][jj].y + p1 * x[1][jj].y + p2 * x[2][jj].y + p3 * x[3][jj].y),
+                                      rstd * (p0 * x[0][jj].z + p1 * x[1][jj].z + p2 * x[2][jj].z + p3 * x[3][jj].z),
+                                      rstd * (p0 * x[0][jj].w + p1 * x[1][jj].w + p2 * x[2][jj].w + p3 * x[3][jj].w));
+        dnw[jj].x += gv.x * xh.x; dnw[jj].y += gv.y * xh.y; dnw[jj].z += gv.z * xh.z; dnw[jj].w += gv.w * xh.w;
+        g[jj] = make_float4(gv.x * (1.f + nw.x), gv.y * (1.f + nw.y), gv.z * (1.f + nw.z), gv.w * (1.f + nw.w));
+        dot += dot4(g[jj], xh);
+      }
+    }
+    dot = warp_sum(dot) / h;
+    float dpre[NB] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int jj = 0; jj < NQ; ++jj) {
+      const int q = lane + 32 * jj;
+      if (q < h4) {
+        const float4 xh = make_float4(rstd * (p0 * x[0][jj].x + p1 * x[1][jj].x + p2 * x[2][jj].x + p3 * x[3][jj].x),
+                                      rstd * (p0 * x[0][jj].y + p1 * x[1][jj].y + p2 * x[2][jj].y + p3 * x[3][jj].y),
+                                      rstd * (p0 * x[0][jj].z + p1 * x[1][jj].z + p2 * x[2][jj].z + p3 * x[3][jj].z),
+                                      rstd * (p0 * x[0][jj].w + p1 * x[1][jj].w + p2 * x[2][jj].w + p3 * x[3][jj].w));
+        const float4 dxin = make_float4(rstd * (g[jj].x - xh.x * dot), rstd * (g[jj].y - xh.y * dot), rstd * (g[jj].z - xh.z * dot), rstd * (g[jj].w - xh.w * dot));
+        store4(dxin_out + (size_t)t * h + 4 * q, dxin);
+#pragma unroll
+        for (int n = 0; n < NB; ++n) dpre[n] += dot4(dxin, x[n][jj]);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NB; ++n) dpre[n] = warp_sum(dpre[n]);
+    // coefficient backward, lane j < 24 owns logit j
+    const float z = lane < NCOEF ? zsave[(size_t)t * NCOEF + lane] : 0.f;
+    float dlogit = 0.f;
+    if (lane < 4) {
+      const float dp = lane == 0 ? dpre[0] : lane == 1 ? dpre[1] : lane == 2 ? dpre[2] : dpre[3];
+      dcoef[(size_t)t * NCOEF + lane] = dp;
+      dlogit = dp * cv * (1.f - cv);
+    } else if (lane < 8) {
+      dlogit = dcoef[(size_t)t * NCOEF + lane] * cv * (1.f - 0.5f * cv);      // post = 2 sigmoid
+    }
+    float dres_logit = 0.f;
+    {
+      const float zr = __shfl_sync(0xffffffffu, z, (lane & 15) + 8);
+      float Y[2 * MAX_SINKHORN], S[2 * MAX_SINKHORN];
+      if (lane < 16) {
+        const float logit = P.b_res[lane] + P.alphas[2] * zr;
+        sinkhorn_fwd(logit, iters, Y, S, true);
+        dres_logit = sinkhorn_bwd(dcoef[(size_t)t * NCOEF + 8 + lane], logit, iters, Y, S);
+      }
+    }
+    const float moved = __shfl_sync(0xffffffffu, dres_logit, (lane + 24) & 31);   // lane j gets lane j - 8
+    if (lane >= 8 && lane < NCOEF) dlogit = moved;
+    if (lane < NCOEF) { db += dlogit; da += dlogit * z; }
+    const float dlin = lane < NCOEF ? dlogit * alpha * (1.f - z * z) : 0.f;
+    if (lane < NCOEF) dlin_out[(size_t)t * NCOEF + lane] = dlin;
+    // dL_i = sum_j B[j,i] dlin_j ;  dLraw_i = inv dL_i ;  dinv = sum_i dL_i Lraw_i
+    const float* Lt = Lraw + (size_t)t * r;
+    const int i0 = min(lane, r - 1), i1 = min(lane + 32, r - 1), i2 = min(lane + 64, r - 1);
+    float dl0 = 0.f, dl1 = 0.f, dl2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCOEF; ++j) {
+      const float dj = __shfl_sync(0xffffffffu, dlin, j);
+      dl0 += Bs[j * RP + i0] * dj;
+      dl1 += Bs[j * RP + i1] * dj;
+      dl2 += Bs[j * RP + i2] * dj;
+    }
+    float dinv = 0.f;
+    if (lane < r) { dLraw[(size_t)t * r + lane] = inv * dl0; dinv += dl0 * Lt[lane]; }
+    if (lane + 32 < r) { dLraw[(size_t)t * r + lane + 32] = inv * dl1; dinv += dl1 * Lt[lane + 32]; }
+    if (lane + 64 < r) { dLraw[(size_t)t * r + lane + 64] = inv * dl2; dinv += dl2 * Lt[lane + 64]; }
+    dinv = warp_sum(dinv);
+    if (lane == 0) c1_out[t] = -dinv * inv * inv * inv / (NB * h);
+  }
+#pragma unroll
+  for (int jj = 0; jj < NQ; ++jj) {
+    const int q = lane + 32 * jj;
+    if (q < h4) {
+      atomicAdd(&dnw_s[4 * q], dnw[jj].x); atomicAdd(&dnw_s[4 * q + 1], dnw[jj].y);
+      atomicAdd(&dnw_s[4 * q + 2], dnw[jj].z); atomicAdd(&dnw_s[4 * q + 3], dnw[jj].w);
+    }
+  }
+  if (lane < NCOEF) {
+    atomicAdd(&dbias_s[lane], db);
+    atomicAdd(&dbias_s[24 + (lane < 4 ? 0 : lane < 8 ? 1 : 2)], da);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < h; i += blockDim.x) atomicAdd(&dnorm_w[i], dnw_s[i]);
+  if (threadIdx.x < 27) atomicAdd(&dbias[threadIdx.x], dbias_s[threadIdx.x]);
+}
+
+// dB[j,i] += sum_t dlin[t,j] inv_t Lraw[t,i] over a slab of tokens per CTA.
+constexpr int DB_TOK = 64;
+__global__ void __launch_bounds__(256) mhc_dB_kernel(const float* __restrict__ dlin, const float* __restrict__ Lraw, const float* __restrict__ inv,
+                                                     float* __restrict__ dBw, int T, int r) {
+  extern __shared__ float sm[];
+  float* dl_s = sm;                    // [DB_TOK][24]
+  float* l_s = sm + DB_TOK * NCOEF;    // [DB_TOK][r]
+  const int t0 = blockIdx.x * DB_TOK, nt = min(DB_TOK, T - t0);
+  for (int i = threadIdx.x; i < nt * NCOEF; i += blockDim.x) dl_s[i] = dlin[(size_t)t0 * NCOEF + i];
+  for (int i = threadIdx.x; i < nt * r; i += blockDim.x) l_s[i] = Lraw[(size_t)t0 * r + i] * inv[t0 + i / r];
+  __syncthreads();
+  for (int o = threadIdx.x; o < NCOEF * r; o += blockDim.x) {
+    const int j = o / r, i = o % r;
+    float acc = 0.f;
+    for (int t = 0; t < nt; ++t) acc += dl_s[t * NCOEF + j] * l_s[t * r + i];
+    atomicAdd(&dBw[o], acc);
+  }
+}
+
 // ---- host wrappers -------------------------------------------------------------------------------------------------------
 static MhcParams params_of(const at::Tensor& Bw, const at::Tensor& b_pre, const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas) {
   return MhcParams{Bw.data_ptr<float>(), b_pre.data_ptr<float>(), b_post.data_ptr<float>(), b_res.data_ptr<float>(), alphas.data_ptr<float>()};
@@ -328,10 +581,25 @@ std::vector<at::Tensor> mhc_coef_fwd(const at::Tensor& X, const at::Tensor& Lraw
   auto f32 = X.options();
   auto xout = at::empty({T, h}, f32.dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
   auto coef = at::empty({T, NCOEF}, f32), z = at::empty({T, NCOEF}, f32), inv = at::empty({T}, f32), rstd = at::empty({T}, f32);
-  const size_t smem = (NCOEF * r + WARPS * h) * sizeof(float);
   auto stream = at::cuda::getCurrentCUDAStream();
-  const int grid = (T + WARPS - 1) / WARPS;
   MhcParams P = params_of(Bw, b_pre, b_post, b_res, alphas);
+  const int nq = (h / 4 + 31) / 32;
+  if (r <= 96 && nq <= 8) {
+    const size_t smem = NCOEF * (r + 1) * sizeof(float);
+    const int grid = std::min((T + RW - 1) / RW, 4 * kNumSMs);
+#define Q38_ROWS(OutT, NQ) mhc_coef_fwd_rows_kernel<OutT, NQ><<<grid, 32 * RW, smem, stream>>>(X.data_ptr<float>(), Lraw.data_ptr<float>(), P, norm_w.data_ptr<float>(), \
+      (OutT*)xout.data_ptr(), coef.data_ptr<float>(), z.data_ptr<float>(), inv.data_ptr<float>(), rstd.data_ptr<float>(), T, h, r, (int)iters, (float)norm_eps)
+#define Q38_ROWS_NQ(OutT) switch (nq) { case 1: Q38_ROWS(OutT, 1); break; case 2: Q38_ROWS(OutT, 2); break; case 3: Q38_ROWS(OutT, 3); break; case 4: Q38_ROWS(OutT, 4); break; \
+      case 5: Q38_ROWS(OutT, 5); break; case 6: Q38_ROWS(OutT, 6); break; default: Q38_ROWS(OutT, 8); break; }
+    if (out_bf16) Q38_ROWS_NQ(__nv_bfloat16) else Q38_ROWS_NQ(float)
+#undef Q38_ROWS_NQ
+#undef Q38_ROWS
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    return {xout, coef, z, inv, rstd};
+  }
+  const size_t smem = (NCOEF * r + WARPS * h) * sizeof(float);
+  const int grid = (T + WARPS - 1) / WARPS;
   if (out_bf16) {
     auto k = mhc_coef_fwd_kernel<__nv_bfloat16>;
     C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
@@ -394,10 +662,31 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
   auto f32 = X.options();
   auto dLraw = at::empty({T, r}, f32), c1 = at::empty({T}, f32), dxin = at::empty({T, h}, f32);
   auto dBw = at::zeros({NCOEF, r}, f32), dbias = at::zeros({27}, f32), dnw = at::zeros({h}, f32);
-  const size_t smem = (2 * NCOEF * r + h + 32 + WARPS * h + WARPS * NCOEF) * sizeof(float);
   auto stream = at::cuda::getCurrentCUDAStream();
-  const int grid = (T + WARPS - 1) / WARPS;
   MhcParams P = params_of(Bw, b_pre, b_post, b_res, alphas);
+  const int nq = (h / 4 + 31) / 32;
+  if (h % 4 == 0 && r <= 96 && nq <= 8) {
+    auto dlin = at::empty({T, NCOEF}, f32);
+    const size_t smem_r = (NCOEF * (r + 1) + h + 32) * sizeof(float);
+    const int grid_r = std::min((T + RW - 1) / RW, 3 * kNumSMs);
+#define Q38_ROWS(GT, NQ) mhc_pre_bwd_a_rows_kernel<GT, NQ><<<grid_r, 32 * RW, smem_r, stream>>>((const GT*)dxout.data_ptr(), X.data_ptr<float>(), Lraw.data_ptr<float>(), P, \
+      norm_w.data_ptr<float>(), coef.data_ptr<float>(), z.data_ptr<float>(), inv.data_ptr<float>(), rstd.data_ptr<float>(), dcoef.data_ptr<float>(), dLraw.data_ptr<float>(), \
+      c1.data_ptr<float>(), dxin.data_ptr<float>(), dlin.data_ptr<float>(), dbias.data_ptr<float>(), dnw.data_ptr<float>(), T, h, r, (int)iters)
+#define Q38_ROWS_NQ(GT) switch (nq) { case 1: Q38_ROWS(GT, 1); break; case 2: Q38_ROWS(GT, 2); break; case 3: Q38_ROWS(GT, 3); break; case 4: Q38_ROWS(GT, 4); break; \
+      case 5: Q38_ROWS(GT, 5); break; case 6: Q38_ROWS(GT, 6); break; default: Q38_ROWS(GT, 8); break; }
+    if (dxout.scalar_type() == at::kBFloat16) Q38_ROWS_NQ(__nv_bfloat16) else Q38_ROWS_NQ(float)
+#undef Q38_ROWS_NQ
+#undef Q38_ROWS
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    mhc_dB_kernel<<<(T + DB_TOK - 1) / DB_TOK, 256, DB_TOK * (NCOEF + r) * sizeof(float), stream>>>(dlin.data_ptr<float>(), Lraw.data_ptr<float>(), inv.data_ptr<float>(),
+                                                                                                  dBw.data_ptr<float>(), T, r);
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    return {dLraw, c1, dxin, dBw, dbias, dnw};
+  }
+  const size_t smem = (2 * NCOEF * r + h + 32 + WARPS * h + WARPS * NCOEF) * sizeof(float);
+  const int grid = (T + WARPS - 1) / WARPS;
 #define LAUNCH(GT) { auto k = mhc_pre_bwd_a_kernel<GT>; \
     C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
     k<<<grid, 32 * WARPS, smem, stream>>>((const GT*)dxout.data_ptr(), X.data_ptr<float>(), Lraw.data_ptr<float>(), P, norm_w.data_ptr<float>(), \

@@ -85,7 +85,7 @@ def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumula
         out3 = torch.empty(a.shape[0], M, N, dtype=out_dtype, device=a.device)
     else:
         out3 = out.unsqueeze(0) if out.dim() == 2 else out
-    if PERSISTENT_GEMM and a.dtype == torch.bfloat16:
+    if PERSISTENT_GEMM:
         ops.gemm_bf16_persistent(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
     else:
         ops.gemm_bf16(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
