@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(128) qsa_attn_bwd_q_kernel(const bf16* __restr
 
 __global__ void __launch_bounds__(128) qsa_attn_bwd_kv_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                                                               const bf16* __restrict__ dout, const float* __restrict__ lse, const float* __restrict__ Din,
-                                                              const unsigned char* __restrict__ sel, bf16* __restrict__ dk, bf16* __restrict__ dv,
+                                                              const unsigned char* __restrict__ sel, float* __restrict__ dk, float* __restrict__ dv,
                                                               int S, int nq, int nkv, float scale) {
   extern __shared__ __align__(16) uint8_t smem_bytes[];
   bf16* Ks = reinterpret_cast<bf16*>(smem_bytes);
@@ -206,7 +206,9 @@ __global__ void __launch_bounds__(128) qsa_attn_bwd_kv_kernel(const bf16* __rest
   bf16* Ps = dOs + TILE_ELEMS;
   bf16* dSs = Ps + TILE_ELEMS;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int j = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, nb = S / 64, rep = nq / nkv;
+  // One CTA per (key block, query head, batch): the key blocks near the start of the sequence are selected by almost every
+  // later query block, so the work of a key block is spread over the heads of its group; partial dK / dV are added in fp32.
+  const int j = blockIdx.x, h = blockIdx.y, b = blockIdx.z, nb = S / 64, rep = nq / nkv, kvh = h / rep;
   load_tile_async(Ks, k + (((long long)b * nkv + kvh) * S + (long long)j * 64) * 64, 64, tid);
   load_tile_async(Vs, v + (((long long)b * nkv + kvh) * S + (long long)j * 64) * 64, 64, tid);
   cp_async_commit();
@@ -217,8 +219,7 @@ __global__ void __launch_bounds__(128) qsa_attn_bwd_kv_kernel(const bf16* __rest
   zero_acc(dV);
   for (int i = j; i < nb; ++i) {
     if (!sel[((long long)b * nb + i) * nb + j]) continue;
-    for (int hh = 0; hh < rep; ++hh) {
-      const int h = kvh * rep + hh;
+    {
       __syncthreads();
       load_tile_async(Qs, q + (((long long)b * nq + h) * S + (long long)i * 64) * 64, 64, tid);
       load_tile_async(dOs, dout + (((long long)b * S + (long long)i * 64) * nq + h) * 64, ld_tok, tid);
@@ -254,8 +255,16 @@ __global__ void __launch_bounds__(128) qsa_attn_bwd_kv_kernel(const bf16* __rest
     }
   }
   cp_async_wait<0>();
-  acc_to_global(dK, dk + (((long long)b * nkv + kvh) * S + (long long)j * 64) * 64, 64, warp, lane);
-  acc_to_global(dV, dv + (((long long)b * nkv + kvh) * S + (long long)j * 64) * 64, 64, warp, lane);
+  float* dkp = dk + (((long long)b * nkv + kvh) * S + (long long)j * 64) * 64;
+  float* dvp = dv + (((long long)b * nkv + kvh) * S + (long long)j * 64) * 64;
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int row = r0 + 8 * (e >> 1), col = 8 * nt + cq + (e & 1);
+      atomicAdd(dkp + row * 64 + col, dK[nt][e]);
+      atomicAdd(dvp + row * 64 + col, dV[nt][e]);
+    }
 }
 
 // ---- host ----------------------------------------------------------------------------------------------------------------------
@@ -302,7 +311,8 @@ std::vector<at::Tensor> qsa_attn_bwd(const at::Tensor& q, const at::Tensor& k, c
   TORCH_CHECK(dout.is_contiguous() && dout.scalar_type() == at::kBFloat16 && o.is_contiguous(), "qsa_attn_bwd: contiguous bf16 dO/o [B,S,nq,64] required");
   const c10::cuda::CUDAGuard guard(q.device());
   const int B = q.size(0), nq = q.size(1), S = q.size(2), nkv = k.size(1), nb = S / 64;
-  auto dq = at::empty_like(q), dk = at::empty_like(k), dv = at::empty_like(v);
+  auto dq = at::empty_like(q);
+  auto dk32 = at::zeros(k.sizes(), k.options().dtype(at::kFloat)), dv32 = at::zeros(v.sizes(), v.options().dtype(at::kFloat));
   auto D = at::empty({B, nq, S}, q.options().dtype(at::kFloat));
   auto stream = at::cuda::getCurrentCUDAStream();
   const int smem_q = 5 * TILE_ELEMS * 2, smem_kv = 6 * TILE_ELEMS * 2;
@@ -315,12 +325,12 @@ std::vector<at::Tensor> qsa_attn_bwd(const at::Tensor& q, const at::Tensor& k, c
   qsa_attn_bwd_q_kernel<<<dim3(nb, nq, B), 128, smem_q, stream>>>((const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(), (const bf16*)v.data_ptr(),
       (const bf16*)o.data_ptr(), (const bf16*)dout.data_ptr(), lse.data_ptr<float>(), sel.data_ptr<unsigned char>(), (bf16*)dq.data_ptr(), D.data_ptr<float>(),
       S, nq, nkv, (float)scale);
-  qsa_attn_bwd_kv_kernel<<<dim3(nb, nkv, B), 128, smem_kv, stream>>>((const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(), (const bf16*)v.data_ptr(),
-      (const bf16*)dout.data_ptr(), lse.data_ptr<float>(), D.data_ptr<float>(), sel.data_ptr<unsigned char>(), (bf16*)dk.data_ptr(), (bf16*)dv.data_ptr(),
+  qsa_attn_bwd_kv_kernel<<<dim3(nb, nq, B), 128, smem_kv, stream>>>((const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(), (const bf16*)v.data_ptr(),
+      (const bf16*)dout.data_ptr(), lse.data_ptr<float>(), D.data_ptr<float>(), sel.data_ptr<unsigned char>(), dk32.data_ptr<float>(), dv32.data_ptr<float>(),
       S, nq, nkv, (float)scale);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch(2);
-  return {dq, dk, dv};
+  return {dq, dk32.to(at::kBFloat16), dv32.to(at::kBFloat16)};
 }
 
 }  // namespace q38

@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(128) qsa_main_block_stats_kernel(const bf16* _
   bf16* Qs = reinterpret_cast<bf16*>(smem_bytes);
   bf16* Ks = Qs + TILE_ELEMS;                      // two buffers
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z, nb = S / 64;
+  const int nb = S / 64, i = nb - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;     // late query blocks (longest loops) first
   const bf16* qsrc = q + (((long long)b * nq + h) * S + (long long)i * 64) * 64;
   const bf16* kbase = k + ((long long)b * nkv + h / (nq / nkv)) * S * 64;
   load_tile_async(Qs, qsrc, 64, tid);
@@ -99,19 +99,22 @@ __global__ void __launch_bounds__(128) qsa_indexer_fwd_kernel(const bf16* __rest
   bf16* Qs = reinterpret_cast<bf16*>(smem_bytes);          // NI tiles
   bf16* Ks = Qs + NI_MAX * TILE_ELEMS;                     // two buffers
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int i = blockIdx.x, b = blockIdx.y, nb = S / 64;
+  // Query block i scores key blocks j <= i; late query blocks (most work) are issued first and the key loop of a query block is
+  // shared by gridDim.z CTAs (j = z, z + gridDim.z, ...), each writing its own columns of blse.
+  const int nb = S / 64, i = nb - 1 - blockIdx.x, b = blockIdx.y, jstep = gridDim.z;
+  if ((int)blockIdx.z > i) return;
   for (int hh = 0; hh < NI; ++hh) load_tile_async(Qs + hh * TILE_ELEMS, qi + (((long long)b * NI + hh) * S + (long long)i * 64) * 64, 64, tid);
   const bf16* kbase = ki + (long long)b * S * 64;
-  load_tile_async(Ks, kbase, 64, tid);
+  load_tile_async(Ks, kbase + (long long)blockIdx.z * 4096, 64, tid);
   cp_async_commit();
   const int r0 = 16 * warp + (lane >> 2);
   float wrow[2][NI_MAX];
 #pragma unroll
   for (int hrow = 0; hrow < 2; ++hrow)
     for (int hh = 0; hh < NI; ++hh) wrow[hrow][hh] = wi[((long long)b * S + (long long)i * 64 + r0 + 8 * hrow) * NI + hh] * scale;
-  for (int j = 0; j <= i; ++j) {
-    const int buf = j & 1;
-    if (j < i) { load_tile_async(Ks + (buf ^ 1) * TILE_ELEMS, kbase + (long long)(j + 1) * 4096, 64, tid); cp_async_commit(); cp_async_wait<1>(); }
+  int buf = 0;
+  for (int j = blockIdx.z; j <= i; j += jstep, buf ^= 1) {
+    if (j + jstep <= i) { load_tile_async(Ks + (buf ^ 1) * TILE_ELEMS, kbase + (long long)(j + jstep) * 4096, 64, tid); cp_async_commit(); cp_async_wait<1>(); }
     else cp_async_wait<0>();
     __syncthreads();
     float score[8][4];
@@ -280,7 +283,7 @@ __global__ void __launch_bounds__(128) qsa_indexer_bwd_q_kernel(const bf16* __re
   bf16* Ks = Qs + NI_MAX * TILE_ELEMS;                     // two buffers
   bf16* Ts = Ks + 2 * TILE_ELEMS;                          // dS_own tile (bf16) as A operand
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int i = blockIdx.x, own = blockIdx.y, b = blockIdx.z, nb = S / 64;
+  const int nb = S / 64, i = nb - 1 - blockIdx.x, own = blockIdx.y, b = blockIdx.z;   // late query blocks (longest loops) first
   for (int hh = 0; hh < NI; ++hh) load_tile_async(Qs + hh * TILE_ELEMS, qi + (((long long)b * NI + hh) * S + (long long)i * 64) * 64, 64, tid);
   const bf16* kbase = ki + (long long)b * S * 64;
   load_tile_async(Ks, kbase, 64, tid);
@@ -330,19 +333,22 @@ __global__ void __launch_bounds__(128) qsa_indexer_bwd_q_kernel(const bf16* __re
 // Key pass, grid (nb, B): d k(s) = sum_{t >= s} sum_h dS_h[t,s] q_h(t), looping over query blocks i >= j.
 __global__ void __launch_bounds__(128) qsa_indexer_bwd_k_kernel(const bf16* __restrict__ qi, const bf16* __restrict__ ki, const float* __restrict__ wi,
                                                                 const float* __restrict__ blse, const float* __restrict__ dblse, float gscale,
-                                                                bf16* __restrict__ dki, int S, int NI, float scale) {
+                                                                float* __restrict__ dki, int S, int NI, float scale) {
   extern __shared__ __align__(16) uint8_t smem_bytes[];
   bf16* Ks = reinterpret_cast<bf16*>(smem_bytes);
   bf16* Qs = Ks + TILE_ELEMS;                              // NI tiles of the current query block
   bf16* Ts = Qs + NI_MAX * TILE_ELEMS;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Key block j is scored by every query block i >= j: the loop is shared by gridDim.z CTAs (i = j + z, j + z + gridDim.z, ...)
+  // whose partial gradients are added in fp32.
   const int j = blockIdx.x, b = blockIdx.y, nb = S / 64;
+  if (j + (int)blockIdx.z >= nb) return;
   load_tile_async(Ks, ki + ((long long)b * S + (long long)j * 64) * 64, 64, tid);
   cp_async_commit();
   const int r0 = 16 * warp + (lane >> 2);
   float dk[8][4];
   zero_acc(dk);
-  for (int i = j; i < nb; ++i) {
+  for (int i = j + blockIdx.z; i < nb; i += gridDim.z) {
     __syncthreads();
     for (int hh = 0; hh < NI; ++hh) load_tile_async(Qs + hh * TILE_ELEMS, qi + (((long long)b * NI + hh) * S + (long long)i * 64) * 64, 64, tid);
     cp_async_commit();
@@ -371,7 +377,12 @@ __global__ void __launch_bounds__(128) qsa_indexer_bwd_k_kernel(const bf16* __re
       mma64<true, false>(Ts, Qs + hh * TILE_ELEMS, dk, warp, lane);           // dS_h^T Q_h
     }
   }
-  acc_to_global(dk, dki + ((long long)b * S + (long long)j * 64) * 64, 64, warp, lane);
+  float* dst = dki + ((long long)b * S + (long long)j * 64) * 64;
+  const int cq = 2 * (lane & 3);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) atomicAdd(dst + (r0 + 8 * (e >> 1)) * 64 + 8 * nt + cq + (e & 1), dk[nt][e]);
 }
 
 // ---- host ----------------------------------------------------------------------------------------------------------------------
@@ -406,7 +417,7 @@ at::Tensor qsa_indexer_fwd(const at::Tensor& qi, const at::Tensor& ki, const at:
   const int smem = (NI_MAX + 2) * TILE_ELEMS * 2;
   static bool cfg = false;
   if (!cfg) { C10_CUDA_CHECK(cudaFuncSetAttribute(qsa_indexer_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); cfg = true; }
-  qsa_indexer_fwd_kernel<<<dim3(nb, B), 128, smem, at::cuda::getCurrentCUDAStream()>>>((const bf16*)qi.data_ptr(), (const bf16*)ki.data_ptr(), wi.data_ptr<float>(),
+  qsa_indexer_fwd_kernel<<<dim3(nb, B, std::min(nb, 4)), 128, smem, at::cuda::getCurrentCUDAStream()>>>((const bf16*)qi.data_ptr(), (const bf16*)ki.data_ptr(), wi.data_ptr<float>(),
       blse.data_ptr<float>(), S, NI, (float)scale);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch(2);
@@ -451,7 +462,8 @@ std::vector<at::Tensor> qsa_indexer_bwd(const at::Tensor& qi, const at::Tensor& 
                                         double gscale, double scale) {
   const c10::cuda::CUDAGuard guard(qi.device());
   const int B = qi.size(0), NI = qi.size(1), S = qi.size(2), nb = S / 64;
-  auto dqi = at::empty_like(qi), dki = at::empty_like(ki);
+  auto dqi = at::empty_like(qi);
+  auto dki32 = at::zeros(ki.sizes(), ki.options().dtype(at::kFloat));
   auto dwi = at::empty_like(wi);
   const int smem = (NI_MAX + 3) * TILE_ELEMS * 2;
   static bool cfg = false;
@@ -463,11 +475,11 @@ std::vector<at::Tensor> qsa_indexer_bwd(const at::Tensor& qi, const at::Tensor& 
   auto stream = at::cuda::getCurrentCUDAStream();
   qsa_indexer_bwd_q_kernel<<<dim3(nb, NI, B), 128, smem, stream>>>((const bf16*)qi.data_ptr(), (const bf16*)ki.data_ptr(), wi.data_ptr<float>(), blse.data_ptr<float>(),
       dblse.data_ptr<float>(), (float)gscale, (bf16*)dqi.data_ptr(), dwi.data_ptr<float>(), S, NI, (float)scale);
-  qsa_indexer_bwd_k_kernel<<<dim3(nb, B), 128, smem, stream>>>((const bf16*)qi.data_ptr(), (const bf16*)ki.data_ptr(), wi.data_ptr<float>(), blse.data_ptr<float>(),
-      dblse.data_ptr<float>(), (float)gscale, (bf16*)dki.data_ptr(), S, NI, (float)scale);
+  qsa_indexer_bwd_k_kernel<<<dim3(nb, B, std::min(nb, 8)), 128, smem, stream>>>((const bf16*)qi.data_ptr(), (const bf16*)ki.data_ptr(), wi.data_ptr<float>(),
+      blse.data_ptr<float>(), dblse.data_ptr<float>(), (float)gscale, dki32.data_ptr<float>(), S, NI, (float)scale);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch(2);
-  return {dqi, dki, dwi};
+  return {dqi, dki32.to(at::kBFloat16), dwi};
 }
 
 }  // namespace q38

@@ -88,6 +88,19 @@ class _GatedRMSNorm(torch.autograd.Function):
         return dx, dgate, dw.to(weight.dtype), None
 
 
+def _tma_rows(t):
+    """A 2-D tensor whose row stride TMA accepts (a multiple of 16 bytes).  A narrow matrix, e.g. the [tokens, 21] gradient of a
+    per-head gate projection, is copied into a buffer with padded rows and returned as a view of it; the tensor map still
+    describes the true width, so the padding is never read."""
+    n, per16 = t.shape[1], 16 // t.element_size()
+    if n % per16 == 0 and t.is_contiguous():
+        return t
+    buf = torch.empty(t.shape[0], (n + per16 - 1) // per16 * per16, dtype=t.dtype, device=t.device)
+    view = buf[:, :n]
+    view.copy_(t)
+    return view
+
+
 def _mm32(a, b, layout):
     """Products of fp32 operands for the mHC low-rank path on the tensor cores.
 
@@ -394,23 +407,23 @@ class Backend:
 
     def mm_nn(self, a, b, out_dtype=torch.bfloat16):
         """a[M,K] @ b[K,N]"""
-        if a.shape[1] % 8 or b.shape[1] % 8 or not self.layouts["nn"]:
+        if b.shape[1] % 8 or not self.layouts["nn"]:
             return (a @ b).to(out_dtype)
-        return gemm(a, b, b_mn_major=True, out_dtype=out_dtype)
+        return gemm(_tma_rows(a), b, b_mn_major=True, out_dtype=out_dtype)
 
     def mm_tn(self, a, b, out_dtype=torch.float32):
         """a[K,M]^T @ b[K,N]   (weight gradients: reduction over the token dimension)"""
-        if a.shape[1] % 8 or b.shape[1] % 8 or not self.layouts["tn"]:
+        if not self.layouts["tn"]:
             return (a.t() @ b).to(out_dtype)
-        return gemm(a, b, a_mn_major=True, b_mn_major=True, out_dtype=out_dtype)
+        return gemm(_tma_rows(a), _tma_rows(b), a_mn_major=True, b_mn_major=True, out_dtype=out_dtype)
 
     def weight_grad(self, dy, x, weight):
         """dW = dy^T x.  When the parameter already has an fp32 gradient buffer (the trainer's arena) the product is
         accumulated straight into it with split-K and nothing is returned to autograd; otherwise a fresh tensor is returned."""
         grad = weight.grad
-        fast = self.layouts["tn"] and dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0
-        if fast and grad is not None and grad.dtype == torch.float32 and grad.is_contiguous() and grad.dim() == 2:
-            gemm(dy, x, out=grad, a_mn_major=True, b_mn_major=True, accumulate=True, splits=-1 if self.deterministic else 0)
+        fast = self.layouts["tn"] and grad is not None and grad.data_ptr() % 16 == 0 and grad.shape[-1] % 4 == 0
+        if fast and grad.dtype == torch.float32 and grad.is_contiguous() and grad.dim() == 2:
+            gemm(_tma_rows(dy), _tma_rows(x), out=grad, a_mn_major=True, b_mn_major=True, accumulate=True, splits=-1 if self.deterministic else 0)
             return None
         return self.mm_tn(dy, x).to(weight.dtype)
 

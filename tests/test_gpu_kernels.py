@@ -413,3 +413,25 @@ def test_gemm_persistent_many_tiles_per_cta(ops, M, N, K, monkeypatch):
     assert rel_err(persistent, ref) < 1e-2
     assert torch.equal(persistent, single)
     assert rel_err(wgrad, a[:, :64].float().t() @ a[:, :72].float()) < 1e-3
+
+
+@pytest.mark.parametrize("out_features", [21, 1])
+def test_linear_with_narrow_output(ops, out_features):
+    """Per-head gate projections ([tokens, 21]) and the shared-expert gate ([tokens, 1]): their gradients have rows that are no
+    multiple of 16 bytes and reach the tensor-core GEMM through padded-row views."""
+    from q38.models import modeling
+    backend = modeling.get_backend()
+    torch.manual_seed(12)
+    x = torch.randn(700, 576, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (0.05 * torch.randn(out_features, 576, device="cuda")).requires_grad_()
+    w.grad = torch.zeros_like(w)                                  # the trainer's arena provides the fp32 gradient buffer
+    dy = torch.randn(700, out_features, device="cuda").to(torch.bfloat16)
+    launches = ops.launch_count()
+    y = backend.linear(x, w)
+    y.backward(dy)
+    assert ops.launch_count() - launches == 3                     # forward, dgrad and wgrad all ran on the extension's GEMM
+    ops.check_errors()
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = xr @ wr.to(torch.bfloat16).float().t()
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2 and rel_err(x.grad, xr.grad) < 1e-2 and rel_err(w.grad, wr.grad) < 1e-2
