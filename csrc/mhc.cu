@@ -417,55 +417,51 @@ __global__ void __launch_bounds__(32 * RW, 4) mhc_coef_fwd_rows_kernel(const flo
   }
 }
 
-// Part A of the pre backward on register rows.  Instead of accumulating dB in shared memory it writes dlin [T,24]; dB is the
-// product dlin^T (inv L_raw), formed by mhc_dB_kernel.  d(norm weight) is accumulated per lane across the warp's tokens.
+// Part A of the pre backward on register rows, in two kernels.
+//   mhc_pre_bwd_rows_kernel   streaming part: norm backward (dxin), dpre_n = <dxin, X_n> (written to dcoef[0,4)), d(norm weight)
+//                             accumulated per lane across the warp's tokens.  No long dependent chain, so the loads of the next
+//                             token are issued while the current one is reduced.
+//   mhc_coef_bwd_kernel       per-token coefficient backward on [T,24] data only (sigmoid / Sinkhorn / tanh backward, dL_raw,
+//                             c1, bias and alpha gradients); it writes dlin [T,24], and dB = dlin^T (inv L_raw) is formed by
+//                             mhc_dB_kernel.  Few registers, so enough warps are resident to hide the Sinkhorn chain.
 template <typename GT, int NQ>
-__global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_a_rows_kernel(const GT* __restrict__ dxout, const float* __restrict__ X,
-                                                                        const float* __restrict__ Lraw, MhcParams P, const float* __restrict__ norm_w,
-                                                                        const float* __restrict__ coef, const float* __restrict__ zsave,
-                                                                        const float* __restrict__ inv_save, const float* __restrict__ rstd_save,
-                                                                        float* __restrict__ dcoef, float* __restrict__ dLraw, float* __restrict__ c1_out,
-                                                                        float* __restrict__ dxin_out, float* __restrict__ dlin_out,
-                                                                        float* __restrict__ dbias, float* __restrict__ dnorm_w, int T, int h, int r, int iters) {
+__global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_rows_kernel(const GT* __restrict__ dxout, const float* __restrict__ X,
+                                                                      const float* __restrict__ norm_w, const float* __restrict__ coef,
+                                                                      const float* __restrict__ rstd_save, float* __restrict__ dcoef,
+                                                                      float* __restrict__ dxin_out, float* __restrict__ dnorm_w, int T, int h) {
   extern __shared__ float sm[];
-  const int RP = r + 1;
-  float* Bs = sm;                      // [24][r + 1]
-  float* dnw_s = Bs + NCOEF * RP;      // [h]
-  float* dbias_s = dnw_s + h;          // [32]
-  for (int i = threadIdx.x; i < NCOEF * r; i += blockDim.x) Bs[(i / r) * RP + i % r] = P.Bw[i];
+  float* dnw_s = sm;                   // [h]
   for (int i = threadIdx.x; i < h; i += blockDim.x) dnw_s[i] = 0.f;
-  if (threadIdx.x < 32) dbias_s[threadIdx.x] = 0.f;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, h4 = h >> 2;
   float4 dnw[NQ];
 #pragma unroll
   for (int jj = 0; jj < NQ; ++jj) dnw[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
-  float db = 0.f, da = 0.f;
-  const float alpha = lane < 4 ? P.alphas[0] : lane < 8 ? P.alphas[1] : P.alphas[2];
   for (int t = blockIdx.x * RW + warp; t < T; t += gridDim.x * RW) {
     const float* Xt = X + (size_t)t * NB * h;
     float4 x[NB][NQ];
     load_row<NQ>(Xt, h, h4, lane, x);
-    const float cv = lane < NCOEF ? coef[(size_t)t * NCOEF + lane] : 0.f;
+    const float cv = lane < 4 ? coef[(size_t)t * NCOEF + lane] : 0.f;
     const float p0 = __shfl_sync(0xffffffffu, cv, 0), p1 = __shfl_sync(0xffffffffu, cv, 1), p2 = __shfl_sync(0xffffffffu, cv, 2),
                 p3 = __shfl_sync(0xffffffffu, cv, 3);
-    const float rstd = rstd_save[t], inv = inv_save[t];
+    const float rstd = rstd_save[t];
     const GT* gt = dxout + (size_t)t * h;
-    float4 g[NQ];          // dxout (1 + w)
+    float4 g[NQ], xh[NQ];          // dxout (1 + w), normalised sub-layer input
     float dot = 0.f;
 #pragma unroll
     for (int jj = 0; jj < NQ; ++jj) {
       const int q = lane + 32 * jj;
       g[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+      xh[jj] = g[jj];
       if (q < h4) {
         const float4 gv = load4<GT>(gt + 4 * q), nw = load4<float>(norm_w + 4 * q);
-        const float4 xh = make_float4(rstd * (p0 * x[0][jj].x + p1 * x[1][jj].x + p2 * x[2][jj].x + p3 * x[3][jj].x),
-                                      rstd * (p0 * x[0][jj].y + p1 * x[1][jj].y + p2 * x[2][jj].y + p3 * x[3][jj].y),
-                                      rstd * (p0 * x[0][jj].z + p1 * x[1][jj].z + p2 * x[2][jj].z + p3 * x[3][jj].z),
-                                      rstd * (p0 * x[0][jj].w + p1 * x[1][jj].w + p2 * x[2][jj].w + p3 * x[3][jj].w));
-        dnw[jj].x += gv.x * xh.x; dnw[jj].y += gv.y * xh.y; dnw[jj].z += gv.z * xh.z; dnw[jj].w += gv.w * xh.w;
+        xh[jj] = make_float4(rstd * (p0 * x[0][jj].x + p1 * x[1][jj].x + p2 * x[2][jj].x + p3 * x[3][jj].x),
+                             rstd * (p0 * x[0][jj].y + p1 * x[1][jj].y + p2 * x[2][jj].y + p3 * x[3][jj].y),
+                             rstd * (p0 * x[0][jj].z + p1 * x[1][jj].z + p2 * x[2][jj].z + p3 * x[3][jj].z),
+                             rstd * (p0 * x[0][jj].w + p1 * x[1][jj].w + p2 * x[2][jj].w + p3 * x[3][jj].w));
+        dnw[jj].x += gv.x * xh[jj].x; dnw[jj].y += gv.y * xh[jj].y; dnw[jj].z += gv.z * xh[jj].z; dnw[jj].w += gv.w * xh[jj].w;
         g[jj] = make_float4(gv.x * (1.f + nw.x), gv.y * (1.f + nw.y), gv.z * (1.f + nw.z), gv.w * (1.f + nw.w));
-        dot += dot4(g[jj], xh);
+        dot += dot4(g[jj], xh[jj]);
       }
     }
     dot = warp_sum(dot) / h;
@@ -474,11 +470,8 @@ __global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_a_rows_kernel(const GT
     for (int jj = 0; jj < NQ; ++jj) {
       const int q = lane + 32 * jj;
       if (q < h4) {
-        const float4 xh = make_float4(rstd * (p0 * x[0][jj].x + p1 * x[1][jj].x + p2 * x[2][jj].x + p3 * x[3][jj].x),
-                                      rstd * (p0 * x[0][jj].y + p1 * x[1][jj].y + p2 * x[2][jj].y + p3 * x[3][jj].y),
-                                      rstd * (p0 * x[0][jj].z + p1 * x[1][jj].z + p2 * x[2][jj].z + p3 * x[3][jj].z),
-                                      rstd * (p0 * x[0][jj].w + p1 * x[1][jj].w + p2 * x[2][jj].w + p3 * x[3][jj].w));
-        const float4 dxin = make_float4(rstd * (g[jj].x - xh.x * dot), rstd * (g[jj].y - xh.y * dot), rstd * (g[jj].z - xh.z * dot), rstd * (g[jj].w - xh.w * dot));
+        const float4 dxin = make_float4(rstd * (g[jj].x - xh[jj].x * dot), rstd * (g[jj].y - xh[jj].y * dot), rstd * (g[jj].z - xh[jj].z * dot),
+                                        rstd * (g[jj].w - xh[jj].w * dot));
         store4(dxin_out + (size_t)t * h + 4 * q, dxin);
 #pragma unroll
         for (int n = 0; n < NB; ++n) dpre[n] += dot4(dxin, x[n][jj]);
@@ -486,24 +479,52 @@ __global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_a_rows_kernel(const GT
     }
 #pragma unroll
     for (int n = 0; n < NB; ++n) dpre[n] = warp_sum(dpre[n]);
-    // coefficient backward, lane j < 24 owns logit j
-    const float z = lane < NCOEF ? zsave[(size_t)t * NCOEF + lane] : 0.f;
-    float dlogit = 0.f;
-    if (lane < 4) {
-      const float dp = lane == 0 ? dpre[0] : lane == 1 ? dpre[1] : lane == 2 ? dpre[2] : dpre[3];
-      dcoef[(size_t)t * NCOEF + lane] = dp;
-      dlogit = dp * cv * (1.f - cv);
-    } else if (lane < 8) {
-      dlogit = dcoef[(size_t)t * NCOEF + lane] * cv * (1.f - 0.5f * cv);      // post = 2 sigmoid
+    if (lane < 4) dcoef[(size_t)t * NCOEF + lane] = lane == 0 ? dpre[0] : lane == 1 ? dpre[1] : lane == 2 ? dpre[2] : dpre[3];
+  }
+#pragma unroll
+  for (int jj = 0; jj < NQ; ++jj) {
+    const int q = lane + 32 * jj;
+    if (q < h4) {
+      atomicAdd(&dnw_s[4 * q], dnw[jj].x); atomicAdd(&dnw_s[4 * q + 1], dnw[jj].y);
+      atomicAdd(&dnw_s[4 * q + 2], dnw[jj].z); atomicAdd(&dnw_s[4 * q + 3], dnw[jj].w);
     }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < h; i += blockDim.x) atomicAdd(&dnorm_w[i], dnw_s[i]);
+}
+
+constexpr int CW = 8;      // warps per CTA of the coefficient backward
+__global__ void __launch_bounds__(32 * CW) mhc_coef_bwd_kernel(const float* __restrict__ Lraw, MhcParams P, const float* __restrict__ coef,
+                                                               const float* __restrict__ zsave, const float* __restrict__ inv_save,
+                                                               const float* __restrict__ dcoef, float* __restrict__ dLraw, float* __restrict__ c1_out,
+                                                               float* __restrict__ dlin_out, float* __restrict__ dbias, int T, int h, int r, int iters) {
+  extern __shared__ float sm[];
+  const int RP = r + 1;
+  float* Bs = sm;                      // [24][r + 1]
+  float* dbias_s = Bs + NCOEF * RP;    // [32]
+  for (int i = threadIdx.x; i < NCOEF * r; i += blockDim.x) Bs[(i / r) * RP + i % r] = P.Bw[i];
+  if (threadIdx.x < 32) dbias_s[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float db = 0.f, da = 0.f;
+  const float alpha = lane < 4 ? P.alphas[0] : lane < 8 ? P.alphas[1] : P.alphas[2];
+  for (int t = blockIdx.x * CW + warp; t < T; t += gridDim.x * CW) {
+    const float cv = lane < NCOEF ? coef[(size_t)t * NCOEF + lane] : 0.f;
+    const float dc = lane < NCOEF ? dcoef[(size_t)t * NCOEF + lane] : 0.f;
+    const float z = lane < NCOEF ? zsave[(size_t)t * NCOEF + lane] : 0.f;
+    const float inv = inv_save[t];
+    float dlogit = 0.f;
+    if (lane < 4) dlogit = dc * cv * (1.f - cv);
+    else if (lane < 8) dlogit = dc * cv * (1.f - 0.5f * cv);                  // post = 2 sigmoid
     float dres_logit = 0.f;
     {
       const float zr = __shfl_sync(0xffffffffu, z, (lane & 15) + 8);
+      const float dres = __shfl_sync(0xffffffffu, dc, (lane & 15) + 8);
       float Y[2 * MAX_SINKHORN], S[2 * MAX_SINKHORN];
       if (lane < 16) {
         const float logit = P.b_res[lane] + P.alphas[2] * zr;
         sinkhorn_fwd(logit, iters, Y, S, true);
-        dres_logit = sinkhorn_bwd(dcoef[(size_t)t * NCOEF + 8 + lane], logit, iters, Y, S);
+        dres_logit = sinkhorn_bwd(dres, logit, iters, Y, S);
       }
     }
     const float moved = __shfl_sync(0xffffffffu, dres_logit, (lane + 24) & 31);   // lane j gets lane j - 8
@@ -529,20 +550,11 @@ __global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_a_rows_kernel(const GT
     dinv = warp_sum(dinv);
     if (lane == 0) c1_out[t] = -dinv * inv * inv * inv / (NB * h);
   }
-#pragma unroll
-  for (int jj = 0; jj < NQ; ++jj) {
-    const int q = lane + 32 * jj;
-    if (q < h4) {
-      atomicAdd(&dnw_s[4 * q], dnw[jj].x); atomicAdd(&dnw_s[4 * q + 1], dnw[jj].y);
-      atomicAdd(&dnw_s[4 * q + 2], dnw[jj].z); atomicAdd(&dnw_s[4 * q + 3], dnw[jj].w);
-    }
-  }
   if (lane < NCOEF) {
     atomicAdd(&dbias_s[lane], db);
     atomicAdd(&dbias_s[24 + (lane < 4 ? 0 : lane < 8 ? 1 : 2)], da);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < h; i += blockDim.x) atomicAdd(&dnorm_w[i], dnw_s[i]);
   if (threadIdx.x < 27) atomicAdd(&dbias[threadIdx.x], dbias_s[threadIdx.x]);
 }
 
@@ -667,16 +679,19 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
   const int nq = (h / 4 + 31) / 32;
   if (h % 4 == 0 && r <= 96 && nq <= 8) {
     auto dlin = at::empty({T, NCOEF}, f32);
-    const size_t smem_r = (NCOEF * (r + 1) + h + 32) * sizeof(float);
     const int grid_r = std::min((T + RW - 1) / RW, 3 * kNumSMs);
-#define Q38_ROWS(GT, NQ) mhc_pre_bwd_a_rows_kernel<GT, NQ><<<grid_r, 32 * RW, smem_r, stream>>>((const GT*)dxout.data_ptr(), X.data_ptr<float>(), Lraw.data_ptr<float>(), P, \
-      norm_w.data_ptr<float>(), coef.data_ptr<float>(), z.data_ptr<float>(), inv.data_ptr<float>(), rstd.data_ptr<float>(), dcoef.data_ptr<float>(), dLraw.data_ptr<float>(), \
-      c1.data_ptr<float>(), dxin.data_ptr<float>(), dlin.data_ptr<float>(), dbias.data_ptr<float>(), dnw.data_ptr<float>(), T, h, r, (int)iters)
+#define Q38_ROWS(GT, NQ) mhc_pre_bwd_rows_kernel<GT, NQ><<<grid_r, 32 * RW, h * sizeof(float), stream>>>((const GT*)dxout.data_ptr(), X.data_ptr<float>(), \
+      norm_w.data_ptr<float>(), coef.data_ptr<float>(), rstd.data_ptr<float>(), dcoef.data_ptr<float>(), dxin.data_ptr<float>(), dnw.data_ptr<float>(), T, h)
 #define Q38_ROWS_NQ(GT) switch (nq) { case 1: Q38_ROWS(GT, 1); break; case 2: Q38_ROWS(GT, 2); break; case 3: Q38_ROWS(GT, 3); break; case 4: Q38_ROWS(GT, 4); break; \
       case 5: Q38_ROWS(GT, 5); break; case 6: Q38_ROWS(GT, 6); break; default: Q38_ROWS(GT, 8); break; }
     if (dxout.scalar_type() == at::kBFloat16) Q38_ROWS_NQ(__nv_bfloat16) else Q38_ROWS_NQ(float)
 #undef Q38_ROWS_NQ
 #undef Q38_ROWS
+    C10_CUDA_KERNEL_LAUNCH_CHECK();
+    count_launch();
+    mhc_coef_bwd_kernel<<<std::min((T + CW - 1) / CW, 8 * kNumSMs), 32 * CW, (NCOEF * (r + 1) + 32) * sizeof(float), stream>>>(
+        Lraw.data_ptr<float>(), P, coef.data_ptr<float>(), z.data_ptr<float>(), inv.data_ptr<float>(), dcoef.data_ptr<float>(), dLraw.data_ptr<float>(),
+        c1.data_ptr<float>(), dlin.data_ptr<float>(), dbias.data_ptr<float>(), T, h, r, (int)iters);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     count_launch();
     mhc_dB_kernel<<<(T + DB_TOK - 1) / DB_TOK, 256, DB_TOK * (NCOEF + r) * sizeof(float), stream>>>(dlin.data_ptr<float>(), Lraw.data_ptr<float>(), inv.data_ptr<float>(),

@@ -20,39 +20,42 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Four 8x8 b16 matrices from shared memory; lane l supplies the (16-byte aligned) address of row l % 8 of matrix l / 8.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const bf16* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
 // acc[64x64] += A * B with four warps; warp w owns rows 16w..16w+15.
 //   A(i,k) = TA ? As[k*LDS + i] : As[i*LDS + k]          B(k,n) = TB ? Bs[n*LDS + k] : Bs[k*LDS + n]
 // Accumulator element acc[nt][e]: row = 16w + lane/4 + 8*(e>>1), col = 8nt + 2*(lane%4) + (e&1).
+// Fragments come from ldmatrix (.trans when the tile is stored with the contraction index as its row): one instruction per
+// A fragment and one per pair of B fragments.  Rows are 144 bytes apart, so the eight row addresses of a matrix hit distinct banks.
 template <bool TA, bool TB>
 __device__ __forceinline__ void mma64(const bf16* __restrict__ As, const bf16* __restrict__ Bs, float (&acc)[8][4], int warp, int lane) {
-  const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+  const int l8 = lane & 7, m = lane >> 3;          // row inside a matrix, matrix index
+  // A: matrices (i 0-7, k 0-7), (i 8-15, k 0-7), (i 0-7, k 8-15), (i 8-15, k 8-15)
+  const bf16* a_ptr = TA ? As + (l8 + 8 * (m >> 1)) * LDS + 16 * warp + 8 * (m & 1)
+                         : As + (16 * warp + l8 + 8 * (m & 1)) * LDS + 8 * (m >> 1);
+  // B, for a pair of n-tiles: (k 0-7, n 0-7), (k 8-15, n 0-7), (k 0-7, n 8-15), (k 8-15, n 8-15)
+  const bf16* b_ptr = TB ? Bs + (l8 + 8 * (m >> 1)) * LDS + 8 * (m & 1)
+                         : Bs + (l8 + 8 * (m & 1)) * LDS + 8 * (m >> 1);
 #pragma unroll
   for (int ks = 0; ks < 4; ++ks) {
-    const int k0 = 16 * ks + cq;
     uint32_t a[4];
-    if (!TA) {
-      a[0] = *reinterpret_cast<const uint32_t*>(As + r * LDS + k0);
-      a[1] = *reinterpret_cast<const uint32_t*>(As + (r + 8) * LDS + k0);
-      a[2] = *reinterpret_cast<const uint32_t*>(As + r * LDS + k0 + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(As + (r + 8) * LDS + k0 + 8);
-    } else {
-      a[0] = pack2(As[k0 * LDS + r], As[(k0 + 1) * LDS + r]);
-      a[1] = pack2(As[k0 * LDS + r + 8], As[(k0 + 1) * LDS + r + 8]);
-      a[2] = pack2(As[(k0 + 8) * LDS + r], As[(k0 + 9) * LDS + r]);
-      a[3] = pack2(As[(k0 + 8) * LDS + r + 8], As[(k0 + 9) * LDS + r + 8]);
-    }
+    if (TA) ldmatrix_x4_trans(a, a_ptr + 16 * ks * LDS);
+    else ldmatrix_x4(a, a_ptr + 16 * ks);
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int n = 8 * nt + (lane >> 2);
-      uint32_t b0, b1;
-      if (TB) {
-        b0 = *reinterpret_cast<const uint32_t*>(Bs + n * LDS + k0);
-        b1 = *reinterpret_cast<const uint32_t*>(Bs + n * LDS + k0 + 8);
-      } else {
-        b0 = pack2(Bs[k0 * LDS + n], Bs[(k0 + 1) * LDS + n]);
-        b1 = pack2(Bs[(k0 + 8) * LDS + n], Bs[(k0 + 9) * LDS + n]);
-      }
-      mma16816(acc[nt], a, b0, b1);
+    for (int np = 0; np < 4; ++np) {
+      uint32_t b[4];
+      if (TB) ldmatrix_x4(b, b_ptr + 16 * np * LDS + 16 * ks);
+      else ldmatrix_x4_trans(b, b_ptr + 16 * ks * LDS + 16 * np);
+      mma16816(acc[2 * np], a, b[0], b[1]);
+      mma16816(acc[2 * np + 1], a, b[2], b[3]);
     }
   }
 }
