@@ -10,7 +10,7 @@
 //
 // Kernels
 //   gdn_scan_fwd   one CTA per (batch, value head): the sequential pass over chunks.  The fp32 state lives in the
-//                  accumulator registers of four warps (warp w owns k-rows 16w..16w+15); every product is a 64x64x64
+//                  accumulator registers of eight warps (16 k-rows x 32 v-columns each); every product is a 64x64x64
 //                  bf16 mma.sync with fp32 accumulation; chunk operands are prefetched with cp.async one chunk ahead.
 //                  The chain per chunk is latency bound (three dependent products), which is why this pass uses
 //                  register-resident warp MMAs instead of the TMEM round trips of tcgen05.
@@ -29,7 +29,7 @@ namespace q38 {
 // Forward scan.  Chunk operands w,u,P,qg,kg: [BH, NT, 64, 64] bf16; dch: [BH, NT] fp32.
 // Outputs: o [B, S, H, 64] bf16 (token-major), vnew [BH, NT, 64, 64] bf16, states [BH, NT, 64, 64] bf16 (chunk-start S).
 // ---------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) gdn_scan_fwd_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, const bf16* __restrict__ P,
+__global__ void __launch_bounds__(256) gdn_scan_fwd_kernel(const bf16* __restrict__ w, const bf16* __restrict__ u, const bf16* __restrict__ P,
                                                            const bf16* __restrict__ qg, const bf16* __restrict__ kg, const float* __restrict__ dch,
                                                            bf16* __restrict__ o, bf16* __restrict__ vnew, bf16* __restrict__ states, int NT, int H) {
   extern __shared__ __align__(16) uint8_t smem_bytes[];
@@ -44,48 +44,49 @@ __global__ void __launch_bounds__(128) gdn_scan_fwd_kernel(const bf16* __restric
                          qg + (long long)bh * NT * tile, kg + (long long)bh * NT * tile};
   auto prefetch = [&](int c, int buf) {
 #pragma unroll
-    for (int t = 0; t < 5; ++t) load_tile_async(sm + (buf * 5 + t) * TILE_ELEMS, srcs[t] + (long long)c * tile, 64, tid);
+    for (int t = 0; t < 5; ++t) load_tile_async_256(sm + (buf * 5 + t) * TILE_ELEMS, srcs[t] + (long long)c * tile, 64, tid);
     cp_async_commit();
   };
-  float S[8][4];
+  // eight warps: warp w keeps rows 16 (w & 3).. and v-columns 32 (w >> 2).. of the fp32 state in registers
+  float S[4][4];
   zero_acc(S);
   prefetch(0, 0);
   for (int c = 0; c < NT; ++c) {
     const int buf = c & 1;
     if (c + 1 < NT) { prefetch(c + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-    acc_to_smem(S, Sb, warp, lane);
-    acc_to_global(S, states + ((long long)bh * NT + c) * tile, 64, warp, lane);
+    acc_to_smem_h(S, Sb, warp, lane);
+    acc_to_global_h(S, states + ((long long)bh * NT + c) * tile, 64, warp, lane);
     __syncthreads();                                   // operand tiles of chunk c and Sb are visible
     const bf16* Wt = sm + (buf * 5 + 0) * TILE_ELEMS;
     const bf16* Ut = Wt + TILE_ELEMS;
     const bf16* Pt = Ut + TILE_ELEMS;
     const bf16* Qt = Pt + TILE_ELEMS;
     const bf16* Kt = Qt + TILE_ELEMS;
-    float acc[8][4];
+    float acc[4][4];
     zero_acc(acc);
-    mma64<false, false>(Wt, Sb, acc, warp, lane);      // w S
+    mma64h<false, false>(Wt, Sb, acc, warp, lane);     // w S
     {
-      const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+      const int r = 16 * (warp & 3) + (lane >> 2), c0 = 32 * (warp >> 2) + 2 * (lane & 3);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const __nv_bfloat162 u0 = *reinterpret_cast<const __nv_bfloat162*>(Ut + r * LDS + 8 * nt + cq);
-        const __nv_bfloat162 u1 = *reinterpret_cast<const __nv_bfloat162*>(Ut + (r + 8) * LDS + 8 * nt + cq);
+      for (int nt = 0; nt < 4; ++nt) {
+        const __nv_bfloat162 u0 = *reinterpret_cast<const __nv_bfloat162*>(Ut + r * LDS + 8 * nt + c0);
+        const __nv_bfloat162 u1 = *reinterpret_cast<const __nv_bfloat162*>(Ut + (r + 8) * LDS + 8 * nt + c0);
         acc[nt][0] = __low2float(u0) - acc[nt][0]; acc[nt][1] = __high2float(u0) - acc[nt][1];
         acc[nt][2] = __low2float(u1) - acc[nt][2]; acc[nt][3] = __high2float(u1) - acc[nt][3];
       }
     }
-    acc_to_smem(acc, Vn, warp, lane);                  // v_new (bf16) for the two products below
-    acc_to_global(acc, vnew + ((long long)bh * NT + c) * tile, 64, warp, lane);
-    float out[8][4];
+    acc_to_smem_h(acc, Vn, warp, lane);                // v_new (bf16) for the two products below
+    acc_to_global_h(acc, vnew + ((long long)bh * NT + c) * tile, 64, warp, lane);
+    float out[4][4];
     zero_acc(out);
-    mma64<false, false>(Qt, Sb, out, warp, lane);      // qg S
+    mma64h<false, false>(Qt, Sb, out, warp, lane);     // qg S
     __syncthreads();                                   // Vn complete
-    mma64<false, false>(Pt, Vn, out, warp, lane);      // + P v_new
-    acc_to_global(out, o + (((long long)b * NT * 64 + (long long)c * 64) * H + hv) * 64, (long long)H * 64, warp, lane);
+    mma64h<false, false>(Pt, Vn, out, warp, lane);     // + P v_new
+    acc_to_global_h(out, o + (((long long)b * NT * 64 + (long long)c * 64) * H + hv) * 64, (long long)H * 64, warp, lane);
     const float d = dch[(long long)bh * NT + c];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) { S[nt][0] *= d; S[nt][1] *= d; S[nt][2] *= d; S[nt][3] *= d; }
-    mma64<true, false>(Kt, Vn, S, warp, lane);         // + kg^T v_new
+    for (int nt = 0; nt < 4; ++nt) { S[nt][0] *= d; S[nt][1] *= d; S[nt][2] *= d; S[nt][3] *= d; }
+    mma64h<true, false>(Kt, Vn, S, warp, lane);        // + kg^T v_new
     __syncthreads();                                   // everyone is done with Sb, Vn and this buffer
   }
 }
@@ -94,7 +95,7 @@ __global__ void __launch_bounds__(128) gdn_scan_fwd_kernel(const bf16* __restric
 // Backward scan (reverse over chunks).  Inputs: the forward operands, vnew, states, and do [B,S,H,64].
 // Outputs per chunk: dw, du, dP, dqg, dkg [BH,NT,64,64] bf16 and dd [BH,NT] fp32.
 // ---------------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) gdn_scan_bwd_kernel(const bf16* __restrict__ w, const bf16* __restrict__ P, const bf16* __restrict__ qg,
+__global__ void __launch_bounds__(256) gdn_scan_bwd_kernel(const bf16* __restrict__ w, const bf16* __restrict__ P, const bf16* __restrict__ qg,
                                                            const bf16* __restrict__ kg, const float* __restrict__ dch, const bf16* __restrict__ vnew,
                                                            const bf16* __restrict__ states, const bf16* __restrict__ dout, bf16* __restrict__ dw,
                                                            bf16* __restrict__ du, bf16* __restrict__ dP, bf16* __restrict__ dqg, bf16* __restrict__ dkg,
@@ -104,28 +105,29 @@ __global__ void __launch_bounds__(128) gdn_scan_bwd_kernel(const bf16* __restric
   // two buffers of seven tiles: w, P, qg, kg, vnew, state, do ; then dS (bf16) and dv_new (bf16)
   bf16* dSb = sm + 14 * TILE_ELEMS;
   bf16* dVn = dSb + TILE_ELEMS;
-  __shared__ float red[4];
+  __shared__ float red[8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bh = blockIdx.x, b = bh / H, hv = bh % H;
   const long long tile = 64 * 64, base = (long long)bh * NT * tile;
   auto prefetch = [&](int c, int buf) {
     bf16* dst = sm + buf * 7 * TILE_ELEMS;
-    load_tile_async(dst + 0 * TILE_ELEMS, w + base + (long long)c * tile, 64, tid);
-    load_tile_async(dst + 1 * TILE_ELEMS, P + base + (long long)c * tile, 64, tid);
-    load_tile_async(dst + 2 * TILE_ELEMS, qg + base + (long long)c * tile, 64, tid);
-    load_tile_async(dst + 3 * TILE_ELEMS, kg + base + (long long)c * tile, 64, tid);
-    load_tile_async(dst + 4 * TILE_ELEMS, vnew + base + (long long)c * tile, 64, tid);
-    load_tile_async(dst + 5 * TILE_ELEMS, states + base + (long long)c * tile, 64, tid);
-    load_tile_async(dst + 6 * TILE_ELEMS, dout + (((long long)b * NT * 64 + (long long)c * 64) * H + hv) * 64, (long long)H * 64, tid);
+    load_tile_async_256(dst + 0 * TILE_ELEMS, w + base + (long long)c * tile, 64, tid);
+    load_tile_async_256(dst + 1 * TILE_ELEMS, P + base + (long long)c * tile, 64, tid);
+    load_tile_async_256(dst + 2 * TILE_ELEMS, qg + base + (long long)c * tile, 64, tid);
+    load_tile_async_256(dst + 3 * TILE_ELEMS, kg + base + (long long)c * tile, 64, tid);
+    load_tile_async_256(dst + 4 * TILE_ELEMS, vnew + base + (long long)c * tile, 64, tid);
+    load_tile_async_256(dst + 5 * TILE_ELEMS, states + base + (long long)c * tile, 64, tid);
+    load_tile_async_256(dst + 6 * TILE_ELEMS, dout + (((long long)b * NT * 64 + (long long)c * 64) * H + hv) * 64, (long long)H * 64, tid);
     cp_async_commit();
   };
-  float dS[8][4];
+  const int r = 16 * (warp & 3) + (lane >> 2), c0 = 32 * (warp >> 2) + 2 * (lane & 3);
+  float dS[4][4];
   zero_acc(dS);
   prefetch(NT - 1, (NT - 1) & 1);
   for (int c = NT - 1; c >= 0; --c) {
     const int buf = c & 1;
     if (c > 0) { prefetch(c - 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-    acc_to_smem(dS, dSb, warp, lane);
+    acc_to_smem_h(dS, dSb, warp, lane);
     __syncthreads();
     const bf16* Wt = sm + buf * 7 * TILE_ELEMS;
     const bf16* Pt = Wt + TILE_ELEMS;
@@ -135,21 +137,20 @@ __global__ void __launch_bounds__(128) gdn_scan_bwd_kernel(const bf16* __restric
     const bf16* St = Vt + TILE_ELEMS;
     const bf16* Dt = St + TILE_ELEMS;
     const long long off = base + (long long)c * tile;
-    float acc[8][4];
+    float acc[4][4];
     // dv_new = P^T dO + kg dS'
     zero_acc(acc);
-    mma64<true, false>(Pt, Dt, acc, warp, lane);
-    mma64<false, false>(Kt, dSb, acc, warp, lane);
-    acc_to_smem(acc, dVn, warp, lane);
-    acc_to_global(acc, du + off, 64, warp, lane);
+    mma64h<true, false>(Pt, Dt, acc, warp, lane);
+    mma64h<false, false>(Kt, dSb, acc, warp, lane);
+    acc_to_smem_h(acc, dVn, warp, lane);
+    acc_to_global_h(acc, du + off, 64, warp, lane);
     // dd = <dS', S>   (fragment of S read from the state tile in accumulator layout)
     {
-      const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
       float part = 0.f;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const __nv_bfloat162 s0 = *reinterpret_cast<const __nv_bfloat162*>(St + r * LDS + 8 * nt + cq);
-        const __nv_bfloat162 s1 = *reinterpret_cast<const __nv_bfloat162*>(St + (r + 8) * LDS + 8 * nt + cq);
+      for (int nt = 0; nt < 4; ++nt) {
+        const __nv_bfloat162 s0 = *reinterpret_cast<const __nv_bfloat162*>(St + r * LDS + 8 * nt + c0);
+        const __nv_bfloat162 s1 = *reinterpret_cast<const __nv_bfloat162*>(St + (r + 8) * LDS + 8 * nt + c0);
         part += dS[nt][0] * __low2float(s0) + dS[nt][1] * __high2float(s0) + dS[nt][2] * __low2float(s1) + dS[nt][3] * __high2float(s1);
       }
       part = warp_sum(part);
@@ -157,40 +158,37 @@ __global__ void __launch_bounds__(128) gdn_scan_bwd_kernel(const bf16* __restric
     }
     // dqg = dO S^T ;  dkg = v_new dS'^T ;  dP = tril(dO v_new^T)
     zero_acc(acc);
-    mma64<false, true>(Dt, St, acc, warp, lane);
-    acc_to_global(acc, dqg + off, 64, warp, lane);
+    mma64h<false, true>(Dt, St, acc, warp, lane);
+    acc_to_global_h(acc, dqg + off, 64, warp, lane);
     zero_acc(acc);
-    mma64<false, true>(Vt, dSb, acc, warp, lane);
-    acc_to_global(acc, dkg + off, 64, warp, lane);
+    mma64h<false, true>(Vt, dSb, acc, warp, lane);
+    acc_to_global_h(acc, dkg + off, 64, warp, lane);
     zero_acc(acc);
-    mma64<false, true>(Dt, Vt, acc, warp, lane);
-    {
-      const int r = 16 * warp + (lane >> 2), cq = 2 * (lane & 3);
+    mma64h<false, true>(Dt, Vt, acc, warp, lane);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int col = 8 * nt + cq;
-        if (col > r) acc[nt][0] = 0.f;
-        if (col + 1 > r) acc[nt][1] = 0.f;
-        if (col > r + 8) acc[nt][2] = 0.f;
-        if (col + 1 > r + 8) acc[nt][3] = 0.f;
-      }
+    for (int nt = 0; nt < 4; ++nt) {
+      const int col = 8 * nt + c0;
+      if (col > r) acc[nt][0] = 0.f;
+      if (col + 1 > r) acc[nt][1] = 0.f;
+      if (col > r + 8) acc[nt][2] = 0.f;
+      if (col + 1 > r + 8) acc[nt][3] = 0.f;
     }
-    acc_to_global(acc, dP + off, 64, warp, lane);
+    acc_to_global_h(acc, dP + off, 64, warp, lane);
     __syncthreads();                                    // dVn and red[] complete
-    if (tid == 0) dd[(long long)bh * NT + c] = red[0] + red[1] + red[2] + red[3];
+    if (tid == 0) dd[(long long)bh * NT + c] = red[0] + red[1] + red[2] + red[3] + red[4] + red[5] + red[6] + red[7];
     // dw = -dv_new S^T
     zero_acc(acc);
-    mma64<false, true>(dVn, St, acc, warp, lane);
-    acc_to_global(acc, dw + off, 64, warp, lane, -1.f);
+    mma64h<false, true>(dVn, St, acc, warp, lane);
+    acc_to_global_h(acc, dw + off, 64, warp, lane, -1.f);
     // dS = d dS' + qg^T dO - w^T dv_new
     const float d = dch[(long long)bh * NT + c];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) { dS[nt][0] *= d; dS[nt][1] *= d; dS[nt][2] *= d; dS[nt][3] *= d; }
-    mma64<true, false>(Qt, Dt, dS, warp, lane);
+    for (int nt = 0; nt < 4; ++nt) { dS[nt][0] *= d; dS[nt][1] *= d; dS[nt][2] *= d; dS[nt][3] *= d; }
+    mma64h<true, false>(Qt, Dt, dS, warp, lane);
     zero_acc(acc);
-    mma64<true, false>(Wt, dVn, acc, warp, lane);
+    mma64h<true, false>(Wt, dVn, acc, warp, lane);
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) { dS[nt][0] -= acc[nt][0]; dS[nt][1] -= acc[nt][1]; dS[nt][2] -= acc[nt][2]; dS[nt][3] -= acc[nt][3]; }
+    for (int nt = 0; nt < 4; ++nt) { dS[nt][0] -= acc[nt][0]; dS[nt][1] -= acc[nt][1]; dS[nt][2] -= acc[nt][2]; dS[nt][3] -= acc[nt][3]; }
     __syncthreads();
   }
 }
@@ -212,7 +210,7 @@ std::vector<at::Tensor> gdn_scan_fwd(const at::Tensor& w, const at::Tensor& u, c
   const int smem = 12 * TILE_ELEMS * 2;
   static bool configured = false;
   if (!configured) { C10_CUDA_CHECK(cudaFuncSetAttribute(gdn_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); configured = true; }
-  gdn_scan_fwd_kernel<<<(int)BH, 128, smem, at::cuda::getCurrentCUDAStream()>>>(
+  gdn_scan_fwd_kernel<<<(int)BH, 256, smem, at::cuda::getCurrentCUDAStream()>>>(
       (const bf16*)w.data_ptr(), (const bf16*)u.data_ptr(), (const bf16*)P.data_ptr(), (const bf16*)qg.data_ptr(), (const bf16*)kg.data_ptr(),
       dch.data_ptr<float>(), (bf16*)o.data_ptr(), (bf16*)vnew.data_ptr(), (bf16*)states.data_ptr(), (int)NT, (int)H);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
@@ -235,7 +233,7 @@ std::vector<at::Tensor> gdn_scan_bwd(const at::Tensor& w, const at::Tensor& P, c
   const int smem = 16 * TILE_ELEMS * 2;
   static bool configured = false;
   if (!configured) { C10_CUDA_CHECK(cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); configured = true; }
-  gdn_scan_bwd_kernel<<<(int)BH, 128, smem, at::cuda::getCurrentCUDAStream()>>>(
+  gdn_scan_bwd_kernel<<<(int)BH, 256, smem, at::cuda::getCurrentCUDAStream()>>>(
       (const bf16*)w.data_ptr(), (const bf16*)P.data_ptr(), (const bf16*)qg.data_ptr(), (const bf16*)kg.data_ptr(), dch.data_ptr<float>(),
       (const bf16*)vnew.data_ptr(), (const bf16*)states.data_ptr(), (const bf16*)dout.data_ptr(), (bf16*)dw.data_ptr(), (bf16*)du.data_ptr(),
       (bf16*)dP.data_ptr(), (bf16*)dqg.data_ptr(), (bf16*)dkg.data_ptr(), dd.data_ptr<float>(), (int)NT, (int)H);

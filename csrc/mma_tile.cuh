@@ -119,5 +119,65 @@ __device__ __forceinline__ void frag_from_smem(const bf16* __restrict__ src, flo
   }
 }
 
+// ---- half-width variants for CTAs of eight warps -----------------------------------------------------------------------
+// Warp w owns rows 16 (w & 3) .. +15 and columns 32 (w >> 2) .. +31 of the 64x64 output: twice the warps of mma64 work on
+// one tile, each with half the accumulator registers, which doubles the latency hiding of chains of dependent products.
+// Accumulator element acc[nt][e]: row = 16 (w & 3) + lane/4 + 8*(e>>1), col = 32 (w >> 2) + 8nt + 2*(lane%4) + (e&1).
+template <bool TA, bool TB>
+__device__ __forceinline__ void mma64h(const bf16* __restrict__ As, const bf16* __restrict__ Bs, float (&acc)[4][4], int warp, int lane) {
+  const int l8 = lane & 7, m = lane >> 3, wr = warp & 3, n0 = 32 * (warp >> 2);
+  const bf16* a_ptr = TA ? As + (l8 + 8 * (m >> 1)) * LDS + 16 * wr + 8 * (m & 1)
+                         : As + (16 * wr + l8 + 8 * (m & 1)) * LDS + 8 * (m >> 1);
+  const bf16* b_ptr = TB ? Bs + (n0 + l8 + 8 * (m >> 1)) * LDS + 8 * (m & 1)
+                         : Bs + (l8 + 8 * (m & 1)) * LDS + n0 + 8 * (m >> 1);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    uint32_t a[4];
+    if (TA) ldmatrix_x4_trans(a, a_ptr + 16 * ks * LDS);
+    else ldmatrix_x4(a, a_ptr + 16 * ks);
+#pragma unroll
+    for (int np = 0; np < 2; ++np) {
+      uint32_t b[4];
+      if (TB) ldmatrix_x4(b, b_ptr + 16 * np * LDS + 16 * ks);
+      else ldmatrix_x4_trans(b, b_ptr + 16 * ks * LDS + 16 * np);
+      mma16816(acc[2 * np], a, b[0], b[1]);
+      mma16816(acc[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+__device__ __forceinline__ void zero_acc(float (&acc)[4][4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+}
+
+__device__ __forceinline__ void acc_to_smem_h(const float (&acc)[4][4], bf16* __restrict__ dst, int warp, int lane) {
+  const int r = 16 * (warp & 3) + (lane >> 2), c0 = 32 * (warp >> 2) + 2 * (lane & 3);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    *reinterpret_cast<__nv_bfloat162*>(dst + r * LDS + 8 * nt + c0) = __floats2bfloat162_rn(acc[nt][0], acc[nt][1]);
+    *reinterpret_cast<__nv_bfloat162*>(dst + (r + 8) * LDS + 8 * nt + c0) = __floats2bfloat162_rn(acc[nt][2], acc[nt][3]);
+  }
+}
+
+__device__ __forceinline__ void acc_to_global_h(const float (&acc)[4][4], bf16* __restrict__ dst, long long ld, int warp, int lane, float scale = 1.f) {
+  const int r = 16 * (warp & 3) + (lane >> 2), c0 = 32 * (warp >> 2) + 2 * (lane & 3);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    *reinterpret_cast<__nv_bfloat162*>(dst + (long long)r * ld + 8 * nt + c0) = __floats2bfloat162_rn(acc[nt][0] * scale, acc[nt][1] * scale);
+    *reinterpret_cast<__nv_bfloat162*>(dst + (long long)(r + 8) * ld + 8 * nt + c0) = __floats2bfloat162_rn(acc[nt][2] * scale, acc[nt][3] * scale);
+  }
+}
+
+// load_tile_async for a CTA of 256 threads.
+__device__ __forceinline__ void load_tile_async_256(bf16* __restrict__ dst, const bf16* __restrict__ src, long long ld, int tid) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int chunk = tid + 256 * i;                 // 512 chunks of 16 bytes
+    const int row = chunk >> 3, col = (chunk & 7) * 8;
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst + row * LDS + col));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + (long long)row * ld + col) : "memory");
+  }
+}
 
 }  // namespace q38
