@@ -13,6 +13,8 @@ TORCH_LIBRARY(q38, m) {
         [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool amn, bool bmn, double alpha, bool acc, at::Tensor& err, int64_t splits) {
           q38::gemm_bf16_persistent(a, b, c, amn, bmn, alpha, acc, err, splits);
         });
+  m.def("ngram_fwd(Tensor ids, Tensor emb2, Tensor emb3, Tensor norm_w, int vocab, int eos, float eps) -> Tensor[]", &q38::ngram_fwd);
+  m.def("ngram_bwd(Tensor de, Tensor rows, Tensor emb2, Tensor emb3, Tensor norm_w, Tensor rstd, Tensor(a!) g2, Tensor(b!) g3) -> Tensor", &q38::ngram_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps, bool out_bf16) -> Tensor[]");
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) -> Tensor[]");
   m.def("gated_rmsnorm_fwd(Tensor x, Tensor gate, Tensor w, float eps) -> Tensor");

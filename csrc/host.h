@@ -23,6 +23,12 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_m
 void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
                           bool accumulate, at::Tensor& err, int64_t splits);
 
+// ngram.cu
+std::vector<at::Tensor> ngram_fwd(const at::Tensor& ids, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w, int64_t vocab,
+                                  int64_t eos, double eps);
+at::Tensor ngram_bwd(const at::Tensor& de, const at::Tensor& rows, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w,
+                     const at::Tensor& rstd, at::Tensor& g2, at::Tensor& g3);
+
 // elementwise.cu
 std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps, bool out_bf16);
 std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w, const at::Tensor& rstd);

@@ -634,7 +634,7 @@ class NGramEmbedding(nn.Module):
     def delta(self, h, ids):
         """The increment ``sigmoid(W h + b) * rmsnorm(emb2[i2] + emb3[i3])`` to add to every branch."""
         fast = _hook("ngram_delta", h)
-        if fast is not None:
+        if fast is not None and not self.collect:
             return fast(self, h, ids)
         i2, i3 = self.indices(ids)
         e = self.norm((self.emb2(i2) + self.emb3(i3)).float()).to(h.dtype)

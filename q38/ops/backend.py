@@ -318,6 +318,26 @@ class _BlockAttention(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+class _NGramEmbed(torch.autograd.Function):
+    """ids -> rmsnorm(emb2[i2] + emb3[i3]) (bf16).  The backward adds the table gradients straight into the parameters' fp32
+    gradient buffers with atomics (so the last bits depend on the order) and returns only d(norm weight) to autograd."""
+
+    @staticmethod
+    def forward(ctx, ids, emb2, emb3, norm_w, vocab, eos, eps):
+        e, rstd, rows = load().ngram_fwd(ids.long().contiguous(), emb2, emb3, norm_w.float().contiguous(), vocab, eos, eps)
+        ctx.save_for_backward(rows, rstd, emb2, emb3, norm_w)
+        return e
+
+    @staticmethod
+    def backward(ctx, de):
+        rows, rstd, emb2, emb3, norm_w = ctx.saved_tensors
+        in_place = all(p.grad is not None and p.grad.dtype == torch.float32 and p.grad.is_contiguous() for p in (emb2, emb3))
+        g2 = emb2.grad if in_place else torch.zeros_like(emb2)
+        g3 = emb3.grad if in_place else torch.zeros_like(emb3)
+        dw = load().ngram_bwd(de.to(torch.bfloat16).contiguous(), rows, emb2, emb3, norm_w.float().contiguous(), rstd, g2, g3)
+        return None, (None if in_place else g2), (None if in_place else g3), dw.to(norm_w.dtype), None, None, None
+
+
 class _Route(torch.autograd.Function):
     """bf16 router logits -> (top-k weights, indices, per-expert probability sums, per-expert assignment counts)."""
 
@@ -542,6 +562,19 @@ class Backend:
             o = _BlockAttention.apply(q, k, v, count, index, attn.scaling)
         o = o.reshape(B, S, -1) * torch.sigmoid(gate)
         return self.linear(o, attn.o_proj.weight), kl
+
+    def ngram_delta(self, m, h, ids):
+        """sigmoid(W h + b) * rmsnorm(emb2[i2] + emb3[i3]) with the hash, gather, norm and scatter-add backward in one kernel pair."""
+        w2, w3 = m.emb2.weight, m.emb3.weight
+        if (h.dtype != torch.bfloat16 or m.collect or w2.dtype != torch.float32 or m.hidden % 4 or not w2.is_contiguous() or not w3.is_contiguous()
+                or m.norm.weight is None):
+            i2, i3 = m.indices(ids)
+            e = m.norm((m.emb2(i2) + m.emb3(i3)).float()).to(h.dtype)
+        else:
+            eos = -1 if m.eos_id is None else int(m.eos_id)
+            e = _NGramEmbed.apply(ids, w2, w3, m.norm.weight, int(m.vocab), eos, float(m.norm.eps if m.norm.eps is not None else 1e-6))
+        gate = torch.sigmoid(self.linear(h, m.gate.weight) + m.gate.bias.to(h.dtype))
+        return gate * e
 
     def moe_block(self, block, x):
         experts = block.experts

@@ -435,3 +435,40 @@ def test_linear_with_narrow_output(ops, out_features):
     yr = xr @ wr.to(torch.bfloat16).float().t()
     yr.backward(dy.float())
     assert rel_err(y, yr) < 1e-2 and rel_err(x.grad, xr.grad) < 1e-2 and rel_err(w.grad, wr.grad) < 1e-2
+
+
+def test_ngram_embedding_matches_specification(ops):
+    """Hash rows (EOS-aware context), gather + RMSNorm forward, and the scatter-add backward against the PyTorch module."""
+    from q38.models import modeling
+    backend = modeling.get_backend()
+    torch.manual_seed(13)
+    h, vocab, rows, eos = 128, 1000, 4099, 7
+    m = modeling.NGramEmbedding(h, vocab, rows, eos).cuda()
+    with torch.no_grad():
+        m.norm.weight.normal_(1.0, 0.2)
+    ids = torch.randint(0, vocab, (3, 257), device="cuda")
+    ids[:, ::23] = eos
+    ids[0, :3] = torch.tensor([eos, 5, eos])
+    hid = torch.randn(3, 257, h, device="cuda").to(torch.bfloat16)
+    dout = torch.randn(3, 257, h, device="cuda").to(torch.bfloat16)
+    _, _, got_rows = ops.load().ngram_fwd(ids, m.emb2.weight, m.emb3.weight, m.norm.weight.float(), vocab, eos, 1e-6)
+    i2, i3 = m.indices(ids)
+    assert torch.equal(got_rows[..., 0].long(), i2) and torch.equal(got_rows[..., 1].long(), i3)
+
+    def run(fast):
+        for p in m.parameters():
+            p.grad = None
+        hx = hid.clone().requires_grad_()
+        out = backend.ngram_delta(m, hx, ids) if fast else m.delta(hx.float(), ids)
+        out.backward(dout if fast else dout.float())
+        return out, hx.grad, {n: p.grad.clone() for n, p in m.named_parameters()}
+
+    modeling.set_backend(None)
+    try:
+        ref_out, ref_dh, ref_g = run(False)
+    finally:
+        modeling.set_backend(backend)
+    out, dh, g = run(True)
+    assert rel_err(out, ref_out) < 2e-2 and rel_err(dh, ref_dh) < 2e-2
+    for name in ref_g:
+        assert rel_err(g[name], ref_g[name]) < 2e-2, name
