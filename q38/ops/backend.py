@@ -406,6 +406,23 @@ class _Experts(torch.autograd.Function):
         return dx, d_top_w, None, d_gate_up, d_down
 
 
+def _nvtx(name):
+    """With Q38_NVTX=1 every call of the decorated hook is an NVTX range (visible in Nsight timelines); otherwise a no-op."""
+    def wrap(fn):
+        if os.environ.get("Q38_NVTX") != "1":
+            return fn
+
+        def ranged(*args, **kwargs):
+            torch.cuda.nvtx.range_push(name)
+            try:
+                return fn(*args, **kwargs)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        ranged.__name__, ranged.__doc__ = fn.__name__, fn.__doc__
+        return ranged
+    return wrap
+
+
 class Backend:
     def __init__(self, self_check=True):
         self.ops = load()
@@ -482,12 +499,14 @@ class Backend:
             return None
         return _GatedRMSNorm.apply(x, gate, weight, eps)
 
+    @_nvtx("q38.mhc_pre_norm")
     def mhc_pre_norm(self, mhc, norm, X, dtype):
         link = _MhcLink()
         x, coef = _MhcPreNorm.apply(X, mhc.A.weight, mhc.B.weight, mhc.b_pre, mhc.b_post, mhc.b_res, mhc.alphas, norm.weight,
                                     mhc.iters, norm.eps, dtype, link)
         return x, (X, coef, link)
 
+    @_nvtx("q38.mhc_post")
     def mhc_post(self, mhc, y, state):
         X, coef, link = state
         return _MhcPost.apply(X, y, coef, link)
@@ -504,6 +523,7 @@ class Backend:
         return _GdnScan.apply(flat(ops["w"]), flat(ops["u"]), flat(ops["P"]), flat(ops["qg"]), flat(ops["kg"]),
                               ops["carry"].reshape(B * Hv, -1), B, Hv)
 
+    @_nvtx("q38.gated_deltanet")
     def gated_deltanet(self, m, x):
         B, S, _ = x.shape
         if x.dtype != torch.bfloat16 or S % 64 or m.head_k_dim != 64 or m.head_v_dim != 64:
@@ -536,6 +556,7 @@ class Backend:
         blse = ops.qsa_indexer_fwd(qi.detach(), ki.detach(), wi.detach(), D ** -0.5)
         return None, ops.qsa_kl_combine(None, blse, 1)[1]
 
+    @_nvtx("q38.qsa_attention")
     def qsa_attention(self, attn, x, cos, sin, indexer, budget, dense, want_kl):
         from ..models import modeling
         F = torch.nn.functional
@@ -552,9 +573,17 @@ class Backend:
         if indexer is not None and (want_kl or not dense):
             if want_kl:
                 kl, lp_blk = self.indexer_block_logprobs(indexer, x.detach(), cos, sin, q.detach(), k.detach(), attn.scaling)
-            else:
+            elif os.environ.get("Q38_INDEXER_BASELINE"):
                 with torch.no_grad():
                     _, lp_blk = self.indexer_block_logprobs(indexer, x.detach(), cos, sin)
+            else:
+                # no KL wanted (evaluation, or training steps that skip it): block selection only looks at the first query of each
+                # 64-token block, so only those S/64 queries are scored -> lp_blk [B, nb, nb]  (reference: modeling_qwen3_8_moe.py:1126)
+                with torch.no_grad():
+                    score = indexer(x.detach(), cos, sin, block_queries=True)
+                    pos = torch.arange(S, device=x.device)
+                    score = score.masked_fill(pos[None, :] > pos[::modeling.BLK][:, None], -1e9)
+                    lp_blk = score.log_softmax(-1).view(B, S // modeling.BLK, S // modeling.BLK, modeling.BLK).logsumexp(-1).contiguous()
         if dense or indexer is None:
             o = _BlockAttention.apply(q, k, v, None, None, attn.scaling)
         else:
@@ -563,6 +592,7 @@ class Backend:
         o = o.reshape(B, S, -1) * torch.sigmoid(gate)
         return self.linear(o, attn.o_proj.weight), kl
 
+    @_nvtx("q38.ngram_delta")
     def ngram_delta(self, m, h, ids):
         """sigmoid(W h + b) * rmsnorm(emb2[i2] + emb3[i3]) with the hash, gather, norm and scatter-add backward in one kernel pair."""
         w2, w3 = m.emb2.weight, m.emb3.weight
@@ -576,6 +606,7 @@ class Backend:
         gate = torch.sigmoid(self.linear(h, m.gate.weight) + m.gate.bias.to(h.dtype))
         return gate * e
 
+    @_nvtx("q38.moe_block")
     def moe_block(self, block, x):
         experts = block.experts
         E, f, h = experts.num_experts, experts.intermediate_dim, experts.hidden_dim
@@ -597,6 +628,7 @@ class Backend:
         mid = torch.nn.functional.silu(self.linear(x2, shared.gate_proj.weight)) * self.linear(x2, shared.up_proj.weight)
         return (routed + shared_gate * self.linear(mid, shared.down_proj.weight)).reshape(shape)
 
+    @_nvtx("q38.linear_cross_entropy")
     def linear_cross_entropy(self, weight, hidden, target, reduction):
         """Chunked logits + CE; logits of one chunk only ever exist, in fp32."""
         return _chunked_linear_ce(self, weight, hidden, target, reduction)

@@ -79,3 +79,21 @@ def test_resume_rejects_changed_accounting():
 def test_budget_is_whole_batches():
     assert budget_tokens(100, 1e9, 4096) % 4096 == 0
     assert budget_tokens(100, 1e9, 4096) * 100 <= 1e9
+
+
+def test_flops_audit_agrees_with_instantiated_models():
+    """Parameter counts of the models built from the presets equal the presets' accounting, and the ledger reproduces
+    the recorded train FLOPs per token (q38.utils.audit_flops)."""
+    from q38.utils.audit_flops import audit
+    for name in ("q38_c1", "q38_c2"):
+        report = audit(name, 4096)
+        assert report["failures"] == [], report["failures"]
+        assert report["weight_gemm_flops_per_token"] < report["fwd_flops_per_token"]
+
+
+def test_launcher_builds_loopback_torchrun_command():
+    from q38.launch import command
+    single = command("q38.train", 1, 29500, ["--preset", "q38_c1"])
+    multi = command("q38.train", 8, 29511, ["--preset", "q38_c2"])
+    assert single[1:3] == ["-m", "q38.train"]
+    assert "--nproc-per-node=8" in multi and multi[multi.index("--master-addr") + 1] == "127.0.0.1" and multi[-2:] == ["--preset", "q38_c2"]

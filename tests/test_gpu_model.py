@@ -80,3 +80,10 @@ def test_public_training_step_reduces_loss():
 def test_graft_smoke():
     import __graft_entry__ as entry
     entry.smoke()
+
+
+def test_kernel_parity_script_passes():
+    """`python -m q38.utils.check_kernels` (model-level parity of the kernel path against the PyTorch path) reports no failure."""
+    from q38.utils import check_kernels
+    assert check_kernels.main(["--hidden", "128", "--seq", "256"]) == 0
+    assert check_kernels.main(["--hidden", "256", "--seq", "1024", "--batch", "4"]) == 0
