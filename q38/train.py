@@ -118,6 +118,7 @@ def parse_args(argv=None):
          "Invalid training or evaluation sampling mode"),
         (a.data_seed >= -1, "data_seed must be -1 (use model seed) or nonnegative"),
         (a.grad_sync in ("auto", "p2p", "collective"), "--grad_sync must be auto, p2p or collective"),
+        (a.fp8_ffn == 0, "--fp8_ffn 1 is not available: the routed experts run in bf16 (no block-scaled FP8 grouped GEMM in this build)"),
     ]
     for ok, message in checks:
         if not ok:
