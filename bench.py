@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--grad_ckpt", type=int, default=-1)
     ap.add_argument("--expert_parallel", type=int, default=0, help="1: split the experts over the GPUs (needs --gpus > 1)")
     ap.add_argument("--ep_capacity", type=float, default=4.0)
+    ap.add_argument("--overlap_wgrad", type=int, default=1, help="0: weight-gradient GEMMs on the main stream instead of a second one")
+    ap.add_argument("--cuda_graphs", type=int, default=1)
     return ap.parse_args()
 
 
@@ -85,7 +87,7 @@ def main():
     cfg = model_config(preset["model"], vocab, a.seq, bos_token_id=1, eos_token_id=eos, pad_token_id=0)
     fc = count(cfg.to_dict(), a.seq)
     args = SimpleNamespace(**{**train, "aux_coef": preset["model"]["aux_coef"], "grad_sync": a.grad_sync, "micro_bs": micro_bs, "seq": a.seq,
-                              "expert_parallel": a.expert_parallel, "ep_capacity": a.ep_capacity,
+                              "expert_parallel": a.expert_parallel, "ep_capacity": a.ep_capacity, "overlap_wgrad": a.overlap_wgrad, "cuda_graphs": a.cuda_graphs,
                               "grad_ckpt": train.get("grad_ckpt", 0) if a.grad_ckpt < 0 else a.grad_ckpt})
     torch.manual_seed(0)
     trainer = Trainer(cfg, args, dev, rank, world)

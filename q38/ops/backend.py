@@ -88,6 +88,43 @@ class _GatedRMSNorm(torch.autograd.Function):
         return dx, dgate, dw.to(weight.dtype), None
 
 
+class _SideStream:
+    """Weight gradients have no consumer until the optimizer step, so the trainer lets them run on a second stream where they
+    fill the SMs that the latency-bound kernels of the backward chain (delta-rule scan, block attention) leave idle.
+
+    `run(fn, *tensors)` makes the side stream wait for the work issued so far, runs `fn` there and tells the caching allocator
+    that `tensors` are in use on that stream.  `join()` makes the current stream wait for everything issued on the side
+    stream; the owner calls it after every backward pass (inside a CUDA-graph capture this is also what joins the forked
+    branch back).  Disabled (fn runs inline) unless `enabled` is set."""
+
+    def __init__(self):
+        self.enabled = False
+        self.stream = None
+        self.pending = False
+
+    def run(self, fn, *tensors):
+        if not self.enabled:
+            return fn()
+        cur = torch.cuda.current_stream()
+        if self.stream is None:
+            self.stream = torch.cuda.Stream()
+        self.stream.wait_stream(cur)
+        with torch.cuda.stream(self.stream):
+            out = fn()
+        for t in tensors:
+            t.record_stream(self.stream)
+        self.pending = True
+        return out
+
+    def join(self):
+        if self.pending:
+            torch.cuda.current_stream().wait_stream(self.stream)
+            self.pending = False
+
+
+WGRAD_STREAM = _SideStream()
+
+
 def _tma_rows(t):
     """A 2-D tensor whose row stride TMA accepts (a multiple of 16 bytes).  A narrow matrix, e.g. the [tokens, 21] gradient of a
     per-head gate projection, is copied into a buffer with padded rows and returned as a view of it; the tensor map still
@@ -126,8 +163,9 @@ def _mhc_weight_grad(dL, Xf, A_w):
     grad = A_w.grad
     if (grad is not None and grad.dtype == torch.float32 and grad.is_contiguous() and dL.shape[1] % 8 == 0 and Xf.shape[1] % 8 == 0
             and not os.environ.get("Q38_MHC_FP32_GEMM")):
-        gemm(dL.to(torch.bfloat16), Xf.to(torch.bfloat16), out=grad, a_mn_major=True, b_mn_major=True, accumulate=True,
-             splits=-1 if os.environ.get("Q38_DETERMINISTIC") == "1" else 0)
+        a, b = dL.to(torch.bfloat16), Xf.to(torch.bfloat16)
+        WGRAD_STREAM.run(lambda: gemm(a, b, out=grad, a_mn_major=True, b_mn_major=True, accumulate=True,
+                                      splits=-1 if os.environ.get("Q38_DETERMINISTIC") == "1" else 0), a, b)
         return None
     return _mm32(dL, Xf, 'tn').to(A_w.dtype)
 
@@ -395,7 +433,8 @@ class _Experts(torch.autograd.Function):
         def weight_grad(a, b, weight):
             grad = weight.grad
             if grad is not None and grad.dtype == torch.float32 and grad.is_contiguous():
-                ops.moe_grouped_wgrad(a, b, grad, offsets, err)          # accumulate in place; autograd gets no extra tensor
+                # accumulate in place; autograd gets no extra tensor
+                WGRAD_STREAM.run(lambda: ops.moe_grouped_wgrad(a, b, grad, offsets, err), a, b, offsets)
                 return None
             fresh = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
             ops.moe_grouped_wgrad(a, b, fresh, offsets, err)
@@ -460,7 +499,8 @@ class Backend:
         grad = weight.grad
         fast = self.layouts["tn"] and grad is not None and grad.data_ptr() % 16 == 0 and grad.shape[-1] % 4 == 0
         if fast and grad.dtype == torch.float32 and grad.is_contiguous() and grad.dim() == 2:
-            gemm(_tma_rows(dy), _tma_rows(x), out=grad, a_mn_major=True, b_mn_major=True, accumulate=True, splits=-1 if self.deterministic else 0)
+            a, b = _tma_rows(dy), _tma_rows(x)
+            WGRAD_STREAM.run(lambda: gemm(a, b, out=grad, a_mn_major=True, b_mn_major=True, accumulate=True, splits=-1 if self.deterministic else 0), a, b)
             return None
         return self.mm_tn(dy, x).to(weight.dtype)
 

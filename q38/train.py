@@ -51,7 +51,7 @@ TRAIN_DEFAULTS = dict(
     eval_sampling="random", eval_offset=0, final_eval_tokens=0, final_eval_offset=0, require_ready_pool=0,
     auto_micro_bs=0, probe_mem_frac=0.92, mtp_coef=0.3, kl_coef=0.05, muon=1, dense_warmup=1, grad_ckpt=0)
 # Options of this framework that the reference trainer does not have (never part of the resume contract).
-ENGINE_DEFAULTS = dict(grad_sync="auto", fp8_ffn=0, expert_parallel=0, ep_capacity=4.0, export_hf=1, device="auto", cuda_graphs=1)
+ENGINE_DEFAULTS = dict(grad_sync="auto", fp8_ffn=0, expert_parallel=0, ep_capacity=4.0, export_hf=1, device="auto", cuda_graphs=1, overlap_wgrad=1)
 
 # Everything that shapes the model, the data stream or the schedule must be unchanged on resume.
 RESUME_KEYS = (
@@ -337,11 +337,18 @@ class Trainer:
         self.use_graphs = bool(getattr(a, "cuda_graphs", 1)) and dev.type == "cuda" and not getattr(a, "grad_ckpt", 0)
         self._graphs = {}
         self.replayed_launches = 0            # kernels of this library executed through graph replays
+        if dev.type == "cuda":
+            from .ops.backend import WGRAD_STREAM
+            WGRAD_STREAM.enabled = bool(getattr(a, "overlap_wgrad", 1))   # weight gradients on a second stream during backward
 
     def close(self):
         """Release peer mappings and detach the expert-parallel context from the kernel backend."""
         from .models import modeling
         backend = modeling.get_backend()
+        if self.dev.type == "cuda":
+            from .ops.backend import WGRAD_STREAM
+            WGRAD_STREAM.join()
+            WGRAD_STREAM.enabled = False
         if backend is not None and getattr(backend, "ep", None) is not None:
             backend.ep = None
         self._graphs = {}
@@ -355,6 +362,12 @@ class Trainer:
         aux_c, mtp_c, kl_c = self.coefficients()
         return (ce + aux_c * aux + mtp_c * mtp + kl_c * kl) / accum, torch.stack(
             [ce.detach().float(), aux.detach().float(), mtp.detach().float(), kl.detach().float()])
+
+    def _join_weight_gradients(self):
+        """Weight-gradient GEMMs run on a second stream during backward (see q38.ops.backend._SideStream); wait for them."""
+        if self.dev.type == "cuda":
+            from .ops.backend import WGRAD_STREAM
+            WGRAD_STREAM.join()
 
     def _captured_micro_step(self, x, y, accum, dense):
         """Forward + backward of one micro-step through a CUDA graph (captured on first use of this configuration).
@@ -374,6 +387,7 @@ class Trainer:
                     for _ in range(2):                       # warm-up: lazy initialisation must not happen inside the capture
                         loss, _ = self.micro_loss(sx, sy, accum)
                         loss.backward()
+                        self._join_weight_gradients()
                 torch.cuda.current_stream(self.dev).wait_stream(side)
                 from . import ops
                 graph = torch.cuda.CUDAGraph()
@@ -381,6 +395,7 @@ class Trainer:
                 with torch.cuda.graph(graph):
                     loss, parts = self.micro_loss(sx, sy, accum)
                     loss.backward()
+                    self._join_weight_gradients()            # the weight-gradient branch rejoins the captured stream
                 self.engine.arena.grads.copy_(saved)         # warm-up and capture passes must not leak into the gradients
                 entry = (graph, sx, sy, parts, ops.launch_count() - before)
             except Exception as exc:                         # pragma: no cover - depends on the driver
@@ -409,6 +424,7 @@ class Trainer:
                 xd, yd = x.to(self.dev, non_blocking=True), y.to(self.dev, non_blocking=True)
                 loss, parts = self.micro_loss(xd, yd, accum)
                 loss.backward()
+                self._join_weight_gradients()
             totals += parts / accum
         grad_norm = self.engine.finish_step(self.a.clip)
         return self.engine.average_metrics(torch.cat([totals, grad_norm.detach().reshape(1).float()]))
@@ -438,6 +454,7 @@ def probe_micro_bs(trainer, train_data, a, log0):
                 x, y = sample_batch(rng, train_data, m, a.seq, dev)
                 loss, _ = trainer.micro_loss(x, y, 1)
                 loss.backward()
+                trainer._join_weight_gradients()
                 del x, y, loss
             torch.cuda.synchronize(dev)
             peak = torch.cuda.max_memory_allocated(dev)

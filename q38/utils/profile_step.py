@@ -82,7 +82,7 @@ def main(argv=None):
         loss, f = timed(forward)
         b = o = 0.0
         if a.mode == "train":
-            _, b = timed(loss.backward)
+            _, b = timed(lambda: (loss.backward(), tr._join_weight_gradients()))
             _, o = timed(lambda: tr.engine.finish_step(train["clip"]))
         if record:
             phases["forward_ms"].append(f), phases["backward_ms"].append(b), phases["optimizer_ms"].append(o)
