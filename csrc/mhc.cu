@@ -428,7 +428,8 @@ template <typename GT, int NQ>
 __global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_rows_kernel(const GT* __restrict__ dxout, const float* __restrict__ X,
                                                                       const float* __restrict__ norm_w, const float* __restrict__ coef,
                                                                       const float* __restrict__ rstd_save, float* __restrict__ dcoef,
-                                                                      float* __restrict__ dxin_out, float* __restrict__ dnorm_w, int T, int h) {
+                                                                      float* __restrict__ dxin_out, float* __restrict__ dnorm_w,
+                                                                      __nv_bfloat16* __restrict__ xbf, int T, int h) {
   extern __shared__ float sm[];
   float* dnw_s = sm;                   // [h]
   for (int i = threadIdx.x; i < h; i += blockDim.x) dnw_s[i] = 0.f;
@@ -441,6 +442,15 @@ __global__ void __launch_bounds__(32 * RW, 3) mhc_pre_bwd_rows_kernel(const GT* 
     const float* Xt = X + (size_t)t * NB * h;
     float4 x[NB][NQ];
     load_row<NQ>(Xt, h, h4, lane, x);
+    // bf16 copy of the row: the operand of the weight-gradient GEMM dA = dL^T X (saves a separate conversion pass over X)
+#pragma unroll
+    for (int jj = 0; jj < NQ; ++jj) {
+      const int q = lane + 32 * jj;
+      if (q < h4) {
+#pragma unroll
+        for (int n = 0; n < NB; ++n) store4(xbf + ((size_t)t * NB + n) * h + 4 * q, x[n][jj]);
+      }
+    }
     const float cv = lane < 4 ? coef[(size_t)t * NCOEF + lane] : 0.f;
     const float p0 = __shfl_sync(0xffffffffu, cv, 0), p1 = __shfl_sync(0xffffffffu, cv, 1), p2 = __shfl_sync(0xffffffffu, cv, 2),
                 p3 = __shfl_sync(0xffffffffu, cv, 3);
@@ -663,7 +673,7 @@ std::vector<at::Tensor> mhc_post_bwd(const at::Tensor& dXo, const at::Tensor& X,
   return {dy, dcoef};
 }
 
-// Returns {dLraw [T,r], c1 [T], dxin [T,h], dBw [24,r], dbias [27], dnorm_w [h]}; dcoef is completed in place.
+// Returns {dLraw [T,r], c1 [T], dxin [T,h], dBw [24,r], dbias [27], dnorm_w [h], bf16 copy of X [T,4h]}; dcoef is completed in place.
 std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor& X, const at::Tensor& Lraw, const at::Tensor& Bw,
                                       const at::Tensor& b_pre, const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas,
                                       const at::Tensor& norm_w, const at::Tensor& coef, const at::Tensor& z, const at::Tensor& inv,
@@ -679,9 +689,11 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
   const int nq = (h / 4 + 31) / 32;
   if (h % 4 == 0 && r <= 96 && nq <= 8) {
     auto dlin = at::empty({T, NCOEF}, f32);
+    auto xbf = at::empty({T, NB * h}, f32.dtype(at::kBFloat16));
     const int grid_r = std::min((T + RW - 1) / RW, 3 * kNumSMs);
 #define Q38_ROWS(GT, NQ) mhc_pre_bwd_rows_kernel<GT, NQ><<<grid_r, 32 * RW, h * sizeof(float), stream>>>((const GT*)dxout.data_ptr(), X.data_ptr<float>(), \
-      norm_w.data_ptr<float>(), coef.data_ptr<float>(), rstd.data_ptr<float>(), dcoef.data_ptr<float>(), dxin.data_ptr<float>(), dnw.data_ptr<float>(), T, h)
+      norm_w.data_ptr<float>(), coef.data_ptr<float>(), rstd.data_ptr<float>(), dcoef.data_ptr<float>(), dxin.data_ptr<float>(), dnw.data_ptr<float>(), \
+      (__nv_bfloat16*)xbf.data_ptr(), T, h)
 #define Q38_ROWS_NQ(GT) switch (nq) { case 1: Q38_ROWS(GT, 1); break; case 2: Q38_ROWS(GT, 2); break; case 3: Q38_ROWS(GT, 3); break; case 4: Q38_ROWS(GT, 4); break; \
       case 5: Q38_ROWS(GT, 5); break; case 6: Q38_ROWS(GT, 6); break; default: Q38_ROWS(GT, 8); break; }
     if (dxout.scalar_type() == at::kBFloat16) Q38_ROWS_NQ(__nv_bfloat16) else Q38_ROWS_NQ(float)
@@ -698,7 +710,7 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
                                                                                                   dBw.data_ptr<float>(), T, r);
     C10_CUDA_KERNEL_LAUNCH_CHECK();
     count_launch();
-    return {dLraw, c1, dxin, dBw, dbias, dnw};
+    return {dLraw, c1, dxin, dBw, dbias, dnw, xbf};
   }
   const size_t smem = (2 * NCOEF * r + h + 32 + WARPS * h + WARPS * NCOEF) * sizeof(float);
   const int grid = (T + WARPS - 1) / WARPS;
@@ -711,7 +723,7 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
 #undef LAUNCH
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
-  return {dLraw, c1, dxin, dBw, dbias, dnw};
+  return {dLraw, c1, dxin, dBw, dbias, dnw, X.reshape({T, NB * h}).to(at::kBFloat16)};
 }
 
 void mhc_pre_bwd_c(at::Tensor& dX, const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& dxin, const at::Tensor& coef, const at::Tensor& c1) {

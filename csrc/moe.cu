@@ -281,6 +281,7 @@ struct GroupedArgs {
   const int* sched;        // tile schedule (EPI_STORE / SWIGLU / DSWIGLU)
   const int* offsets;      // expert row offsets [E+1] (EPI_WGRAD)
   int bn;                  // UMMA N (multiple of 16, <= 256); for SWIGLU the expert width f
+  int bn_alloc;            // rows of the B tile in shared memory: bn, rounded up to whole 64-wide boxes when B is MN-major
   int stages;
   int K;                   // reduction length (not used by WGRAD)
   int N;                   // valid output columns per expert
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
   const uint32_t raw = ptx::smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   const int nacc = EPI == EPI_SWIGLU ? 2 : 1;
-  const int A_BYTES = G_BM * G_BK * 2, B_BYTES = nacc * p.bn * G_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  const int A_BYTES = G_BM * G_BK * 2, B_BYTES = nacc * p.bn_alloc * G_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * STAGE_BYTES);
   uint64_t* empty = full + p.stages;
   uint64_t* acc_ready = empty + p.stages;
@@ -360,9 +361,9 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
           ptx::tma_load_3d(a_dst, &tmA, &full[s], k0, a_row0, 0);
         }
         if (EPI == EPI_WGRAD) {            // B MN-major, rows = the same sorted rows as A
-          for (int i = 0; i < p.bn / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], n0 + 64 * i, k0, 0);
+          for (int i = 0; i < p.bn_alloc / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], n0 + 64 * i, k0, 0);
         } else if (B_MN) {                 // B_e stored [K, N]: row = expert * K_total + k
-          for (int i = 0; i < p.bn / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], n0 + 64 * i, b_row_base + k0, 0);
+          for (int i = 0; i < p.bn_alloc / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], n0 + 64 * i, b_row_base + k0, 0);
         } else if (EPI == EPI_SWIGLU) {    // gate rows [0,f) and up rows [f,2f) of expert e
           ptx::tma_load_3d(b_dst, &tmB, &full[s], k0, b_row_base, 0);
           ptx::tma_load_3d(b_dst + p.bn * G_BK * 2, &tmB, &full[s], k0, b_row_base + p.bn, 0);
@@ -383,7 +384,7 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
         if (valid < G_BK) {
           // MN-major box = 64 K-rows of 128 bytes: rows >= valid hold another expert's data and are cleared
           // both operands: rows past the expert's range may be another expert's rows or never-written buffer space
-          const int boxes = G_BM / 64 + p.bn / 64;               // the B boxes follow the A boxes in the stage
+          const int boxes = G_BM / 64 + p.bn_alloc / 64;         // the B boxes follow the A boxes in the stage
           for (int i = lane; i < (G_BK - valid) * 8 * boxes; i += 32) {
             const int box = i / ((G_BK - valid) * 8), rem = i % ((G_BK - valid) * 8);
             *reinterpret_cast<uint4*>(a_tile + box * 8192 + (valid + rem / 8) * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
@@ -528,18 +529,36 @@ __global__ void __launch_bounds__(G_THREADS) grouped_gemm_kernel(const __grid_co
 }
 
 // ---- host ----------------------------------------------------------------------------------------------------------------
-static int pick_stages(int bn, int nacc) {
-  const int stage = G_BM * G_BK * 2 + nacc * bn * G_BK * 2;
-  int s = (200 * 1024) / stage;
-  const int cap = nacc == 1 ? 3 : 4;          // three 32 KB stages let two single-accumulator CTAs share an SM
-  return s > cap ? cap : (s < 2 ? 2 : s);
+static int pick_stages(int bn_alloc, int nacc) {
+  const int stage = G_BM * G_BK * 2 + nacc * bn_alloc * G_BK * 2;
+  if (nacc == 1) {                              // two single-accumulator CTAs share an SM: one runs its epilogue while the other multiplies
+    const int s = (110 * 1024) / stage;
+    return s > 3 ? 3 : (s < 2 ? 2 : s);
+  }
+  const int s = (200 * 1024) / stage;
+  return s > 4 ? 4 : (s < 2 ? 2 : s);
+}
+
+// Width of the N tile of a grouped product: a multiple of 16 up to 192 (two CTAs x 256 TMEM columns per SM) that covers N with the
+// least tile time, a tile costing its width plus a fixed part worth about 32 columns.  144 -> 144, 576 -> 192.
+static int pick_group_bn(int N) {
+  if (N <= 64) return 64;
+  int best = 128;
+  double best_cost = 1e30;
+  for (int bn = 192; bn >= 64; bn -= 16) {
+    const int tiles = (N + bn - 1) / bn;
+    const double cost = tiles * (bn + 32.0);
+    if (cost < best_cost - 1e-9) { best = bn; best_cost = cost; }
+  }
+  return best;
 }
 
 template <int EPI, bool A_MN, bool B_MN>
 static void launch_grouped(const CUtensorMap& ta, const CUtensorMap& tb, GroupedArgs p, dim3 grid, int nacc, cudaStream_t stream) {
   auto kernel = grouped_gemm_kernel<EPI, A_MN, B_MN>;
-  p.stages = pick_stages(p.bn, nacc);
-  const int smem = p.stages * (G_BM * G_BK * 2 + nacc * p.bn * G_BK * 2) + 1024 + 256;
+  p.bn_alloc = (B_MN || EPI == EPI_WGRAD) ? (p.bn + 63) / 64 * 64 : p.bn;
+  p.stages = pick_stages(p.bn_alloc, nacc);
+  const int smem = p.stages * (G_BM * G_BK * 2 + nacc * p.bn_alloc * G_BK * 2) + 1024 + 256;
   static int configured = 0;
   if (configured < smem) { C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); configured = 227 * 1024; }
   kernel<<<grid, G_THREADS, smem, stream>>>(ta, tb, p);
@@ -575,7 +594,7 @@ void moe_grouped_gemm_impl(const at::Tensor& rows, const at::Tensor& weight, at:
   const int P = rows.size(0), K = rows.size(1), E = weight.size(0);
   const int N = b_mn_major ? weight.size(2) : weight.size(1);
   TORCH_CHECK((b_mn_major ? weight.size(1) : weight.size(2)) == K && (ret_rank || out.size(0) == P) && out.size(1) == N, "moe_grouped_gemm: shape mismatch");
-  const int bn = N <= 64 ? 64 : 128;
+  const int bn = pick_group_bn(N);
   const int max_tiles = (sched.numel() - 1) / 3;
   CUtensorMap ta = make_tmap_bf16(rows.data_ptr(), K, P, 1, K, 0, G_BM);
   CUtensorMap tb = b_mn_major ? make_tmap_bf16(weight.data_ptr(), N, (int64_t)E * K, 1, N, 0, 64)
@@ -612,7 +631,7 @@ void moe_grouped_dswiglu(const at::Tensor& dy, const at::Tensor& w_down, const a
   const c10::cuda::CUDAGuard guard(dy.device());
   const int P = dy.size(0), K = dy.size(1), E = w_down.size(0), f = w_down.size(2);
   TORCH_CHECK(w_down.size(1) == K && gu.size(1) == 2 * f && dgu.size(1) == 2 * f && f % 8 == 0, "moe_grouped_dswiglu: shape mismatch");
-  const int bn = f <= 64 ? 64 : 128;
+  const int bn = pick_group_bn(f);
   const int max_tiles = (sched.numel() - 1) / 3;
   CUtensorMap ta = make_tmap_bf16(dy.data_ptr(), K, P, 1, K, 0, G_BM);
   CUtensorMap tb = make_tmap_bf16(w_down.data_ptr(), f, (int64_t)E * K, 1, f, 0, 64);
@@ -629,7 +648,7 @@ void moe_grouped_wgrad(const at::Tensor& a, const at::Tensor& b, at::Tensor& gra
   const c10::cuda::CUDAGuard guard(a.device());
   const int P = a.size(0), M = a.size(1), N = b.size(1), E = grad.size(0);
   TORCH_CHECK(b.size(0) == P && grad.size(1) == M && grad.size(2) == N && M % 8 == 0 && N % 8 == 0, "moe_grouped_wgrad: shape mismatch");
-  const int bn = N <= 64 ? 64 : 128;
+  const int bn = pick_group_bn(N);
   CUtensorMap ta = make_tmap_bf16(a.data_ptr(), M, P, 1, M, 0, 64);
   CUtensorMap tb = make_tmap_bf16(b.data_ptr(), N, P, 1, N, 0, 64);
   GroupedArgs p{};

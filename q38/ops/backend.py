@@ -206,12 +206,12 @@ class _MhcPreNorm(torch.autograd.Function):
         if dcoef is None:
             dcoef = torch.zeros_like(coef)
         dcoef = dcoef.contiguous()
-        dLraw, c1, dxin, dBw, dbias, dnw = ops.mhc_pre_bwd_a(
+        dLraw, c1, dxin, dBw, dbias, dnw, Xbf = ops.mhc_pre_bwd_a(
             dxout.reshape(T, h).contiguous(), Xc.view(T, n, h), Lraw, B_w.float().contiguous(), b_pre.float().contiguous(),
             b_post.float().contiguous(), b_res.float().contiguous(), alphas.float().contiguous(), norm_w.float().contiguous(),
             coef, z, inv, rstd, dcoef, ctx.iters)
         Xf = Xc.view(T, n * h)
-        dA = _mhc_weight_grad(dLraw, Xf, A_w)
+        dA = _mhc_weight_grad(dLraw, Xf if os.environ.get("Q38_MHC_FP32_GEMM") else Xbf, A_w)
         dX = _mm32(dLraw, A_w, 'nn')                          # G, completed in place below
         dXo = ctx.link.dXo if ctx.link.dXo is not None else torch.zeros_like(Xf)
         ctx.link.dXo = None
