@@ -13,6 +13,10 @@ TORCH_LIBRARY(q38, m) {
         [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool amn, bool bmn, double alpha, bool acc, at::Tensor& err, int64_t splits) {
           q38::gemm_bf16_persistent(a, b, c, amn, bmn, alpha, acc, err, splits);
         });
+  m.def("qsa_headprep_fwd(Tensor src, Tensor? w, Tensor cos, Tensor sin, float eps, bool split_gate) -> Tensor[]", &q38::qsa_headprep_fwd);
+  m.def("qsa_headprep_bwd(Tensor dout, Tensor? dgate, Tensor src, Tensor? w, Tensor cos, Tensor sin, Tensor rstd) -> Tensor[]", &q38::qsa_headprep_bwd);
+  m.def("gate_add_fwd(Tensor routed, Tensor shared, Tensor logit) -> Tensor", &q38::gate_add_fwd);
+  m.def("gate_add_bwd(Tensor dy, Tensor shared, Tensor logit) -> Tensor[]", &q38::gate_add_bwd);
   m.def("ngram_fwd(Tensor ids, Tensor emb2, Tensor emb3, Tensor norm_w, int vocab, int eos, float eps) -> Tensor[]", &q38::ngram_fwd);
   m.def("ngram_bwd(Tensor de, Tensor rows, Tensor emb2, Tensor emb3, Tensor norm_w, Tensor rstd, Tensor(a!) g2, Tensor(b!) g3) -> Tensor", &q38::ngram_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps, bool out_bf16) -> Tensor[]");

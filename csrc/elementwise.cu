@@ -101,18 +101,50 @@ std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, c
 }
 
 // ---- gated RMSNorm over one 64-wide head: y = bf16( w * bf16(xhat) * silu(gate) ) ------------------------------------
-// One warp per row, two elements per lane (dim is fixed at 64 by the model's linear_value_head_dim).
+// Eight lanes per row, eight elements (16 bytes) per lane, so a warp moves four rows per access (dim is fixed at 64 by the
+// model's linear_value_head_dim).  Row reductions are three xor-shuffles inside the 8-lane group.
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(h[i]); v[2 * i + 1] = __high2float(h[i]); }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 out;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return out;
+}
+__device__ __forceinline__ float group8_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
 __global__ void __launch_bounds__(256) gated_rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
                                                                  const float* __restrict__ w, __nv_bfloat16* __restrict__ y, int rows, float eps) {
-  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  const __nv_bfloat162 xv = reinterpret_cast<const __nv_bfloat162*>(x + (size_t)row * 64)[lane];
-  const __nv_bfloat162 gv = reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)row * 64)[lane];
-  const float x0 = __low2float(xv), x1 = __high2float(xv);
-  const float r = rsqrtf(warp_sum(x0 * x0 + x1 * x1) / 64.f + eps);
-  const float y0 = w[2 * lane] * bf16_round(x0 * r) * siluf_(__low2float(gv));
-  const float y1 = w[2 * lane + 1] * bf16_round(x1 * r) * siluf_(__high2float(gv));
-  reinterpret_cast<__nv_bfloat162*>(y + (size_t)row * 64)[lane] = __floats2bfloat162_rn(y0, y1);
+  const int sub = threadIdx.x & 7;
+  const long long row = ((long long)blockIdx.x * 256 + threadIdx.x) >> 3;
+  const bool live = row < rows;
+  float xv[8], gv[8], wv[8];
+  if (live) {
+    unpack8(reinterpret_cast<const uint4*>(x + row * 64)[sub], xv);
+    unpack8(reinterpret_cast<const uint4*>(gate + row * 64)[sub], gv);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xv[i] = gv[i] = 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) wv[i] = w[8 * sub + i];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss += xv[i] * xv[i];
+  const float r = rsqrtf(group8_sum(ss) / 64.f + eps);
+  float out[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = wv[i] * bf16_round(xv[i] * r) * siluf_(gv[i]);
+  if (live) reinterpret_cast<uint4*>(y + row * 64)[sub] = pack8(out);
 }
 
 __global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
@@ -122,31 +154,120 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const __nv_bfloa
   __shared__ float dw_acc[64];
   if (threadIdx.x < 64) dw_acc[threadIdx.x] = 0.f;
   __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float dw0 = 0.f, dw1 = 0.f;
-  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
-    const __nv_bfloat162 xv = reinterpret_cast<const __nv_bfloat162*>(x + (size_t)row * 64)[lane];
-    const __nv_bfloat162 gv = reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)row * 64)[lane];
-    const __nv_bfloat162 dv = reinterpret_cast<const __nv_bfloat162*>(dy + (size_t)row * 64)[lane];
-    const float x0 = __low2float(xv), x1 = __high2float(xv), g0 = __low2float(gv), g1 = __high2float(gv);
-    const float d0 = __low2float(dv), d1 = __high2float(dv);
-    const float r = rsqrtf(warp_sum(x0 * x0 + x1 * x1) / 64.f + eps);
-    const float h0 = x0 * r, h1 = x1 * r;
-    const float s0 = sigmoidf_(g0), s1 = sigmoidf_(g1);
-    const float w0 = w[2 * lane], w1 = w[2 * lane + 1];
-    // y = w * xhat * g * s
-    dw0 += d0 * h0 * g0 * s0; dw1 += d1 * h1 * g1 * s1;
-    const float dh0 = d0 * w0 * g0 * s0, dh1 = d1 * w1 * g1 * s1;
-    const float dot = warp_sum(dh0 * h0 + dh1 * h1) / 64.f;
-    reinterpret_cast<__nv_bfloat162*>(dx + (size_t)row * 64)[lane] = __floats2bfloat162_rn(r * (dh0 - h0 * dot), r * (dh1 - h1 * dot));
-    // d silu(g) = s * (1 + g * (1 - s))
-    reinterpret_cast<__nv_bfloat162*>(dgate + (size_t)row * 64)[lane] =
-        __floats2bfloat162_rn(d0 * w0 * h0 * s0 * (1.f + g0 * (1.f - s0)), d1 * w1 * h1 * s1 * (1.f + g1 * (1.f - s1)));
+  const int sub = threadIdx.x & 7;
+  float wv[8], dwv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { wv[i] = w[8 * sub + i]; dwv[i] = 0.f; }
+  const long long stride = ((long long)gridDim.x * 256) >> 3;
+  const long long first = ((long long)blockIdx.x * 256 + threadIdx.x) >> 3;
+  // every 8-lane group walks rows first, first + stride, ...; the loop bound is uniform per warp up to the last iteration,
+  // where finished groups keep shuffling on zeros
+  for (long long base = first - (threadIdx.x >> 3 & 3); base < rows; base += stride) {
+    const long long row = base + (threadIdx.x >> 3 & 3);
+    const bool live = row < rows;
+    float xv[8], gv[8], dv[8];
+    if (live) {
+      unpack8(reinterpret_cast<const uint4*>(x + row * 64)[sub], xv);
+      unpack8(reinterpret_cast<const uint4*>(gate + row * 64)[sub], gv);
+      unpack8(reinterpret_cast<const uint4*>(dy + row * 64)[sub], dv);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xv[i] = gv[i] = dv[i] = 0.f;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += xv[i] * xv[i];
+    const float r = rsqrtf(group8_sum(ss) / 64.f + eps);
+    float hv[8], sv[8], dh[8], dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      hv[i] = xv[i] * r;
+      sv[i] = sigmoidf_(gv[i]);
+      dwv[i] += dv[i] * hv[i] * gv[i] * sv[i];                 // y = w * xhat * g * s
+      dh[i] = dv[i] * wv[i] * gv[i] * sv[i];
+      dot += dh[i] * hv[i];
+    }
+    dot = group8_sum(dot) / 64.f;
+    float ox[8], og[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ox[i] = r * (dh[i] - hv[i] * dot);
+      og[i] = dv[i] * wv[i] * hv[i] * sv[i] * (1.f + gv[i] * (1.f - sv[i]));   // d silu(g) = s (1 + g (1 - s))
+    }
+    if (live) {
+      reinterpret_cast<uint4*>(dx + row * 64)[sub] = pack8(ox);
+      reinterpret_cast<uint4*>(dgate + row * 64)[sub] = pack8(og);
+    }
   }
-  atomicAdd(&dw_acc[2 * lane], dw0);
-  atomicAdd(&dw_acc[2 * lane + 1], dw1);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) atomicAdd(&dw_acc[8 * sub + i], dwv[i]);
   __syncthreads();
   if (threadIdx.x < 64) atomicAdd(&dw[threadIdx.x], dw_acc[threadIdx.x]);
+}
+
+// ---- shared-expert merge: out = routed + sigmoid(logit_t) * shared  (one warp per token row, 16-byte accesses) ------------
+__global__ void __launch_bounds__(256) gate_add_fwd_kernel(const __nv_bfloat16* __restrict__ routed, const __nv_bfloat16* __restrict__ shared,
+                                                            const __nv_bfloat16* __restrict__ logit, __nv_bfloat16* __restrict__ out, int T, int h) {
+  const int lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float s = bf16_round(sigmoidf_(__bfloat162float(logit[t])));
+  for (int c = lane; c < h / 8; c += 32) {
+    float a[8], b[8], o[8];
+    unpack8(reinterpret_cast<const uint4*>(routed + t * h)[c], a);
+    unpack8(reinterpret_cast<const uint4*>(shared + t * h)[c], b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = a[i] + bf16_round(s * b[i]);
+    reinterpret_cast<uint4*>(out + t * h)[c] = pack8(o);
+  }
+}
+
+// d(shared) = dy * sigmoid(logit);  d(logit)_t = sigmoid'(logit) * <dy_t, shared_t>;  d(routed) = dy needs no kernel
+__global__ void __launch_bounds__(256) gate_add_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ shared,
+                                                            const __nv_bfloat16* __restrict__ logit, __nv_bfloat16* __restrict__ dshared,
+                                                            __nv_bfloat16* __restrict__ dlogit, int T, int h) {
+  const int lane = threadIdx.x & 31;
+  const long long t = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const float s = bf16_round(sigmoidf_(__bfloat162float(logit[t])));
+  float dot = 0.f;
+  for (int c = lane; c < h / 8; c += 32) {
+    float g[8], b[8], o[8];
+    unpack8(reinterpret_cast<const uint4*>(dy + t * h)[c], g);
+    unpack8(reinterpret_cast<const uint4*>(shared + t * h)[c], b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { o[i] = g[i] * s; dot += g[i] * b[i]; }
+    reinterpret_cast<uint4*>(dshared + t * h)[c] = pack8(o);
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) dlogit[t] = __float2bfloat16_rn(dot * s * (1.f - s));
+}
+
+at::Tensor gate_add_fwd(const at::Tensor& routed, const at::Tensor& shared, const at::Tensor& logit) {
+  TORCH_CHECK(routed.is_cuda() && routed.scalar_type() == at::kBFloat16 && routed.is_contiguous() && shared.is_contiguous() && logit.is_contiguous() &&
+                  routed.dim() == 2 && routed.sizes() == shared.sizes() && logit.numel() == routed.size(0) && routed.size(1) % 8 == 0,
+              "gate_add_fwd: contiguous bf16 [T,h] (h a multiple of 8) and [T,1] required");
+  const c10::cuda::CUDAGuard guard(routed.device());
+  const int T = routed.size(0), h = routed.size(1);
+  auto out = at::empty_like(routed);
+  if (T) gate_add_fwd_kernel<<<(T + 7) / 8, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)routed.data_ptr(), (const __nv_bfloat16*)shared.data_ptr(), (const __nv_bfloat16*)logit.data_ptr(), (__nv_bfloat16*)out.data_ptr(), T, h);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return out;
+}
+
+std::vector<at::Tensor> gate_add_bwd(const at::Tensor& dy, const at::Tensor& shared, const at::Tensor& logit) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && shared.is_contiguous() && dy.sizes() == shared.sizes(), "gate_add_bwd: bad inputs");
+  const c10::cuda::CUDAGuard guard(dy.device());
+  const int T = dy.size(0), h = dy.size(1);
+  auto dshared = at::empty_like(shared), dlogit = at::empty_like(logit);
+  if (T) gate_add_bwd_kernel<<<(T + 7) / 8, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)shared.data_ptr(), (const __nv_bfloat16*)logit.data_ptr(), (__nv_bfloat16*)dshared.data_ptr(),
+      (__nv_bfloat16*)dlogit.data_ptr(), T, h);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {dshared, dlogit};
 }
 
 at::Tensor gated_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& gate, const at::Tensor& w, double eps) {
@@ -155,7 +276,7 @@ at::Tensor gated_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& gate, const 
   const c10::cuda::CUDAGuard guard(x.device());
   const int rows = x.numel() / 64;
   auto y = at::empty_like(x);
-  if (rows) gated_rmsnorm_fwd_kernel<<<(rows + 7) / 8, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+  if (rows) gated_rmsnorm_fwd_kernel<<<(rows + 31) / 32, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       (const __nv_bfloat16*)x.data_ptr(), (const __nv_bfloat16*)gate.data_ptr(), w.data_ptr<float>(), (__nv_bfloat16*)y.data_ptr(), rows, (float)eps);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
@@ -168,7 +289,7 @@ std::vector<at::Tensor> gated_rmsnorm_bwd(const at::Tensor& dy, const at::Tensor
   const int rows = x.numel() / 64;
   auto dx = at::empty_like(x), dgate = at::empty_like(gate);
   auto dw = at::zeros({64}, x.options().dtype(at::kFloat));
-  if (rows) gated_rmsnorm_bwd_kernel<<<std::min((rows + 7) / 8, kNumSMs * 8), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+  if (rows) gated_rmsnorm_bwd_kernel<<<std::min((rows + 31) / 32, kNumSMs * 8), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       (const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)x.data_ptr(), (const __nv_bfloat16*)gate.data_ptr(), w.data_ptr<float>(),
       (__nv_bfloat16*)dx.data_ptr(), (__nv_bfloat16*)dgate.data_ptr(), dw.data_ptr<float>(), rows, (float)eps);
   C10_CUDA_KERNEL_LAUNCH_CHECK();

@@ -23,6 +23,15 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_m
 void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
                           bool accumulate, at::Tensor& err, int64_t splits);
 
+// qsa_prep.cu
+std::vector<at::Tensor> qsa_headprep_fwd(const at::Tensor& src, const c10::optional<at::Tensor>& w, const at::Tensor& cosv, const at::Tensor& sinv, double eps,
+                                         bool split_gate);
+std::vector<at::Tensor> qsa_headprep_bwd(const at::Tensor& dout, const c10::optional<at::Tensor>& dgate, const at::Tensor& src, const c10::optional<at::Tensor>& w,
+                                         const at::Tensor& cosv, const at::Tensor& sinv, const at::Tensor& rstd);
+
+at::Tensor gate_add_fwd(const at::Tensor& routed, const at::Tensor& shared, const at::Tensor& logit);
+std::vector<at::Tensor> gate_add_bwd(const at::Tensor& dy, const at::Tensor& shared, const at::Tensor& logit);
+
 // ngram.cu
 std::vector<at::Tensor> ngram_fwd(const at::Tensor& ids, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w, int64_t vocab,
                                   int64_t eos, double eps);

@@ -337,6 +337,62 @@ class _IndexerKL(torch.autograd.Function):
         return dqi * dkl.to(dqi.dtype), dki * dkl.to(dki.dtype), dwi * dkl, None, None, None, None
 
 
+class _GateAdd(torch.autograd.Function):
+    """routed + sigmoid(logit) * shared for [T,h] bf16 rows and one logit per row (the shared-expert merge of the MoE block)."""
+
+    @staticmethod
+    def forward(ctx, routed, shared, logit):
+        shared, logit = shared.contiguous(), logit.contiguous()
+        ctx.save_for_backward(shared, logit)
+        return load().gate_add_fwd(routed.contiguous(), shared, logit)
+
+    @staticmethod
+    def backward(ctx, dy):
+        shared, logit = ctx.saved_tensors
+        dy = dy.contiguous()
+        dshared, dlogit = load().gate_add_bwd(dy, shared, logit)
+        return dy, dshared, dlogit
+
+
+class _HeadPrep(torch.autograd.Function):
+    """Projection output [B,S,H,64] (or [B,S,H,128] = q | gate per head) -> (heads [B,H,S,64] after the optional per-head
+    zero-centred RMSNorm and the partial rotary embedding, gate [B,S,H*64] or None), one kernel each way (csrc/qsa_prep.cu)."""
+
+    @staticmethod
+    def forward(ctx, src, weight, cos, sin, eps):
+        src = src.contiguous()
+        split = src.shape[-1] == 128
+        w = None if weight is None else weight.float().contiguous()
+        cos, sin = cos.float().contiguous(), sin.float().contiguous()
+        out, gate, rstd = load().qsa_headprep_fwd(src, w, cos, sin, eps, split)
+        ctx.save_for_backward(src, cos, sin, rstd, *(() if weight is None else (weight,)))
+        ctx.split, ctx.has_w = split, weight is not None
+        if split:
+            return out, gate
+        ctx.mark_non_differentiable(gate)
+        return out, gate
+
+    @staticmethod
+    def backward(ctx, dout, dgate):
+        src, cos, sin, rstd, *rest = ctx.saved_tensors
+        weight = rest[0] if ctx.has_w else None
+        w = None if weight is None else weight.float().contiguous()
+        if dout is None:
+            dout = torch.zeros(src.shape[0], src.shape[2], src.shape[1], 64, dtype=torch.bfloat16, device=src.device)
+        if ctx.split and dgate is None:
+            dgate = torch.zeros(src.shape[0], src.shape[1], src.shape[2] * 64, dtype=torch.bfloat16, device=src.device)
+        dsrc, dw = load().qsa_headprep_bwd(dout.to(torch.bfloat16).contiguous(), dgate.to(torch.bfloat16).contiguous() if ctx.split else None,
+                                           src, w, cos, sin, rstd)
+        return dsrc, (None if weight is None else dw.to(weight.dtype)), None, None, None
+
+
+def _head_prep(src, norm, cos, sin):
+    """`src` [B,S,H,64|128] bf16; `norm` a zero-centred RMSNorm module or None.  Returns (heads, gate-or-None)."""
+    weight, eps = (None, 0.0) if norm is None else (norm.weight, float(norm.eps))
+    out, gate = _HeadPrep.apply(src, weight, cos, sin, eps)
+    return out, (gate if src.shape[-1] == 128 else None)
+
+
 class _BlockAttention(torch.autograd.Function):
     """GQA attention over the selected 64-token key blocks (or all causal blocks when `count` is None).
     q [B,nq,S,64], k/v [B,nkv,S,64] -> o [B,S,nq,64]."""
@@ -587,8 +643,12 @@ class Backend:
         from ..models import modeling
         B, S, _ = x.shape
         NI, D = indexer.n_ih, indexer.d_ih
-        qi = modeling.apply_rope(self.linear(x, indexer.wq.weight).view(B, S, NI, D).transpose(1, 2), cos, sin).contiguous()
-        ki = modeling.apply_rope(self.linear(x, indexer.wk.weight).view(B, S, 1, D).transpose(1, 2), cos, sin)[:, 0].contiguous()
+        if D == 64 and cos.shape[-1] == 16 and x.dtype == torch.bfloat16:
+            qi = _head_prep(self.linear(x, indexer.wq.weight).view(B, S, NI, D), None, cos, sin)[0]
+            ki = _head_prep(self.linear(x, indexer.wk.weight).view(B, S, 1, D), None, cos, sin)[0][:, 0]
+        else:
+            qi = modeling.apply_rope(self.linear(x, indexer.wq.weight).view(B, S, NI, D).transpose(1, 2), cos, sin).contiguous()
+            ki = modeling.apply_rope(self.linear(x, indexer.wk.weight).view(B, S, 1, D).transpose(1, 2), cos, sin)[:, 0].contiguous()
         wi = (self.linear(x, indexer.ww.weight).float() * NI ** -0.5).contiguous()
         if q_main is not None:
             return _IndexerKL.apply(qi, ki, wi, q_main, k_main, main_scale, D ** -0.5)
@@ -605,9 +665,13 @@ class Backend:
         if x.dtype != torch.bfloat16 or hd != 64 or S % 64 or S > 8192 or (indexer is not None and (indexer.d_ih != 64 or indexer.n_ih > 4)):
             return None
         qg = self.linear(x, attn.q_proj.weight).view(B, S, -1, 2 * hd)
-        q, gate = qg[..., :hd], qg[..., hd:].reshape(B, S, -1)
-        q = modeling.apply_rope(attn.q_norm(q).transpose(1, 2), cos, sin).contiguous()
-        k = modeling.apply_rope(attn.k_norm(self.linear(x, attn.k_proj.weight).view(B, S, -1, hd)).transpose(1, 2), cos, sin).contiguous()
+        if cos.shape[-1] == 16:
+            q, gate = _head_prep(qg, attn.q_norm, cos, sin)
+            k = _head_prep(self.linear(x, attn.k_proj.weight).view(B, S, -1, hd), attn.k_norm, cos, sin)[0]
+        else:
+            q, gate = qg[..., :hd], qg[..., hd:].reshape(B, S, -1)
+            q = modeling.apply_rope(attn.q_norm(q).transpose(1, 2), cos, sin).contiguous()
+            k = modeling.apply_rope(attn.k_norm(self.linear(x, attn.k_proj.weight).view(B, S, -1, hd)).transpose(1, 2), cos, sin).contiguous()
         v = self.linear(x, attn.v_proj.weight).view(B, S, -1, hd).transpose(1, 2)
         kl = lp_blk = None
         if indexer is not None and (want_kl or not dense):
@@ -663,10 +727,12 @@ class Backend:
             routed = _ExpertsEP.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj, self.ep, self.ep.layer_index(block))
         else:
             routed = _Experts.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj)
-        shared_gate = torch.sigmoid(self.linear(x2, block.shared_expert_gate.weight))
         shared = block.shared_expert
         mid = torch.nn.functional.silu(self.linear(x2, shared.gate_proj.weight)) * self.linear(x2, shared.up_proj.weight)
-        return (routed + shared_gate * self.linear(mid, shared.down_proj.weight)).reshape(shape)
+        gate_logit = self.linear(x2, block.shared_expert_gate.weight)
+        if h % 8 == 0 and gate_logit.shape[1] == 1:
+            return _GateAdd.apply(routed, self.linear(mid, shared.down_proj.weight), gate_logit).reshape(shape)
+        return (routed + torch.sigmoid(gate_logit) * self.linear(mid, shared.down_proj.weight)).reshape(shape)
 
     @_nvtx("q38.linear_cross_entropy")
     def linear_cross_entropy(self, weight, hidden, target, reduction):

@@ -472,3 +472,51 @@ def test_ngram_embedding_matches_specification(ops):
     assert rel_err(out, ref_out) < 2e-2 and rel_err(dh, ref_dh) < 2e-2
     for name in ref_g:
         assert rel_err(g[name], ref_g[name]) < 2e-2, name
+
+
+@pytest.mark.parametrize("with_norm,split", [(True, True), (True, False), (False, False)])
+def test_qsa_head_preparation(ops, with_norm, split):
+    """Per-head zero-centred RMSNorm + partial RoPE + move to [B,H,S,64] (+ gate split) in one kernel, values and gradients."""
+    from q38.models import modeling
+    from q38.ops.backend import _head_prep
+    torch.manual_seed(14)
+    B, S, H = 2, 192, 5
+    width = 128 if split else 64
+    src = torch.randn(B, S, H, width, device="cuda").to(torch.bfloat16)
+    norm = modeling.Qwen3_8MoeRMSNorm(64).cuda() if with_norm else None
+    if norm is not None:
+        with torch.no_grad():
+            norm.weight.normal_(0, 0.2)
+    cos, sin = modeling.rope_tables(torch.arange(S, device="cuda")[None], 16, 1e7, torch.float32)
+    dq = torch.randn(B, H, S, 64, device="cuda").to(torch.bfloat16)
+    dg = torch.randn(B, S, H * 64, device="cuda").to(torch.bfloat16)
+
+    def run(fast):
+        x = src.clone().requires_grad_()
+        if norm is not None:
+            norm.weight.grad = None
+        if fast:
+            q, gate = _head_prep(x, norm, cos, sin)
+        else:
+            backend = modeling.get_backend()
+            modeling.set_backend(None)
+            try:
+                xf = x.float()
+                q = xf[..., :64]
+                q = norm(q) if norm is not None else q
+                q = modeling.apply_rope(q.transpose(1, 2), cos, sin)
+                gate = xf[..., 64:].reshape(B, S, -1) if split else None
+            finally:
+                modeling.set_backend(backend)
+        loss = (q.float() * dq.float()).sum() + ((gate.float() * dg.float()).sum() if split else 0.0)
+        loss.backward()
+        return q, gate, x.grad, (norm.weight.grad.clone() if norm is not None else None)
+
+    qa, ga, dxa, dwa = run(True)
+    qb, gb, dxb, dwb = run(False)
+    assert qa.shape == (B, H, S, 64) and rel_err(qa, qb) < 1e-2
+    assert rel_err(dxa, dxb) < 2e-2
+    if split:
+        assert torch.equal(ga.float(), gb.float().to(torch.bfloat16).float())
+    if with_norm:
+        assert rel_err(dwa, dwb) < 2e-2
