@@ -17,6 +17,9 @@ TORCH_LIBRARY(q38, m) {
   m.def("qsa_headprep_bwd(Tensor dout, Tensor? dgate, Tensor src, Tensor? w, Tensor cos, Tensor sin, Tensor rstd) -> Tensor[]", &q38::qsa_headprep_bwd);
   m.def("gate_add_fwd(Tensor routed, Tensor shared, Tensor logit) -> Tensor", &q38::gate_add_fwd);
   m.def("gate_add_bwd(Tensor dy, Tensor shared, Tensor logit) -> Tensor[]", &q38::gate_add_bwd);
+  m.def("gdn_gates_fwd(Tensor b_raw, Tensor a_raw, Tensor A_log, Tensor dt_bias) -> Tensor[]", &q38::gdn_gates_fwd);
+  m.def("gdn_gates_bwd(Tensor dbeta, Tensor dg, Tensor b_raw, Tensor a_raw, Tensor A_log, Tensor dt_bias) -> Tensor[]", &q38::gdn_gates_bwd);
+  m.def("embed_bwd(Tensor ids, Tensor dout, Tensor(a!) grad) -> ()", &q38::embed_bwd);
   m.def("ngram_fwd(Tensor ids, Tensor emb2, Tensor emb3, Tensor norm_w, int vocab, int eos, float eps) -> Tensor[]", &q38::ngram_fwd);
   m.def("ngram_bwd(Tensor de, Tensor rows, Tensor emb2, Tensor emb3, Tensor norm_w, Tensor rstd, Tensor(a!) g2, Tensor(b!) g3) -> Tensor", &q38::ngram_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps, bool out_bf16) -> Tensor[]");

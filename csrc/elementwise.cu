@@ -270,6 +270,91 @@ std::vector<at::Tensor> gate_add_bwd(const at::Tensor& dy, const at::Tensor& sha
   return {dshared, dlogit};
 }
 
+// ---- Gated DeltaNet gates: beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias), per (token, value head) ----------
+__global__ void __launch_bounds__(256) gdn_gates_fwd_kernel(const __nv_bfloat16* __restrict__ b_raw, const __nv_bfloat16* __restrict__ a_raw,
+                                                             const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                             __nv_bfloat16* __restrict__ beta, float* __restrict__ g, long long n, int H) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const int h = i % H;
+  beta[i] = __float2bfloat16_rn(sigmoidf_(__bfloat162float(b_raw[i])));
+  const float x = __bfloat162float(a_raw[i]) + dt_bias[h];
+  const float sp = x > 20.f ? x : log1pf(__expf(x));
+  g[i] = -__expf(A_log[h]) * sp;
+}
+
+// d(b) = d(beta) beta (1 - beta);  d(a) = d(g) (-exp(A_log)) sigmoid(a + dt_bias);  d(dt_bias)_h = sum_t d(a);  d(A_log)_h = sum_t d(g) g
+__global__ void __launch_bounds__(256) gdn_gates_bwd_kernel(const __nv_bfloat16* __restrict__ dbeta, const float* __restrict__ dg,
+                                                             const __nv_bfloat16* __restrict__ b_raw, const __nv_bfloat16* __restrict__ a_raw,
+                                                             const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                                                             __nv_bfloat16* __restrict__ db_raw, __nv_bfloat16* __restrict__ da_raw,
+                                                             float* __restrict__ dA_log, float* __restrict__ ddt_bias, long long rows, int H) {
+  extern __shared__ float acc[];                     // [2 * H]
+  for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) acc[i] = 0.f;
+  __syncthreads();
+  // thread -> fixed head column, walking rows: a thread's partial sums belong to one head
+  const int per_row = H, cols_per_block = (256 / per_row) * per_row;
+  if (cols_per_block > 0 && (int)threadIdx.x < cols_per_block) {
+    const int h = threadIdx.x % per_row, r0 = threadIdx.x / per_row, rstep = 256 / per_row;
+    const float na = -__expf(A_log[h]), bias = dt_bias[h];
+    float s_a = 0.f, s_l = 0.f;
+    for (long long r = (long long)blockIdx.x * rstep + r0; r < rows; r += (long long)gridDim.x * rstep) {
+      const long long i = r * H + h;
+      const float be = sigmoidf_(__bfloat162float(b_raw[i]));
+      db_raw[i] = __float2bfloat16_rn(__bfloat162float(dbeta[i]) * be * (1.f - be));
+      const float x = __bfloat162float(a_raw[i]) + bias;
+      const float sp = x > 20.f ? x : log1pf(__expf(x));
+      const float dgi = dg[i];
+      const float da = dgi * na * (x > 20.f ? 1.f : sigmoidf_(x));
+      da_raw[i] = __float2bfloat16_rn(da);
+      s_a += da;
+      s_l += dgi * na * sp;
+    }
+    atomicAdd(&acc[h], s_l);
+    atomicAdd(&acc[H + h], s_a);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { atomicAdd(&dA_log[i], acc[i]); atomicAdd(&ddt_bias[i], acc[H + i]); }
+}
+
+// b_raw, a_raw [T,H] bf16 -> {beta [T,H] bf16, g [T,H] fp32}
+std::vector<at::Tensor> gdn_gates_fwd(const at::Tensor& b_raw, const at::Tensor& a_raw, const at::Tensor& A_log, const at::Tensor& dt_bias) {
+  TORCH_CHECK(b_raw.is_cuda() && b_raw.scalar_type() == at::kBFloat16 && a_raw.scalar_type() == at::kBFloat16 && b_raw.is_contiguous() && a_raw.is_contiguous() &&
+                  b_raw.sizes() == a_raw.sizes() && A_log.scalar_type() == at::kFloat && dt_bias.scalar_type() == at::kFloat && A_log.is_contiguous() &&
+                  dt_bias.is_contiguous() && A_log.numel() == b_raw.size(-1) && dt_bias.numel() == b_raw.size(-1) && b_raw.size(-1) <= 256,
+              "gdn_gates_fwd: bf16 [..,H] projections and fp32 [H] parameters required (H <= 256)");
+  const c10::cuda::CUDAGuard guard(b_raw.device());
+  const int H = b_raw.size(-1);
+  const long long n = b_raw.numel();
+  auto beta = at::empty_like(b_raw);
+  auto g = at::empty(b_raw.sizes(), b_raw.options().dtype(at::kFloat));
+  if (n) gdn_gates_fwd_kernel<<<(unsigned)((n + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)b_raw.data_ptr(), (const __nv_bfloat16*)a_raw.data_ptr(), A_log.data_ptr<float>(), dt_bias.data_ptr<float>(),
+      (__nv_bfloat16*)beta.data_ptr(), g.data_ptr<float>(), n, H);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {beta, g};
+}
+
+// -> {d(b_raw), d(a_raw) bf16, d(A_log), d(dt_bias) fp32 [H]}
+std::vector<at::Tensor> gdn_gates_bwd(const at::Tensor& dbeta, const at::Tensor& dg, const at::Tensor& b_raw, const at::Tensor& a_raw, const at::Tensor& A_log,
+                                      const at::Tensor& dt_bias) {
+  TORCH_CHECK(dbeta.is_cuda() && dbeta.scalar_type() == at::kBFloat16 && dg.scalar_type() == at::kFloat && dbeta.is_contiguous() && dg.is_contiguous() &&
+                  dbeta.sizes() == b_raw.sizes() && dg.sizes() == b_raw.sizes(), "gdn_gates_bwd: bf16 d(beta) and fp32 d(g) shaped like the projections required");
+  const c10::cuda::CUDAGuard guard(b_raw.device());
+  const int H = b_raw.size(-1);
+  const long long rows = b_raw.numel() / H;
+  auto db = at::empty_like(b_raw), da = at::empty_like(a_raw);
+  auto dA = at::zeros({H}, A_log.options()), dbias = at::zeros({H}, A_log.options());
+  if (rows) gdn_gates_bwd_kernel<<<(unsigned)std::min<long long>((rows + 11) / 12, 4 * kNumSMs), 256, 2 * H * sizeof(float), at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)dbeta.data_ptr(), dg.data_ptr<float>(), (const __nv_bfloat16*)b_raw.data_ptr(), (const __nv_bfloat16*)a_raw.data_ptr(),
+      A_log.data_ptr<float>(), dt_bias.data_ptr<float>(), (__nv_bfloat16*)db.data_ptr(), (__nv_bfloat16*)da.data_ptr(), dA.data_ptr<float>(),
+      dbias.data_ptr<float>(), rows, H);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {db, da, dA, dbias};
+}
+
 at::Tensor gated_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& gate, const at::Tensor& w, double eps) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && gate.scalar_type() == at::kBFloat16 && x.size(-1) == 64 &&
               x.is_contiguous() && gate.is_contiguous() && w.scalar_type() == at::kFloat, "gated_rmsnorm_fwd: bf16 [.., 64] inputs required");

@@ -32,7 +32,12 @@ std::vector<at::Tensor> qsa_headprep_bwd(const at::Tensor& dout, const c10::opti
 at::Tensor gate_add_fwd(const at::Tensor& routed, const at::Tensor& shared, const at::Tensor& logit);
 std::vector<at::Tensor> gate_add_bwd(const at::Tensor& dy, const at::Tensor& shared, const at::Tensor& logit);
 
+std::vector<at::Tensor> gdn_gates_fwd(const at::Tensor& b_raw, const at::Tensor& a_raw, const at::Tensor& A_log, const at::Tensor& dt_bias);
+std::vector<at::Tensor> gdn_gates_bwd(const at::Tensor& dbeta, const at::Tensor& dg, const at::Tensor& b_raw, const at::Tensor& a_raw, const at::Tensor& A_log,
+                                      const at::Tensor& dt_bias);
+
 // ngram.cu
+void embed_bwd(const at::Tensor& ids, const at::Tensor& dout, at::Tensor& grad);
 std::vector<at::Tensor> ngram_fwd(const at::Tensor& ids, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w, int64_t vocab,
                                   int64_t eos, double eps);
 at::Tensor ngram_bwd(const at::Tensor& de, const at::Tensor& rows, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w,

@@ -51,6 +51,44 @@ __device__ __forceinline__ float sinkhorn_fwd(float logit, int iters, float* Y, 
   return p;
 }
 
+// Forward + backward with a compile-time iteration count: the loops unroll completely, so the saved iterates live in
+// registers instead of a per-thread local-memory array.  Lanes 0..15 (lane = 4 m + n); returns d(logit) given d(result).
+template <int ITERS>
+__device__ __forceinline__ float sinkhorn_fwd_bwd_unrolled(float logit, float dres) {
+  float Y[2 * ITERS], S[2 * ITERS];
+  float mx = logit;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0x0000ffffu, mx, o));
+  const float p0 = __expf(logit - mx);
+  float p = p0;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    float s = p + __shfl_xor_sync(0x0000ffffu, p, 1);
+    s += __shfl_xor_sync(0x0000ffffu, s, 2);
+    s = fmaxf(s, 1e-9f);
+    p = p / s;
+    Y[2 * it] = p; S[2 * it] = s;
+    float c = p + __shfl_xor_sync(0x0000ffffu, p, 4);
+    c += __shfl_xor_sync(0x0000ffffu, c, 8);
+    c = fmaxf(c, 1e-9f);
+    p = p / c;
+    Y[2 * it + 1] = p; S[2 * it + 1] = c;
+  }
+  float d = dres;
+#pragma unroll
+  for (int it = ITERS - 1; it >= 0; --it) {
+    float t = d * Y[2 * it + 1];
+    t += __shfl_xor_sync(0x0000ffffu, t, 4);
+    t += __shfl_xor_sync(0x0000ffffu, t, 8);
+    d = (d - t) / S[2 * it + 1];
+    t = d * Y[2 * it];
+    t += __shfl_xor_sync(0x0000ffffu, t, 1);
+    t += __shfl_xor_sync(0x0000ffffu, t, 2);
+    d = (d - t) / S[2 * it];
+  }
+  return d * p0;
+}
+
 // d(logit) given d(result); y = p / sum(p)  =>  dp = (dy - sum(dy * y)) / s
 __device__ __forceinline__ float sinkhorn_bwd(float dres, float logit, int iters, const float* Y, const float* S) {
   float d = dres;
@@ -530,11 +568,15 @@ __global__ void __launch_bounds__(32 * CW) mhc_coef_bwd_kernel(const float* __re
     {
       const float zr = __shfl_sync(0xffffffffu, z, (lane & 15) + 8);
       const float dres = __shfl_sync(0xffffffffu, dc, (lane & 15) + 8);
-      float Y[2 * MAX_SINKHORN], S[2 * MAX_SINKHORN];
       if (lane < 16) {
         const float logit = P.b_res[lane] + P.alphas[2] * zr;
-        sinkhorn_fwd(logit, iters, Y, S, true);
-        dres_logit = sinkhorn_bwd(dres, logit, iters, Y, S);
+        if (iters == 20) {                                  // the presets' iteration count: register-resident variant
+          dres_logit = sinkhorn_fwd_bwd_unrolled<20>(logit, dres);
+        } else {
+          float Y[2 * MAX_SINKHORN], S[2 * MAX_SINKHORN];
+          sinkhorn_fwd(logit, iters, Y, S, true);
+          dres_logit = sinkhorn_bwd(dres, logit, iters, Y, S);
+        }
       }
     }
     const float moved = __shfl_sync(0xffffffffu, dres_logit, (lane + 24) & 31);   // lane j gets lane j - 8

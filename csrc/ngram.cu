@@ -99,6 +99,31 @@ __global__ void __launch_bounds__(32 * NG_WARPS) ngram_bwd_kernel(const __nv_bfl
   for (int i = threadIdx.x; i < h; i += blockDim.x) atomicAdd(&dnorm_w[i], dw_s[i]);
 }
 
+// Token-embedding backward: grad[ids[t], :] += dout[t, :] with fp32 atomics, one warp per token.
+__global__ void __launch_bounds__(32 * NG_WARPS) embed_bwd_kernel(const long long* __restrict__ ids, const float* __restrict__ dout, float* __restrict__ grad,
+                                                                  long long tokens, int h, long long vocab) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long tok = (long long)blockIdx.x * NG_WARPS + warp;
+  if (tok >= tokens) return;
+  const long long id = ids[tok];
+  if (id < 0 || id >= vocab) return;
+  const float* src = dout + tok * h;
+  float* dst = grad + id * h;
+  for (int i = lane; i < h; i += 32) atomicAdd(dst + i, src[i]);
+}
+
+void embed_bwd(const at::Tensor& ids, const at::Tensor& dout, at::Tensor& grad) {
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && dout.scalar_type() == at::kFloat && dout.is_contiguous() &&
+                  grad.scalar_type() == at::kFloat && grad.is_contiguous() && grad.dim() == 2 && dout.numel() == ids.numel() * grad.size(1),
+              "embed_bwd: int64 ids, fp32 gradient rows and an fp32 [vocab,h] gradient table required");
+  const c10::cuda::CUDAGuard guard(ids.device());
+  const long long tokens = ids.numel();
+  if (tokens) embed_bwd_kernel<<<(unsigned)((tokens + NG_WARPS - 1) / NG_WARPS), 32 * NG_WARPS, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const long long*)ids.data_ptr<int64_t>(), dout.data_ptr<float>(), grad.data_ptr<float>(), tokens, (int)grad.size(1), (long long)grad.size(0));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
 // ids [B,T] int64, tables [rows,h] fp32 -> {e [B,T,h] bf16, rstd [B,T] fp32, rows [B,T,2] int32}
 std::vector<at::Tensor> ngram_fwd(const at::Tensor& ids, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w, int64_t vocab,
                                   int64_t eos, double eps) {

@@ -59,6 +59,14 @@ def _hook(name: str, t: torch.Tensor):
     return getattr(_BACKEND, name, None)
 
 
+def _embed(table: nn.Embedding, ids):
+    """Embedding lookup; on a GPU the backend scatters the gradient straight into the table's gradient buffer."""
+    fast = _hook("embedding", table.weight)
+    if fast is not None:
+        return fast(table.weight, ids)
+    return table(ids)
+
+
 def _linear(x, weight, bias=None):
     """``x @ weight.T`` in the dtype of ``x`` (fp32 master weights are cast per use)."""
     fast = _hook("linear", x)
@@ -684,7 +692,7 @@ class Q38TextCore(nn.Module):
             raise ValueError("Indexer and attention head dimensions must match for shared partial RoPE")
         if length % BLK:
             ids = F.pad(ids, (0, (-length) % BLK), value=self.config.pad_token_id or 0)
-        e = self.embed_tokens(ids)
+        e = _embed(self.embed_tokens, ids)
         dtype = self.compute_dtype or e.dtype
         cos, sin = self.rope(ids.shape[1], ids.device, e.dtype)
         X = e.float().unsqueeze(2).expand(-1, -1, self.config.n_branch, -1).contiguous()
@@ -761,7 +769,7 @@ class Q38CausalCore(nn.Module):
         """MTP trunk: ``proj([enorm(embed(next token)); hnorm(hidden)])`` -> one plain GDN+MoE layer -> norm."""
         m = self.mtp
         dtype = self.model.compute_dtype or hs.dtype
-        z = torch.cat([m["enorm"](self.model.embed_tokens(ids_next), out_dtype=dtype), m["hnorm"](hs, out_dtype=dtype)], -1)
+        z = torch.cat([m["enorm"](_embed(self.model.embed_tokens, ids_next), out_dtype=dtype), m["hnorm"](hs, out_dtype=dtype)], -1)
         return m["norm"](m["block"](_linear(z, m["proj"].weight)))
 
     def logits(self, input_ids):

@@ -337,6 +337,42 @@ class _IndexerKL(torch.autograd.Function):
         return dqi * dkl.to(dqi.dtype), dki * dkl.to(dki.dtype), dwi * dkl, None, None, None, None
 
 
+class _Embed(torch.autograd.Function):
+    """Row gather; the backward adds the rows into the table's fp32 gradient buffer in place (atomics) when it exists."""
+
+    @staticmethod
+    def forward(ctx, weight, ids):
+        ctx.save_for_backward(weight, ids)
+        return torch.nn.functional.embedding(ids, weight)
+
+    @staticmethod
+    def backward(ctx, dout):
+        weight, ids = ctx.saved_tensors
+        in_place = weight.grad is not None and weight.grad.dtype == torch.float32 and weight.grad.is_contiguous()
+        grad = weight.grad if in_place else torch.zeros_like(weight, dtype=torch.float32)
+        load().embed_bwd(ids.long().contiguous(), dout.float().contiguous(), grad)
+        return (None if in_place else grad.to(weight.dtype)), None
+
+
+class _GdnGates(torch.autograd.Function):
+    """(b, a) projections [.., Hv] bf16 -> beta = sigmoid(b) (bf16), g = -exp(A_log) softplus(a + dt_bias) (fp32), one kernel each way."""
+
+    @staticmethod
+    def forward(ctx, b_raw, a_raw, A_log, dt_bias):
+        b_raw, a_raw = b_raw.contiguous(), a_raw.contiguous()
+        beta, g = load().gdn_gates_fwd(b_raw, a_raw, A_log.float().contiguous(), dt_bias.float().contiguous())
+        ctx.save_for_backward(b_raw, a_raw, A_log, dt_bias)
+        return beta, g
+
+    @staticmethod
+    def backward(ctx, dbeta, dg):
+        b_raw, a_raw, A_log, dt_bias = ctx.saved_tensors
+        dbeta = torch.zeros_like(b_raw) if dbeta is None else dbeta.to(torch.bfloat16).contiguous()
+        dg = torch.zeros(b_raw.shape, dtype=torch.float32, device=b_raw.device) if dg is None else dg.float().contiguous()
+        db, da, dA, dbias = load().gdn_gates_bwd(dbeta, dg, b_raw, a_raw, A_log.float().contiguous(), dt_bias.float().contiguous())
+        return db, da, dA.to(A_log.dtype), dbias.to(dt_bias.dtype)
+
+
 class _GateAdd(torch.autograd.Function):
     """routed + sigmoid(logit) * shared for [T,h] bf16 rows and one logit per row (the shared-expert merge of the MoE block)."""
 
@@ -628,8 +664,7 @@ class Backend:
         F = torch.nn.functional
         qkv = _ConvSilu.apply(self.linear(x, m.in_proj_qkv.weight), m.conv1d.weight)
         z = self.linear(x, m.in_proj_z.weight)
-        beta = self.linear(x, m.in_proj_b.weight).sigmoid()
-        g = -m.A_log.float().exp() * F.softplus(self.linear(x, m.in_proj_a.weight).float() + m.dt_bias.float())
+        beta, g = _GdnGates.apply(self.linear(x, m.in_proj_b.weight), self.linear(x, m.in_proj_a.weight), m.A_log, m.dt_bias)
         if self.hybrid_delta_rule:
             q, k, v = qkv.split([m.key_dim, m.key_dim, m.value_dim], dim=-1)
             o = self.delta_rule(q.reshape(B, S, -1, 64), k.reshape(B, S, -1, 64), v.reshape(B, S, -1, 64), g, beta)
@@ -695,6 +730,11 @@ class Backend:
             o = _BlockAttention.apply(q, k, v, count, index, attn.scaling)
         o = o.reshape(B, S, -1) * torch.sigmoid(gate)
         return self.linear(o, attn.o_proj.weight), kl
+
+    def embedding(self, weight, ids):
+        if weight.dtype != torch.float32 or not weight.is_contiguous():
+            return torch.nn.functional.embedding(ids, weight)
+        return _Embed.apply(weight, ids)
 
     @_nvtx("q38.ngram_delta")
     def ngram_delta(self, m, h, ids):

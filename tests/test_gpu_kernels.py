@@ -520,3 +520,33 @@ def test_qsa_head_preparation(ops, with_norm, split):
         assert torch.equal(ga.float(), gb.float().to(torch.bfloat16).float())
     if with_norm:
         assert rel_err(dwa, dwb) < 2e-2
+
+
+def test_gdn_gates(ops):
+    """beta = sigmoid(b), g = -exp(A_log) softplus(a + dt_bias) and their gradients (incl. the per-head parameter sums)."""
+    from q38.ops.backend import _GdnGates
+    torch.manual_seed(15)
+    T, H = 1000, 21
+    b = torch.randn(2, T // 2, H, device="cuda").to(torch.bfloat16)
+    a = (3 * torch.randn(2, T // 2, H, device="cuda")).to(torch.bfloat16)
+    a[0, 0, 0] = 30.0                                            # softplus linear branch
+    A_log = torch.randn(H, device="cuda").requires_grad_()
+    dt_bias = torch.randn(H, device="cuda").requires_grad_()
+    dbeta = torch.randn_like(b)
+    dg = torch.randn(2, T // 2, H, device="cuda")
+
+    def run(fast):
+        bb, aa = b.clone().requires_grad_(), a.clone().requires_grad_()
+        A_log.grad = dt_bias.grad = None
+        if fast:
+            beta, g = _GdnGates.apply(bb, aa, A_log, dt_bias)
+        else:
+            beta = bb.float().sigmoid()
+            g = -A_log.float().exp() * torch.nn.functional.softplus(aa.float() + dt_bias.float())
+        (beta.float() * dbeta.float()).sum().backward(retain_graph=True)
+        (g * dg).sum().backward()
+        return beta, g, bb.grad, aa.grad, A_log.grad.clone(), dt_bias.grad.clone()
+
+    got, ref = run(True), run(False)
+    for x, y, tol in zip(got, ref, (1e-2, 1e-5, 2e-2, 2e-2, 1e-3, 1e-3)):
+        assert rel_err(x, y) < tol
