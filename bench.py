@@ -156,7 +156,7 @@ def main():
     published = None          # the reference publishes no B200 number for this config
     if rank == 0:
         print(json.dumps({
-            "metric": "train tokens/sec, q38_c2 seq 4096", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "metric": f"train tokens/sec, {a.preset} seq {a.seq}", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms_dev / a.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": published, "dtype": "bf16", "data": "synthetic packed stream (uniform ids, EOS at geometric(1024) boundaries), random-init weights",
             "impl": "ours",

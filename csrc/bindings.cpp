@@ -82,7 +82,7 @@ TORCH_LIBRARY(q38, m) {
   m.def("mhc_post_fwd(Tensor X, Tensor y, Tensor coef) -> Tensor");
   m.def("mhc_post_bwd(Tensor dXo, Tensor X, Tensor y, Tensor coef) -> Tensor[]");
   m.def("mhc_pre_bwd_a(Tensor dxout, Tensor X, Tensor Lraw, Tensor Bw, Tensor b_pre, Tensor b_post, Tensor b_res, Tensor alphas, Tensor norm_w, Tensor coef, Tensor z, Tensor inv, Tensor rstd, Tensor(a!) dcoef, int iters) -> Tensor[]");
-  m.def("mhc_pre_bwd_c(Tensor(a!) dX, Tensor dXo, Tensor X, Tensor dxin, Tensor coef, Tensor c1) -> ()");
+  m.def("mhc_pre_bwd_c(Tensor G, Tensor dXo, Tensor X, Tensor dxin, Tensor coef, Tensor c1) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(q38, CUDA, m) {
@@ -142,7 +142,5 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
                              const at::Tensor& k, const at::Tensor& l, const at::Tensor& mm, at::Tensor& n, int64_t it) {
     return q38::mhc_pre_bwd_a(a, b, c, d, e, f, g, h, i, j, k, l, mm, n, it);
   });
-  m.impl("mhc_pre_bwd_c", [](at::Tensor& dX, const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, const at::Tensor& d, const at::Tensor& e) {
-    q38::mhc_pre_bwd_c(dX, a, b, c, d, e);
-  });
+  m.impl("mhc_pre_bwd_c", &q38::mhc_pre_bwd_c);
 }

@@ -281,7 +281,8 @@ static void launch_p(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     if (!cfg) { C10_CUDA_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); cfg = true; } \
     k<<<grid, P_THREADS, smem, stream>>>(ta, tb, tc, p); }
   if constexpr (TF32) {
-    if (tma_out) { if (accum) Q38_LAUNCH(float, true, true) else Q38_LAUNCH(float, false, true) }
+    if (!out_fp32) { if (tma_out) Q38_LAUNCH(__nv_bfloat16, false, true) else Q38_LAUNCH(__nv_bfloat16, false, false) }
+    else if (tma_out) { if (accum) Q38_LAUNCH(float, true, true) else Q38_LAUNCH(float, false, true) }
     else { if (accum) Q38_LAUNCH(float, true, false) else Q38_LAUNCH(float, false, false) }
   } else if (tma_out) {
     if (!out_fp32) Q38_LAUNCH(__nv_bfloat16, false, true)
@@ -307,7 +308,7 @@ void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& 
   const bool tf32 = a.scalar_type() == at::kFloat;
   TORCH_CHECK(a.is_cuda() && (tf32 || a.scalar_type() == at::kBFloat16) && b.scalar_type() == a.scalar_type() && a.dim() == 3 && b.dim() == 3 && c.dim() == 3,
               "gemm_bf16_persistent: bf16 (or fp32 for tf32 math) [batch, rows, cols] operands required");
-  TORCH_CHECK(!tf32 || (!a_mn_major && !b_mn_major && c.scalar_type() == at::kFloat), "gemm_bf16_persistent: the tf32 path takes K-major operands and writes fp32");
+  TORCH_CHECK(!tf32 || (!a_mn_major && !b_mn_major), "gemm_bf16_persistent: the tf32 path takes K-major operands only");
   const int eb = tf32 ? 4 : 2, bk = 128 / eb;
   TORCH_CHECK(a.stride(2) == 1 && b.stride(2) == 1 && c.stride(2) == 1, "gemm_bf16_persistent: innermost dimension must be contiguous");
   const c10::cuda::CUDAGuard guard(a.device());

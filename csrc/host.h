@@ -62,7 +62,7 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
                                       const at::Tensor& b_pre, const at::Tensor& b_post, const at::Tensor& b_res, const at::Tensor& alphas,
                                       const at::Tensor& norm_w, const at::Tensor& coef, const at::Tensor& z, const at::Tensor& inv,
                                       const at::Tensor& rstd, at::Tensor& dcoef, int64_t iters);
-void mhc_pre_bwd_c(at::Tensor& dX, const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& dxin, const at::Tensor& coef, const at::Tensor& c1);
+at::Tensor mhc_pre_bwd_c(const at::Tensor& G, const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& dxin, const at::Tensor& coef, const at::Tensor& c1);
 
 // moe.cu
 std::vector<at::Tensor> moe_route_fwd(const at::Tensor& logits, int64_t k);

@@ -332,24 +332,44 @@ __global__ void __launch_bounds__(32 * WARPS) mhc_pre_bwd_a_kernel(const GT* __r
   if (threadIdx.x < 27) atomicAdd(&dbias[threadIdx.x], dbias_s[threadIdx.x]);
 }
 
-// dX (holding G on entry) <- G + c1 X + pre_n dxin + sum_m res[m,n] dX'_m
-__global__ void __launch_bounds__(256) mhc_pre_bwd_c_kernel(float* __restrict__ dX, const float* __restrict__ dXo, const float* __restrict__ X,
-                                                            const float* __restrict__ dxin, const float* __restrict__ coef,
+// dX_n = G_n + c1 X_n + pre_n dxin + sum_m res[m,n] dX'_m, four columns per thread.  G (= dL_raw . A from the GEMM) may be bf16:
+// it is the low-rank correction to the stream gradient, whose other terms stay fp32.
+template <typename GT>
+__global__ void __launch_bounds__(256) mhc_pre_bwd_c_kernel(float* __restrict__ dX, const GT* __restrict__ G, const float* __restrict__ dXo,
+                                                            const float* __restrict__ X, const float* __restrict__ dxin, const float* __restrict__ coef,
                                                             const float* __restrict__ c1, int T, int h) {
+  const int h4 = h >> 2;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (size_t)T * h) return;
-  const int t = idx / h, i = idx % h;
+  if (idx >= (size_t)T * h4) return;
+  const int t = idx / h4, q = idx % h4;
   const float* c = coef + (size_t)t * NCOEF;
-  const size_t base = (size_t)t * NB * h + i;
-  const float d0 = dXo[base], d1 = dXo[base + h], d2 = dXo[base + 2 * h], d3 = dXo[base + 3 * h];
-  const float k1 = c1[t], di = dxin[idx];
+  const size_t base = (size_t)t * NB * h + 4 * q;
+  float4 d[NB];
+#pragma unroll
+  for (int m = 0; m < NB; ++m) d[m] = __ldcs(reinterpret_cast<const float4*>(dXo + base + (size_t)m * h));
+  const float k1 = c1[t];
+  const float4 di = *reinterpret_cast<const float4*>(dxin + (size_t)t * h + 4 * q);
 #pragma unroll
   for (int n = 0; n < NB; ++n) {
     const size_t o = base + (size_t)n * h;
-    dX[o] = dX[o] + k1 * X[o] + c[n] * di + c[8 + n] * d0 + c[12 + n] * d1 + c[16 + n] * d2 + c[20 + n] * d3;
+    const float4 x = __ldcs(reinterpret_cast<const float4*>(X + o));
+    float4 g;
+    if constexpr (sizeof(GT) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(G + o);
+      const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      g = make_float4(lo.x, lo.y, hi.x, hi.y);
+    } else {
+      g = *reinterpret_cast<const float4*>(G + o);
+    }
+    const float pn = c[n], r0 = c[8 + n], r1 = c[12 + n], r2 = c[16 + n], r3 = c[20 + n];
+    float4 out;
+    out.x = g.x + k1 * x.x + pn * di.x + r0 * d[0].x + r1 * d[1].x + r2 * d[2].x + r3 * d[3].x;
+    out.y = g.y + k1 * x.y + pn * di.y + r0 * d[0].y + r1 * d[1].y + r2 * d[2].y + r3 * d[3].y;
+    out.z = g.z + k1 * x.z + pn * di.z + r0 * d[0].z + r1 * d[1].z + r2 * d[2].z + r3 * d[3].z;
+    out.w = g.w + k1 * x.w + pn * di.w + r0 * d[0].w + r1 * d[1].w + r2 * d[2].w + r3 * d[3].w;
+    *reinterpret_cast<float4*>(dX + o) = out;
   }
 }
-
 
 // ---- row-in-registers variants ---------------------------------------------------------------------------------------
 // One warp per token, looping over tokens.  A lane owns the float4 columns q = lane + 32 jj (jj < NQ) of all four branches,
@@ -768,15 +788,25 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
   return {dLraw, c1, dxin, dBw, dbias, dnw, X.reshape({T, NB * h}).to(at::kBFloat16)};
 }
 
-void mhc_pre_bwd_c(at::Tensor& dX, const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& dxin, const at::Tensor& coef, const at::Tensor& c1) {
-  TORCH_CHECK(dX.is_cuda() && dX.is_contiguous() && dXo.is_contiguous() && X.is_contiguous() && dxin.is_contiguous(), "mhc_pre_bwd_c: bad inputs");
+// G [T,4,h] bf16 or fp32 -> dX [T,4,h] fp32
+at::Tensor mhc_pre_bwd_c(const at::Tensor& G, const at::Tensor& dXo, const at::Tensor& X, const at::Tensor& dxin, const at::Tensor& coef, const at::Tensor& c1) {
+  TORCH_CHECK(G.is_cuda() && G.is_contiguous() && dXo.is_contiguous() && X.is_contiguous() && dxin.is_contiguous() && X.size(2) % 4 == 0 &&
+                  (G.scalar_type() == at::kFloat || G.scalar_type() == at::kBFloat16) && G.numel() == X.numel() && dXo.scalar_type() == at::kFloat,
+              "mhc_pre_bwd_c: bad inputs");
   const c10::cuda::CUDAGuard guard(X.device());
   const int T = X.size(0), h = X.size(2);
-  const size_t n = (size_t)T * h;
-  mhc_pre_bwd_c_kernel<<<(n + 255) / 256, 256, 0, at::cuda::getCurrentCUDAStream()>>>(dX.data_ptr<float>(), dXo.data_ptr<float>(), X.data_ptr<float>(),
-                                                                                      dxin.data_ptr<float>(), coef.data_ptr<float>(), c1.data_ptr<float>(), T, h);
+  auto dX = at::empty_like(X);
+  const size_t n = (size_t)T * (h / 4);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  if (G.scalar_type() == at::kFloat)
+    mhc_pre_bwd_c_kernel<float><<<(n + 255) / 256, 256, 0, stream>>>(dX.data_ptr<float>(), G.data_ptr<float>(), dXo.data_ptr<float>(), X.data_ptr<float>(),
+                                                                     dxin.data_ptr<float>(), coef.data_ptr<float>(), c1.data_ptr<float>(), T, h);
+  else
+    mhc_pre_bwd_c_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, stream>>>(dX.data_ptr<float>(), (const __nv_bfloat16*)G.data_ptr(), dXo.data_ptr<float>(),
+                                                                             X.data_ptr<float>(), dxin.data_ptr<float>(), coef.data_ptr<float>(), c1.data_ptr<float>(), T, h);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
+  return dX;
 }
 
 }  // namespace q38

@@ -138,7 +138,7 @@ def _tma_rows(t):
     return view
 
 
-def _mm32(a, b, layout):
+def _mm32(a, b, layout, out_dtype=torch.float32):
     """Products of fp32 operands for the mHC low-rank path on the tensor cores.
 
     'nt' a[M,K] b[N,K]^T and 'nn' a[M,K] b[K,N] run as tf32 (fp32 data read by TMA, 10-bit mantissa math, fp32 accumulate);
@@ -154,8 +154,8 @@ def _mm32(a, b, layout):
     if layout == "nn":
         b = b.t().contiguous()
     if a.shape[1] % 4 or a.data_ptr() % 16 or b.data_ptr() % 16:
-        return a @ b.t()
-    return gemm(a, b, out_dtype=torch.float32)
+        return (a @ b.t()).to(out_dtype)
+    return gemm(a, b, out_dtype=out_dtype)
 
 
 def _mhc_weight_grad(dL, Xf, A_w):
@@ -212,10 +212,12 @@ class _MhcPreNorm(torch.autograd.Function):
             coef, z, inv, rstd, dcoef, ctx.iters)
         Xf = Xc.view(T, n * h)
         dA = _mhc_weight_grad(dLraw, Xf if os.environ.get("Q38_MHC_FP32_GEMM") else Xbf, A_w)
-        dX = _mm32(dLraw, A_w, 'nn')                          # G, completed in place below
+        # G = dL_raw A: the low-rank correction of the stream gradient, kept in bf16 between the GEMM and the combine kernel
+        # (fp32 with Q38_MHC_FP32_GEMM); every other term of dX is fp32
+        G = _mm32(dLraw, A_w, 'nn', torch.float32 if os.environ.get("Q38_MHC_FP32_GEMM") else torch.bfloat16)
         dXo = ctx.link.dXo if ctx.link.dXo is not None else torch.zeros_like(Xf)
         ctx.link.dXo = None
-        ops.mhc_pre_bwd_c(dX.view(T, n, h), dXo.contiguous().view(T, n, h), Xc.view(T, n, h), dxin, coef, c1)
+        dX = ops.mhc_pre_bwd_c(G.view(T, n, h), dXo.contiguous().view(T, n, h), Xc.view(T, n, h), dxin, coef, c1)
         return (dX.view(B_, S, n, h), dA, dBw.to(B_w.dtype), dbias[0:4].to(b_pre.dtype), dbias[4:8].to(b_post.dtype),
                 dbias[8:24].view(4, 4).to(b_res.dtype), dbias[24:27].to(alphas.dtype), dnw.to(norm_w.dtype), None, None, None, None)
 
