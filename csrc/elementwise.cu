@@ -205,6 +205,64 @@ __global__ void __launch_bounds__(256) gated_rmsnorm_bwd_kernel(const __nv_bfloa
   if (threadIdx.x < 64) atomicAdd(&dw[threadIdx.x], dw_acc[threadIdx.x]);
 }
 
+// ---- SwiGLU: y = bf16(silu(g)) * u, elementwise on bf16 (eight elements per thread) --------------------------------------
+__global__ void __launch_bounds__(256) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+                                                          __nv_bfloat16* __restrict__ y, long long n8) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float gv[8], uv[8], o[8];
+  unpack8(reinterpret_cast<const uint4*>(g)[i], gv);
+  unpack8(reinterpret_cast<const uint4*>(u)[i], uv);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = bf16_round(siluf_(gv[k])) * uv[k];
+  reinterpret_cast<uint4*>(y)[i] = pack8(o);
+}
+
+__global__ void __launch_bounds__(256) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ g,
+                                                          const __nv_bfloat16* __restrict__ u, __nv_bfloat16* __restrict__ dg,
+                                                          __nv_bfloat16* __restrict__ du, long long n8) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float dv[8], gv[8], uv[8], og[8], ou[8];
+  unpack8(reinterpret_cast<const uint4*>(dy)[i], dv);
+  unpack8(reinterpret_cast<const uint4*>(g)[i], gv);
+  unpack8(reinterpret_cast<const uint4*>(u)[i], uv);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float s = sigmoidf_(gv[k]);
+    ou[k] = dv[k] * gv[k] * s;
+    og[k] = dv[k] * uv[k] * s * (1.f + gv[k] * (1.f - s));
+  }
+  reinterpret_cast<uint4*>(dg)[i] = pack8(og);
+  reinterpret_cast<uint4*>(du)[i] = pack8(ou);
+}
+
+at::Tensor swiglu_fwd(const at::Tensor& g, const at::Tensor& u) {
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kBFloat16 && u.scalar_type() == at::kBFloat16 && g.is_contiguous() && u.is_contiguous() &&
+                  g.sizes() == u.sizes() && g.numel() % 8 == 0, "swiglu_fwd: contiguous bf16 tensors of equal shape (a multiple of 8 elements) required");
+  const c10::cuda::CUDAGuard guard(g.device());
+  auto y = at::empty_like(g);
+  const long long n8 = g.numel() / 8;
+  if (n8) swiglu_fwd_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)g.data_ptr(), (const __nv_bfloat16*)u.data_ptr(), (__nv_bfloat16*)y.data_ptr(), n8);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return y;
+}
+
+std::vector<at::Tensor> swiglu_bwd(const at::Tensor& dy, const at::Tensor& g, const at::Tensor& u) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.sizes() == g.sizes(), "swiglu_bwd: bad gradient");
+  const c10::cuda::CUDAGuard guard(g.device());
+  auto dg = at::empty_like(g), du = at::empty_like(u);
+  const long long n8 = g.numel() / 8;
+  if (n8) swiglu_bwd_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)g.data_ptr(), (const __nv_bfloat16*)u.data_ptr(), (__nv_bfloat16*)dg.data_ptr(),
+      (__nv_bfloat16*)du.data_ptr(), n8);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {dg, du};
+}
+
 // ---- shared-expert merge: out = routed + sigmoid(logit_t) * shared  (one warp per token row, 16-byte accesses) ------------
 __global__ void __launch_bounds__(256) gate_add_fwd_kernel(const __nv_bfloat16* __restrict__ routed, const __nv_bfloat16* __restrict__ shared,
                                                             const __nv_bfloat16* __restrict__ logit, __nv_bfloat16* __restrict__ out, int T, int h) {

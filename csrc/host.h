@@ -36,6 +36,9 @@ std::vector<at::Tensor> gdn_gates_fwd(const at::Tensor& b_raw, const at::Tensor&
 std::vector<at::Tensor> gdn_gates_bwd(const at::Tensor& dbeta, const at::Tensor& dg, const at::Tensor& b_raw, const at::Tensor& a_raw, const at::Tensor& A_log,
                                       const at::Tensor& dt_bias);
 
+at::Tensor swiglu_fwd(const at::Tensor& g, const at::Tensor& u);
+std::vector<at::Tensor> swiglu_bwd(const at::Tensor& dy, const at::Tensor& g, const at::Tensor& u);
+
 // ngram.cu
 void embed_bwd(const at::Tensor& ids, const at::Tensor& dout, at::Tensor& grad);
 std::vector<at::Tensor> ngram_fwd(const at::Tensor& ids, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w, int64_t vocab,

@@ -170,20 +170,37 @@ __global__ void __launch_bounds__(32 * WARPS) mhc_coef_fwd_kernel(const float* _
   for (int i = lane; i < h; i += 32) xo[i] = from_float<OutT>(xs[i] * rstd * (1.f + norm_w[i]));
 }
 
+// X'_m = sum_n res[m,n] X_n + post_m y, four columns per thread (16-byte accesses; h is a multiple of 4).
 template <typename YT>
 __global__ void __launch_bounds__(256) mhc_post_fwd_kernel(const float* __restrict__ X, const YT* __restrict__ y,
                                                            const float* __restrict__ coef, float* __restrict__ Xout, int T, int h) {
+  const int h4 = h >> 2;
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (size_t)T * h) return;
-  const int t = idx / h, i = idx % h;
+  if (idx >= (size_t)T * h4) return;
+  const int t = idx / h4, q = idx % h4;
   const float* c = coef + (size_t)t * NCOEF;
-  const float* Xt = X + (size_t)t * NB * h;
-  const float x0 = Xt[i], x1 = Xt[h + i], x2 = Xt[2 * h + i], x3 = Xt[3 * h + i];
-  const float yv = to_float(y[idx]);
-  float* Xo = Xout + (size_t)t * NB * h;
+  const size_t base = (size_t)t * NB * h + 4 * q;
+  float4 x[NB];
 #pragma unroll
-  for (int m = 0; m < NB; ++m)
-    Xo[m * h + i] = c[8 + 4 * m] * x0 + c[8 + 4 * m + 1] * x1 + c[8 + 4 * m + 2] * x2 + c[8 + 4 * m + 3] * x3 + c[4 + m] * yv;
+  for (int n = 0; n < NB; ++n) x[n] = __ldcs(reinterpret_cast<const float4*>(X + base + (size_t)n * h));
+  float4 yv;
+  if constexpr (sizeof(YT) == 2) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(y + (size_t)t * h + 4 * q);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    yv = make_float4(lo.x, lo.y, hi.x, hi.y);
+  } else {
+    yv = *reinterpret_cast<const float4*>(y + (size_t)t * h + 4 * q);
+  }
+#pragma unroll
+  for (int m = 0; m < NB; ++m) {
+    const float r0 = c[8 + 4 * m], r1 = c[8 + 4 * m + 1], r2 = c[8 + 4 * m + 2], r3 = c[8 + 4 * m + 3], pm = c[4 + m];
+    float4 o;
+    o.x = r0 * x[0].x + r1 * x[1].x + r2 * x[2].x + r3 * x[3].x + pm * yv.x;
+    o.y = r0 * x[0].y + r1 * x[1].y + r2 * x[2].y + r3 * x[3].y + pm * yv.y;
+    o.z = r0 * x[0].z + r1 * x[1].z + r2 * x[2].z + r3 * x[3].z + pm * yv.z;
+    o.w = r0 * x[0].w + r1 * x[1].w + r2 * x[2].w + r3 * x[3].w + pm * yv.w;
+    *reinterpret_cast<float4*>(Xout + base + (size_t)m * h) = o;
+  }
 }
 
 template <typename YT>
@@ -705,7 +722,8 @@ at::Tensor mhc_post_fwd(const at::Tensor& X, const at::Tensor& y, const at::Tens
   const c10::cuda::CUDAGuard guard(X.device());
   const int T = X.size(0), h = X.size(2);
   auto out = at::empty_like(X);
-  const size_t n = (size_t)T * h;
+  TORCH_CHECK(h % 4 == 0, "mhc_post_fwd: hidden size must be a multiple of 4");
+  const size_t n = (size_t)T * (h / 4);
   auto stream = at::cuda::getCurrentCUDAStream();
   if (y.scalar_type() == at::kBFloat16)
     mhc_post_fwd_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, stream>>>(X.data_ptr<float>(), (const __nv_bfloat16*)y.data_ptr(), coef.data_ptr<float>(), out.data_ptr<float>(), T, h);

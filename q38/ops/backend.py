@@ -375,6 +375,22 @@ class _GdnGates(torch.autograd.Function):
         return db, da, dA.to(A_log.dtype), dbias.to(dt_bias.dtype)
 
 
+class _SwiGLU(torch.autograd.Function):
+    """silu(g) * u on bf16 tensors, one kernel each way."""
+
+    @staticmethod
+    def forward(ctx, g, u):
+        g, u = g.contiguous(), u.contiguous()
+        ctx.save_for_backward(g, u)
+        return load().swiglu_fwd(g, u)
+
+    @staticmethod
+    def backward(ctx, dy):
+        g, u = ctx.saved_tensors
+        dg, du = load().swiglu_bwd(dy.contiguous(), g, u)
+        return dg, du
+
+
 class _GateAdd(torch.autograd.Function):
     """routed + sigmoid(logit) * shared for [T,h] bf16 rows and one logit per row (the shared-expert merge of the MoE block)."""
 
@@ -770,7 +786,8 @@ class Backend:
         else:
             routed = _Experts.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj)
         shared = block.shared_expert
-        mid = torch.nn.functional.silu(self.linear(x2, shared.gate_proj.weight)) * self.linear(x2, shared.up_proj.weight)
+        sg, su = self.linear(x2, shared.gate_proj.weight), self.linear(x2, shared.up_proj.weight)
+        mid = _SwiGLU.apply(sg, su) if sg.numel() % 8 == 0 else torch.nn.functional.silu(sg) * su
         gate_logit = self.linear(x2, block.shared_expert_gate.weight)
         if h % 8 == 0 and gate_logit.shape[1] == 1:
             return _GateAdd.apply(routed, self.linear(mid, shared.down_proj.weight), gate_logit).reshape(shape)
