@@ -800,7 +800,7 @@ class Backend:
 
     def describe(self):
         native = sorted(n for n in ("linear", "rmsnorm", "gated_rmsnorm", "mhc_pre_norm", "mhc_post", "gated_deltanet",
-                                    "qsa_attention", "moe_block", "ngram_delta", "linear_cross_entropy") if hasattr(self, n))
+                                    "qsa_attention", "moe_block", "ngram_delta", "embedding", "linear_cross_entropy") if hasattr(self, n))
         return dict(native=native, gemm_layouts=self.layouts)
 
 
