@@ -54,6 +54,8 @@ class GradEngine:
         if self.transport is not None:
             self.transport.bind(self.arena)
         self._last = True
+        import os
+        self._timing = [] if (os.environ.get("Q38_ENGINE_TIMING") == "1" and self.device.type == "cuda") else None
 
     # ------------------------------------------------------------------ step protocol
     def set_lr(self, lr):
@@ -118,16 +120,44 @@ class GradEngine:
         return ops.sum_squares(self.arena.grads[s:e])
 
     def finish_step(self, clip):
-        """Reduce, clip, update owned parameters, publish them, clear gradients.  Returns the pre-clip gradient norm."""
+        """Reduce, clip, update owned parameters, publish them, clear gradients.  Returns the pre-clip gradient norm.
+        With Q38_ENGINE_TIMING=1 on a GPU the phases are bracketed by CUDA events and `phase_times()` reports their means."""
+        mark = self._mark
+        mark("start")
         self._reduce_scatter()
+        mark("reduce_scatter")
         norm = self.grad_norm()
         scale = None
         if clip and clip > 0:
             scale = (clip / (norm + 1e-6)).clamp(max=1.0)
+        mark("grad_norm")
         self.optimizer.step(grad_scale=scale)
+        mark("optimizer")
         self._all_gather()
+        mark("all_gather")
         self.zero_grad()
+        mark("zero_grad")
         return norm
+
+    def _mark(self, name):
+        if self._timing is None:
+            return
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        self._timing.append((name, event))
+
+    def phase_times(self):
+        """Mean milliseconds per phase of `finish_step` over the steps recorded so far (Q38_ENGINE_TIMING=1)."""
+        if not self._timing:
+            return {}
+        torch.cuda.synchronize(self.device)
+        sums, counts = {}, {}
+        for (_, e0), (name, e1) in zip(self._timing, self._timing[1:]):
+            if name == "start":
+                continue
+            sums[name] = sums.get(name, 0.0) + e0.elapsed_time(e1)
+            counts[name] = counts.get(name, 0) + 1
+        return {k: round(sums[k] / counts[k], 3) for k in sums}
 
     def average_metrics(self, values):
         """Mean over ranks of the loss terms; the last entry (gradient norm) is already global."""
