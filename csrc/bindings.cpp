@@ -28,7 +28,7 @@ TORCH_LIBRARY(q38, m) {
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) -> Tensor[]");
   m.def("gated_rmsnorm_fwd(Tensor x, Tensor gate, Tensor w, float eps) -> Tensor");
   m.def("gated_rmsnorm_bwd(Tensor dy, Tensor x, Tensor gate, Tensor w, float eps) -> Tensor[]");
-  m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps) -> ()");
+  m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps, Tensor? hyper) -> ()");
   m.def("sum_squares(Tensor x) -> Tensor");
   m.def("qsa_main_block_stats(Tensor q, Tensor k, float scale) -> Tensor");
   m.def("qsa_indexer_fwd(Tensor qi, Tensor ki, Tensor wi, float scale) -> Tensor");
@@ -96,8 +96,9 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
   m.impl("gated_rmsnorm_fwd", &q38::gated_rmsnorm_fwd);
   m.impl("gated_rmsnorm_bwd", &q38::gated_rmsnorm_bwd);
   m.impl("adamw_flat", [](at::Tensor& p, const at::Tensor& g, at::Tensor& mm, at::Tensor& v, c10::optional<at::Tensor> shadow,
-                          c10::optional<at::Tensor> gs, int64_t step, double lr, double wd, double b1, double b2, double eps) {
-    q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps);
+                          c10::optional<at::Tensor> gs, int64_t step, double lr, double wd, double b1, double b2, double eps,
+                          c10::optional<at::Tensor> hyper) {
+    q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps, hyper);
   });
   m.impl("sum_squares", &q38::sum_squares);
   m.impl("qsa_main_block_stats", &q38::qsa_main_block_stats);

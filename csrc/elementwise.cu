@@ -444,8 +444,10 @@ std::vector<at::Tensor> gated_rmsnorm_bwd(const at::Tensor& dy, const at::Tensor
 __global__ void __launch_bounds__(256) adamw_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                                                           float* __restrict__ v, __nv_bfloat16* __restrict__ shadow,
                                                           const float* __restrict__ grad_scale, size_t n, float lr, float wd, float b1,
-                                                          float b2, float eps, float inv_bc1, float inv_sqrt_bc2) {
+                                                          float b2, float eps, float inv_bc1, float inv_sqrt_bc2,
+                                                          const float* __restrict__ hyper) {
   const float gs = grad_scale ? *grad_scale : 1.f;
+  if (hyper) { lr = hyper[0]; inv_bc1 = hyper[1]; inv_sqrt_bc2 = hyper[2]; }   // step-dependent scalars from device memory (CUDA-graph replay)
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const float gi = g[i] * gs;
     float pi = p[i] * (1.f - lr * wd);
@@ -458,7 +460,10 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(float* __restrict__ p, 
 }
 
 void adamw_flat(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v, c10::optional<at::Tensor> shadow,
-                c10::optional<at::Tensor> grad_scale, int64_t step, double lr, double wd, double beta1, double beta2, double eps) {
+                c10::optional<at::Tensor> grad_scale, int64_t step, double lr, double wd, double beta1, double beta2, double eps,
+                c10::optional<at::Tensor> hyper) {
+  TORCH_CHECK(!hyper.has_value() || (hyper->is_cuda() && hyper->scalar_type() == at::kFloat && hyper->is_contiguous() && hyper->numel() >= 3),
+              "adamw_flat: hyper must be a CUDA fp32 tensor {lr, 1/(1-b1^t), 1/sqrt(1-b2^t)}");
   TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kFloat && p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(),
               "adamw_flat: contiguous fp32 CUDA tensors required");
   const c10::cuda::CUDAGuard guard(p.device());
@@ -469,7 +474,8 @@ void adamw_flat(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v
   adamw_flat_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
       shadow.has_value() ? (__nv_bfloat16*)shadow->data_ptr() : nullptr, grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr,
-      n, (float)lr, (float)wd, (float)beta1, (float)beta2, (float)eps, (float)(1.0 / bc1), (float)(1.0 / std::sqrt(bc2)));
+      n, (float)lr, (float)wd, (float)beta1, (float)beta2, (float)eps, (float)(1.0 / bc1), (float)(1.0 / std::sqrt(bc2)),
+      hyper.has_value() ? hyper->data_ptr<float>() : nullptr);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }

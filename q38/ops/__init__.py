@@ -96,13 +96,16 @@ def sum_squares(x):
     return load().sum_squares(x)
 
 
-def adamw_flat(p, g, m, v, step, lr, wd, beta1, beta2, eps, grad_scale=None, shadow=None):
+def adamw_flat(p, g, m, v, step, lr, wd, beta1, beta2, eps, grad_scale=None, shadow=None, hyper=None):
+    """`hyper`: optional CUDA fp32 tensor {lr, 1/(1-b1^t), 1/sqrt(1-b2^t)} that overrides the step-dependent scalars, so that a
+    captured launch can be replayed with new values."""
     if grad_scale is not None:
         grad_scale = grad_scale.reshape(1).float()
-    load().adamw_flat(p, g, m, v, shadow, grad_scale, int(step), float(lr), float(wd), float(beta1), float(beta2), float(eps))
+    load().adamw_flat(p, g, m, v, shadow, grad_scale, int(step), float(lr), float(wd), float(beta1), float(beta2), float(eps), hyper)
 
 
 def muon_batched_step(views, per_call, lr, momentum, weight_decay, ns_steps, scale, grad_scale=None):
+    """`lr` is a float or a 0-dim CUDA tensor (replayable step)."""
     from .muon_gpu import batched_step
     batched_step(views, per_call, lr, momentum, weight_decay, ns_steps, scale, grad_scale)
 

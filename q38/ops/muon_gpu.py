@@ -58,6 +58,13 @@ def batched_step(views, per_call, lr, momentum, weight_decay, ns_steps, scale, g
         X = _ns_chain(X.contiguous(), ns_steps)
         if rows > cols:
             X = X.transpose(1, 2)
+        if torch.is_tensor(lr):
+            # learning rate in device memory: the whole step can be captured once and replayed with a new value
+            pieces = list((X.float() * (lr * -scale)).split(counts))
+            if weight_decay:
+                torch._foreach_mul_(params, 1 - lr * weight_decay)
+            torch._foreach_add_(params, pieces)
+            continue
         pieces = list(X.float().split(counts))
         if weight_decay:
             torch._foreach_mul_(params, 1 - lr * weight_decay)

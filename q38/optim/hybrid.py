@@ -15,6 +15,7 @@ contiguous (owner, group) range and only the units owned by ``rank`` are updated
 the stand-alone layout because the torch optimizer objects hold those views as their state.
 """
 import math
+import os
 
 import torch
 
@@ -41,11 +42,11 @@ def split_parameters(model, muon=True):
     return matrices, decay, no_decay
 
 
-def adamw_flat_(p, g, m, v, step, lr, wd, grad_scale=None, betas=ADAM_BETAS, eps=ADAM_EPS):
+def adamw_flat_(p, g, m, v, step, lr, wd, grad_scale=None, betas=ADAM_BETAS, eps=ADAM_EPS, hyper=None):
     """In-place AdamW on flat fp32 tensors with torch.optim.AdamW's arithmetic (decoupled decay first)."""
     if p.is_cuda:
         from ..ops import adamw_flat
-        return adamw_flat(p, g, m, v, step, lr, wd, betas[0], betas[1], eps, grad_scale)
+        return adamw_flat(p, g, m, v, step, lr, wd, betas[0], betas[1], eps, grad_scale, hyper=hyper)
     if grad_scale is not None:
         g = g * grad_scale
     b1, b2 = betas
@@ -62,6 +63,7 @@ class HybridOptimizer:
         matrices, decay, no_decay = split_parameters(model, muon)
         self.names = dict(muon=[n for n, _ in matrices], decay=[n for n, _ in decay], no_decay=[n for n, _ in no_decay])
         self.arena, self.rank, self.steps_done = arena, rank, 0
+        self._graph, self._warmed, self._hyper = None, False, None
         on_gpu = next(model.parameters()).is_cuda
         fused = (on_gpu if fused_adam is None else fused_adam) and arena is None
         self.adam = torch.optim.AdamW(
@@ -104,11 +106,23 @@ class HybridOptimizer:
             return
         a = self.arena
         self.steps_done += 1
+        if a.device.type == "cuda" and os.environ.get("Q38_OPTIMIZER_GRAPH", "1") != "0" and self._same_lr():
+            return self._replayed_step(grad_scale)
+        self._arena_step(grad_scale, None, None)
+
+    def _same_lr(self):
+        lrs = {g["lr"] for g in self.param_groups}
+        return len(lrs) == 1
+
+    def _arena_step(self, grad_scale, hyper, lr_tensor):
+        """AdamW over this rank's flat ranges, then Muon over the matrices it owns.  With `hyper` / `lr_tensor` the learning
+        rate and the bias corrections are read from device memory."""
+        a = self.arena
         for group_name, group in zip(("decay", "no_decay"), self.adam.param_groups):
             s, e = a.group_ranges[(self.rank, group_name)]
             if e > s:
                 adamw_flat_(a.params[s:e], a.grads[s:e], a.exp_avg[s:e], a.exp_avg_sq[s:e], self.steps_done,
-                            group["lr"], group["weight_decay"], grad_scale)
+                            group["lr"], group["weight_decay"], grad_scale, hyper=hyper)
         if self.muon:
             owned = [u.param for u in a.owned(self.rank, "muon")]
             slices = {}
@@ -116,7 +130,43 @@ class HybridOptimizer:
                 owned.append(unit.param)
                 n = unit.param.shape[0] // a.world
                 slices[id(unit.param)] = slice(self.rank * n, (self.rank + 1) * n)
-            self.muon.step(params=owned, grad_scale=grad_scale, slices=slices)
+            self.muon.step(params=owned, grad_scale=grad_scale, slices=slices, lr_tensor=lr_tensor)
+
+    def _replayed_step(self, grad_scale):
+        """The optimizer step as one CUDA graph.  Hundreds of small launches (Newton-Schulz chains per matrix shape) otherwise
+        leave the GPU waiting for the host; learning rate, bias corrections and the clip factor live in device tensors that
+        are refreshed before every replay.  The first step runs eagerly (lazy initialisation), the second is captured."""
+        dev = self.arena.device
+        if self._hyper is None:
+            self._hyper = torch.zeros(4, dtype=torch.float32, device=dev)
+            self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+            self._scale = torch.ones((), dtype=torch.float32, device=dev)
+        lr = self.param_groups[0]["lr"]
+        b1, b2 = ADAM_BETAS
+        t = self.steps_done
+        self._hyper_host[0], self._hyper_host[1], self._hyper_host[2] = lr, 1.0 / (1.0 - b1 ** t), 1.0 / math.sqrt(1.0 - b2 ** t)
+        self._hyper.copy_(self._hyper_host, non_blocking=True)
+        if grad_scale is None:
+            self._scale.fill_(1.0)
+        else:
+            self._scale.copy_(grad_scale.reshape(()).float())
+        if self._graph is None:
+            if not self._warmed:
+                self._warmed = True
+                self._arena_step(self._scale, self._hyper, self._hyper[0])
+                return
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._arena_step(self._scale, self._hyper, self._hyper[0])
+                self._graph = graph
+            except Exception as exc:                         # pragma: no cover - depends on the driver
+                print(f"[q38.optim] optimizer graph capture failed ({type(exc).__name__}: {exc}); stepping eagerly", flush=True)
+                os.environ["Q38_OPTIMIZER_GRAPH"] = "0"
+                torch.cuda.synchronize(dev)
+                self._arena_step(self._scale, self._hyper, self._hyper[0])
+                return
+        self._graph.replay()
 
     def zero_grad(self, set_to_none=True):
         if self.arena is not None:

@@ -55,10 +55,11 @@ class Muon(torch.optim.Optimizer):
         return state["buf"]
 
     @torch.no_grad()
-    def step(self, closure=None, params=None, grad_scale=None, slices=None):
+    def step(self, closure=None, params=None, grad_scale=None, slices=None, lr_tensor=None):
         """`params`: optional subset (the units this rank owns).  `grad_scale`: optional scalar tensor the
         gradients are multiplied with before use (the clip coefficient), without modifying `.grad`.
-        `slices`: ``{id(param): slice}`` restricts a stacked parameter (experts ``[E, a, b]``) to a range of its matrices."""
+        `slices`: ``{id(param): slice}`` restricts a stacked parameter (experts ``[E, a, b]``) to a range of its matrices.
+        `lr_tensor`: optional 0-dim CUDA tensor used instead of the groups' learning rate (CUDA-graph replay)."""
         keep = None if params is None else {id(p) for p in params}
         slices = slices or {}
         on_gpu = any(p.is_cuda for g in self.param_groups for p in g["params"])
@@ -77,7 +78,7 @@ class Muon(torch.optim.Optimizer):
                     buf = self._buffer(p)
                     sl = slices.get(id(p), slice(None))
                     views.append((p.view(-1, rows, cols)[sl], p.grad.view(-1, rows, cols)[sl], buf.view(-1, rows, cols)[sl]))
-                muon_batched_step(views, per_call, lr=group["lr"], momentum=group["momentum"],
+                muon_batched_step(views, per_call, lr=group["lr"] if lr_tensor is None else lr_tensor, momentum=group["momentum"],
                                   weight_decay=group["weight_decay"], ns_steps=group["ns_steps"],
                                   scale=update_scale((rows, cols), group["rms_scale"]), grad_scale=grad_scale)
 

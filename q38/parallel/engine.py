@@ -147,17 +147,16 @@ class GradEngine:
         self._timing.append((name, event))
 
     def phase_times(self):
-        """Mean milliseconds per phase of `finish_step` over the steps recorded so far (Q38_ENGINE_TIMING=1)."""
+        """Median milliseconds per phase of `finish_step` over the steps recorded so far (Q38_ENGINE_TIMING=1); the median
+        ignores the first steps, whose device timeline contains host-side lazy initialisation and graph capture."""
         if not self._timing:
             return {}
         torch.cuda.synchronize(self.device)
-        sums, counts = {}, {}
+        samples = {}
         for (_, e0), (name, e1) in zip(self._timing, self._timing[1:]):
-            if name == "start":
-                continue
-            sums[name] = sums.get(name, 0.0) + e0.elapsed_time(e1)
-            counts[name] = counts.get(name, 0) + 1
-        return {k: round(sums[k] / counts[k], 3) for k in sums}
+            if name != "start":
+                samples.setdefault(name, []).append(e0.elapsed_time(e1))
+        return {k: round(sorted(v)[len(v) // 2], 3) for k, v in samples.items()}
 
     def average_metrics(self, values):
         """Mean over ranks of the loss terms; the last entry (gradient norm) is already global."""

@@ -87,3 +87,28 @@ def test_kernel_parity_script_passes():
     from q38.utils import check_kernels
     assert check_kernels.main(["--hidden", "128", "--seq", "256"]) == 0
     assert check_kernels.main(["--hidden", "256", "--seq", "1024", "--batch", "4"]) == 0
+
+
+def test_replayed_optimizer_step_matches_eager(monkeypatch):
+    """The CUDA-graph replay of the optimizer step (learning rate, bias corrections and clip factor read from device memory)
+    leaves the same parameters as the eager step over several steps with a changing learning rate."""
+    from q38.train import TRAIN_DEFAULTS, Trainer
+    cfg, _ = build()
+    torch.manual_seed(2)
+    x = torch.randint(1, 512, (2, 256)).pin_memory()
+    y = x.roll(-1, 1).pin_memory()
+    results = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("Q38_OPTIMIZER_GRAPH", mode)
+        monkeypatch.setenv("Q38_DETERMINISTIC", "1")
+        torch.manual_seed(0)
+        args = SimpleNamespace(**{**TRAIN_DEFAULTS, "aux_coef": 0.001, "lr": 3e-3, "grad_sync": "collective", "cuda_graphs": 0, "overlap_wgrad": 0})
+        trainer = Trainer(cfg, args, torch.device("cuda", 0))
+        for step in range(5):
+            trainer.train_step([(x, y)], lr=3e-3 * (1.0 - 0.1 * step), dense=True)
+        results[mode] = trainer.engine.arena.params.clone()
+        assert (trainer.opt._graph is not None) == (mode == "1")
+        trainer.close()
+    diff = (results["1"] - results["0"]).abs().max().item()
+    scale = results["0"].abs().max().item()
+    assert diff <= 2e-3 * scale, (diff, scale)
