@@ -700,7 +700,8 @@ class Q38TextCore(nn.Module):
         ckpt = self.gradient_checkpointing and self.training and torch.is_grad_enabled()
         for i in range(len(self.layers)):
             if ckpt:
-                X, kl = torch.utils.checkpoint.checkpoint(self._layer, i, X, ids, cos, sin, dtype, use_reentrant=False)
+                # the layers draw no random numbers, so the RNG state is not saved (reading it is not allowed during CUDA-graph capture)
+                X, kl = torch.utils.checkpoint.checkpoint(self._layer, i, X, ids, cos, sin, dtype, use_reentrant=False, preserve_rng_state=False)
             else:
                 X, kl = self._layer(i, X, ids, cos, sin, dtype)
             if kl is not None:

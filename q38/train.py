@@ -334,7 +334,7 @@ class Trainer:
         self.model.train()
         # One CUDA graph per (micro-batch shape, accumulation count, attention phase) replays forward + backward of a
         # micro-step without any per-kernel host work; the optimizer step stays eager.
-        self.use_graphs = bool(getattr(a, "cuda_graphs", 1)) and dev.type == "cuda" and not getattr(a, "grad_ckpt", 0)
+        self.use_graphs = bool(getattr(a, "cuda_graphs", 1)) and dev.type == "cuda"
         self._graphs = {}
         self.replayed_launches = 0            # kernels of this library executed through graph replays
         if dev.type == "cuda":
