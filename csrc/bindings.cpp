@@ -22,6 +22,8 @@ TORCH_LIBRARY(q38, m) {
   m.def("embed_bwd(Tensor ids, Tensor dout, Tensor(a!) grad) -> ()", &q38::embed_bwd);
   m.def("swiglu_fwd(Tensor g, Tensor u) -> Tensor", &q38::swiglu_fwd);
   m.def("swiglu_bwd(Tensor dy, Tensor g, Tensor u) -> Tensor[]", &q38::swiglu_bwd);
+  m.def("sigmoid_mul_fwd(Tensor x, Tensor g) -> Tensor", &q38::sigmoid_mul_fwd);
+  m.def("sigmoid_mul_bwd(Tensor dy, Tensor x, Tensor g) -> Tensor[]", &q38::sigmoid_mul_bwd);
   m.def("ngram_fwd(Tensor ids, Tensor emb2, Tensor emb3, Tensor norm_w, int vocab, int eos, float eps) -> Tensor[]", &q38::ngram_fwd);
   m.def("ngram_bwd(Tensor de, Tensor rows, Tensor emb2, Tensor emb3, Tensor norm_w, Tensor rstd, Tensor(a!) g2, Tensor(b!) g3) -> Tensor", &q38::ngram_bwd);
   m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps, bool out_bf16) -> Tensor[]");

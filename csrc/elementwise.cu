@@ -263,6 +263,64 @@ std::vector<at::Tensor> swiglu_bwd(const at::Tensor& dy, const at::Tensor& g, co
   return {dg, du};
 }
 
+// ---- output gate of the attention layer: y = x * bf16(sigmoid(g)), elementwise on bf16 (eight elements per thread) -------
+__global__ void __launch_bounds__(256) sigmoid_mul_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                                                               __nv_bfloat16* __restrict__ y, long long n8) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float xv[8], gv[8], o[8];
+  unpack8(reinterpret_cast<const uint4*>(x)[i], xv);
+  unpack8(reinterpret_cast<const uint4*>(g)[i], gv);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) o[k] = xv[k] * bf16_round(sigmoidf_(gv[k]));
+  reinterpret_cast<uint4*>(y)[i] = pack8(o);
+}
+
+__global__ void __launch_bounds__(256) sigmoid_mul_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ dx,
+                                                               __nv_bfloat16* __restrict__ dg, long long n8) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float dv[8], xv[8], gv[8], ox[8], og[8];
+  unpack8(reinterpret_cast<const uint4*>(dy)[i], dv);
+  unpack8(reinterpret_cast<const uint4*>(x)[i], xv);
+  unpack8(reinterpret_cast<const uint4*>(g)[i], gv);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float s = sigmoidf_(gv[k]);
+    ox[k] = dv[k] * s;
+    og[k] = dv[k] * xv[k] * s * (1.f - s);
+  }
+  reinterpret_cast<uint4*>(dx)[i] = pack8(ox);
+  reinterpret_cast<uint4*>(dg)[i] = pack8(og);
+}
+
+at::Tensor sigmoid_mul_fwd(const at::Tensor& x, const at::Tensor& g) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kBFloat16 && x.is_contiguous() && g.is_contiguous() &&
+                  x.numel() == g.numel() && x.numel() % 8 == 0, "sigmoid_mul_fwd: contiguous bf16 tensors of equal size (a multiple of 8 elements) required");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto y = at::empty_like(x);
+  const long long n8 = x.numel() / 8;
+  if (n8) sigmoid_mul_fwd_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)x.data_ptr(), (const __nv_bfloat16*)g.data_ptr(), (__nv_bfloat16*)y.data_ptr(), n8);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return y;
+}
+
+std::vector<at::Tensor> sigmoid_mul_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& g) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.numel() == x.numel(), "sigmoid_mul_bwd: bad gradient");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto dx = at::empty_like(x), dg = at::empty_like(g);
+  const long long n8 = x.numel() / 8;
+  if (n8) sigmoid_mul_bwd_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      (const __nv_bfloat16*)dy.data_ptr(), (const __nv_bfloat16*)x.data_ptr(), (const __nv_bfloat16*)g.data_ptr(), (__nv_bfloat16*)dx.data_ptr(),
+      (__nv_bfloat16*)dg.data_ptr(), n8);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+  return {dx, dg};
+}
+
 // ---- shared-expert merge: out = routed + sigmoid(logit_t) * shared  (one warp per token row, 16-byte accesses) ------------
 __global__ void __launch_bounds__(256) gate_add_fwd_kernel(const __nv_bfloat16* __restrict__ routed, const __nv_bfloat16* __restrict__ shared,
                                                             const __nv_bfloat16* __restrict__ logit, __nv_bfloat16* __restrict__ out, int T, int h) {

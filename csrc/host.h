@@ -39,6 +39,9 @@ std::vector<at::Tensor> gdn_gates_bwd(const at::Tensor& dbeta, const at::Tensor&
 at::Tensor swiglu_fwd(const at::Tensor& g, const at::Tensor& u);
 std::vector<at::Tensor> swiglu_bwd(const at::Tensor& dy, const at::Tensor& g, const at::Tensor& u);
 
+at::Tensor sigmoid_mul_fwd(const at::Tensor& x, const at::Tensor& g);
+std::vector<at::Tensor> sigmoid_mul_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& g);
+
 // ngram.cu
 void embed_bwd(const at::Tensor& ids, const at::Tensor& dout, at::Tensor& grad);
 std::vector<at::Tensor> ngram_fwd(const at::Tensor& ids, const at::Tensor& emb2, const at::Tensor& emb3, const at::Tensor& norm_w, int64_t vocab,

@@ -391,6 +391,22 @@ class _SwiGLU(torch.autograd.Function):
         return dg, du
 
 
+class _SigmoidMul(torch.autograd.Function):
+    """x * sigmoid(g) on bf16 tensors of equal shape (the output gate of the attention layer), one kernel each way."""
+
+    @staticmethod
+    def forward(ctx, x, g):
+        x, g = x.contiguous(), g.contiguous()
+        ctx.save_for_backward(x, g)
+        return load().sigmoid_mul_fwd(x, g)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, g = ctx.saved_tensors
+        dx, dg = load().sigmoid_mul_bwd(dy.contiguous(), x, g)
+        return dx, dg
+
+
 class _GateAdd(torch.autograd.Function):
     """routed + sigmoid(logit) * shared for [T,h] bf16 rows and one logit per row (the shared-expert merge of the MoE block)."""
 
@@ -746,7 +762,8 @@ class Backend:
         else:
             count, index = load().qsa_select(lp_blk, budget)
             o = _BlockAttention.apply(q, k, v, count, index, attn.scaling)
-        o = o.reshape(B, S, -1) * torch.sigmoid(gate)
+        o = o.reshape(B, S, -1)
+        o = _SigmoidMul.apply(o, gate) if (o.numel() % 8 == 0 and o.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16) else o * torch.sigmoid(gate)
         return self.linear(o, attn.o_proj.weight), kl
 
     def embedding(self, weight, ids):
