@@ -47,7 +47,7 @@ def parse():
     return ap.parse_args()
 
 
-REFERENCE_UNAVAILABLE = ("not installable: /root/reference has no setup.py/pyproject.toml (pip exit 1), and its model file fails to "
+REFERENCE_UNAVAILABLE = ("not installable: the reference source tree has no setup.py/pyproject.toml (pip exit 1), and its model file fails to "
                          "import under the image's transformers 5.5.0 (ImportError: use_kernel_func_from_hub_with_fallback)")
 
 
