@@ -63,3 +63,33 @@ def test_synthetic_stream(tmp_path):
     ids = np.fromfile(tmp_path / "s" / "train.bin", dtype="<u4")
     assert len(ids) == 20000 and ids.max() < 10112 and 100 < np.count_nonzero(ids == 53) < 400
     assert (tmp_path / "s" / "train.bin").stat().st_size % 4 == 0
+
+
+def test_evaluator_packing(tmp_path):
+    """JSONL -> packed token / text-mask files -> fixed-length batches whose labels skip document separators and padding
+    (q38.evaluate; reference: q38/evaluate.py:26-71)."""
+    import json
+    import numpy as np
+    from transformers import PreTrainedTokenizerFast
+    from q38.data import DEFAULT_TOKENIZER
+    from q38.evaluate import pack_jsonl, packed_batch
+    tok = PreTrainedTokenizerFast.from_pretrained(str(DEFAULT_TOKENIZER), local_files_only=True)
+    texts = ["hello world, this is a test.", "second document", "third one is a little longer than the others"]
+    path = tmp_path / "eval.jsonl"
+    path.write_text("".join(json.dumps({"text": t}) + "\n" for t in texts) + "\n")
+    meta = pack_jsonl(path, tok, tmp_path)
+    tokens = np.fromfile(tmp_path / "tokens.bin", dtype=np.int32)
+    is_text = np.fromfile(tmp_path / "is_text.bin", dtype=np.bool_)
+    assert meta["total_bytes"] == sum(len(t.encode()) for t in texts)
+    assert len(tokens) == len(is_text) == meta["total_tokens"] + len(texts)
+    assert int((~is_text).sum()) == len(texts) and tokens[0] == tok.eos_token_id and not is_text[0]
+    seq = 8
+    n_seq = -(-(len(tokens) - 1) // seq)
+    x, y = packed_batch(tokens, is_text, 0, n_seq, seq, meta["pad_token_id"])
+    assert x.shape == y.shape == (n_seq, seq)
+    flat_x, flat_y = x.reshape(-1), y.reshape(-1)
+    n = len(tokens) - 1
+    assert np.array_equal(flat_x[:n], tokens[:n]) and (flat_x[n:] == meta["pad_token_id"]).all() and (flat_y[n:] == -100).all()
+    scored = flat_y[:n] != -100
+    assert np.array_equal(scored, is_text[1:n + 1]) and np.array_equal(flat_y[:n][scored], tokens[1:n + 1][scored])
+    assert int(scored.sum()) == meta["total_tokens"]                   # every text token is a label exactly once
