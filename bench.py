@@ -23,7 +23,6 @@ from pathlib import Path
 from types import SimpleNamespace
 
 ROOT = Path(__file__).resolve().parent
-sys.path.insert(0, str(ROOT))
 
 
 def parse():
@@ -47,15 +46,19 @@ def parse():
     return ap.parse_args()
 
 
-REFERENCE_UNAVAILABLE = ("not installable: the reference source tree has no setup.py/pyproject.toml (pip exit 1), and its model file fails to "
-                         "import under the image's transformers 5.5.0 (ImportError: use_kernel_func_from_hub_with_fallback)")
+def reference_arm(a):
+    """Run the unmodified reference (baseline/_ref) in this process; this repository's q38 package is never imported."""
+    sys.path[:] = [p for p in sys.path if Path(p or ".").resolve() != ROOT]
+    sys.path.insert(0, str(ROOT / "baseline"))
+    import ref_bench
+    return ref_bench.main(a)
 
 
 def main():
     a = parse()
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return reference_arm(a)
+    sys.path.insert(0, str(ROOT))
     import numpy as np
     import torch
     import torch.distributed as dist
