@@ -15,6 +15,12 @@ have a different signature.  They are added to *transformers* here; no file of t
 4. ``PreTrainedModel._initialize_weights`` – accept the ``is_custom_code=`` keyword the reference passes and forward
    it as this release's ``is_remote_code``.
 
+5. torch 2.11's Inductor picks ``FlexBwDConfig(64, 128, 128, 64)`` as the only flex-attention backward candidate on
+   sm_100 and then drops it because the reference's sparse block size (64) is not a multiple of 128, so the stock QSA
+   backward fails to compile ("NoValidChoicesError: No choices exist for backend", target flex_attention_backward).
+   The candidate list gets the (64, 64, 64, 64, stages 2, warps 4) entry that the same table uses on sm_8x, where the
+   reference was developed; the block sizes actually compiled are the ones the reference passes in ``kernel_options``.
+
 ``activate()`` applies the shims once and puts ``baseline/_ref`` first on ``sys.path`` so that ``import q38`` is the
 reference's package.  It must run in a process that never imports this repository's own ``q38``.
 """
@@ -74,6 +80,27 @@ def _missing_mask(*_args, **_kwargs):
     raise NotImplementedError("create_recurrent_attention_mask is not part of this transformers release")
 
 
+def _add_flex_backward_candidate():
+    try:
+        from torch._inductor.template_heuristics import triton as heuristics
+    except Exception:
+        return
+    cls = getattr(heuristics, "CUDAConfigHeuristic", None)
+    if cls is None or getattr(cls, "_q38_ref_patch", False):
+        return
+    original = cls.get_flex_attn_bwd_configs
+
+    def get_flex_attn_bwd_configs(self, head_dim, dtype):
+        configs = list(original(self, head_dim, dtype))
+        extra = heuristics.FlexBwDConfig(64, 64, 64, 64, 2, 4)
+        if extra not in configs:
+            configs.append(extra)
+        return configs
+
+    cls.get_flex_attn_bwd_configs = get_flex_attn_bwd_configs
+    cls._q38_ref_patch = True
+
+
 def activate():
     global _DONE
     if _DONE:
@@ -98,5 +125,6 @@ def activate():
         def _initialize_weights(self, module, is_remote_code=False, is_custom_code=None):
             return original(self, module, is_remote_code=bool(is_custom_code) if is_custom_code is not None else is_remote_code)
         PreTrainedModel._initialize_weights = _initialize_weights
+    _add_flex_backward_candidate()
     sys.path.insert(0, str(REF_ROOT))
     _DONE = True

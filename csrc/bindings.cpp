@@ -9,10 +9,27 @@ namespace q38 { std::atomic<long long> g_launches{0}; }
 TORCH_LIBRARY(q38, m) {
   m.def("launch_count() -> int", []() -> int64_t { return (int64_t)q38::g_launches.load(); });
   m.def("gemm_bf16(Tensor a, Tensor b, Tensor(a!) c, bool a_mn_major, bool b_mn_major, float alpha, bool accumulate, Tensor(b!) err, int splits) -> ()");
-  m.def("gemm_bf16_persistent(Tensor a, Tensor b, Tensor(a!) c, bool a_mn_major, bool b_mn_major, float alpha, bool accumulate, Tensor(b!) err, int splits) -> ()",
-        [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool amn, bool bmn, double alpha, bool acc, at::Tensor& err, int64_t splits) {
-          q38::gemm_bf16_persistent(a, b, c, amn, bmn, alpha, acc, err, splits);
+  m.def("gemm_bf16_persistent(Tensor a, Tensor b, Tensor(a!) c, bool a_mn_major, bool b_mn_major, float alpha, bool accumulate, Tensor(b!) err, int splits, Tensor? addend=None, float beta=0.0) -> ()",
+        [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool amn, bool bmn, double alpha, bool acc, at::Tensor& err, int64_t splits,
+           c10::optional<at::Tensor> addend, double beta) {
+          q38::gemm_bf16_persistent(a, b, c, amn, bmn, alpha, acc, err, splits, addend, beta);
         });
+  m.def("muon_prepass(Tensor grads, Tensor(a!) buf, Tensor(b!) work, Tensor(c!) sumsq, Tensor mats, Tensor tiles, Tensor? grad_scale, float momentum, Tensor? err) -> ()",
+        [](const at::Tensor& g, at::Tensor& b, at::Tensor& w, at::Tensor& s, const at::Tensor& mats, const at::Tensor& tiles, c10::optional<at::Tensor> gs, double mom,
+           c10::optional<at::Tensor> err) { q38::muon_prepass(g, b, w, s, mats, tiles, gs, mom, err); });
+  m.def("muon_normalize(Tensor(a!) work, Tensor(b!) sumsq, Tensor mats, Tensor tiles, float eps, Tensor? err) -> ()",
+        [](at::Tensor& w, at::Tensor& s, const at::Tensor& mats, const at::Tensor& tiles, double eps, c10::optional<at::Tensor> err) {
+          q38::muon_normalize(w, s, mats, tiles, eps, err);
+        });
+  m.def("muon_apply(Tensor(a!) params, Tensor? shadow, Tensor work, Tensor mats, Tensor tiles, Tensor scales, Tensor? hyper, float lr, float wd, Tensor? err) -> ()",
+        [](at::Tensor& p, c10::optional<at::Tensor> sh, const at::Tensor& w, const at::Tensor& mats, const at::Tensor& tiles, const at::Tensor& scales,
+           c10::optional<at::Tensor> hyper, double lr, double wd, c10::optional<at::Tensor> err) { q38::muon_apply(p, sh, w, mats, tiles, scales, hyper, lr, wd, err); });
+  m.def("muon_small_ns(Tensor src, Tensor(a!) dst, int rows, int cols, int steps, Tensor? err) -> ()",
+        [](const at::Tensor& src, at::Tensor& dst, int64_t rows, int64_t cols, int64_t steps, c10::optional<at::Tensor> err) {
+          q38::muon_small_ns(src, dst, rows, cols, steps, err);
+        });
+  m.def("cast_shadow_except(Tensor params, Tensor(a!) shadow, int skip_start, int skip_count, Tensor? err) -> ()",
+        [](const at::Tensor& p, at::Tensor& sh, int64_t s0, int64_t n, c10::optional<at::Tensor> err) { q38::cast_shadow_except(p, sh, s0, n, err); });
   m.def("qsa_headprep_fwd(Tensor src, Tensor? w, Tensor cos, Tensor sin, float eps, bool split_gate) -> Tensor[]", &q38::qsa_headprep_fwd);
   m.def("qsa_headprep_bwd(Tensor dout, Tensor? dgate, Tensor src, Tensor? w, Tensor cos, Tensor sin, Tensor rstd) -> Tensor[]", &q38::qsa_headprep_bwd);
   m.def("gate_add_fwd(Tensor routed, Tensor shared, Tensor logit) -> Tensor", &q38::gate_add_fwd);
@@ -30,7 +47,7 @@ TORCH_LIBRARY(q38, m) {
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) -> Tensor[]");
   m.def("gated_rmsnorm_fwd(Tensor x, Tensor gate, Tensor w, float eps) -> Tensor");
   m.def("gated_rmsnorm_bwd(Tensor dy, Tensor x, Tensor gate, Tensor w, float eps) -> Tensor[]");
-  m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps, Tensor? hyper) -> ()");
+  m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps, Tensor? hyper, Tensor? err=None) -> ()");
   m.def("sum_squares(Tensor x) -> Tensor");
   m.def("qsa_main_block_stats(Tensor q, Tensor k, float scale) -> Tensor");
   m.def("qsa_indexer_fwd(Tensor qi, Tensor ki, Tensor wi, float scale) -> Tensor");
@@ -56,12 +73,13 @@ TORCH_LIBRARY(q38, m) {
   m.def("p2p_close_handle(int ptr, int device) -> ()", &q38::p2p_close_handle);
   m.def("p2p_barrier(Tensor(a!) own_flags, int[] peer_flags, int rank, int epoch, float wait_seconds, Tensor(b!) err) -> ()",
         [](at::Tensor& f, std::vector<int64_t> peers, int64_t rank, int64_t epoch, double wait, at::Tensor& err) { q38::p2p_barrier(f, peers, rank, epoch, wait, err); });
-  m.def("p2p_reduce_scatter(int[] grads, int rank, int start, int count, float scale, int device) -> ()",
-        [](std::vector<int64_t> g, int64_t rank, int64_t start, int64_t count, double scale, int64_t dev) { q38::p2p_reduce_scatter(g, rank, start, count, scale, dev); });
-  m.def("p2p_all_gather(Tensor params, Tensor? shadow, int[] peer_params, int[] peer_shadow, int rank, int start, int count) -> ()",
-        [](const at::Tensor& p, c10::optional<at::Tensor> sh, std::vector<int64_t> pp, std::vector<int64_t> ps, int64_t rank, int64_t start, int64_t count) {
-          q38::p2p_all_gather(p, sh, pp, ps, rank, start, count);
+  m.def("p2p_reduce_scatter(int[] grads, int rank, int start, int count, float scale, int device, Tensor? err=None) -> ()",
+        [](std::vector<int64_t> g, int64_t rank, int64_t start, int64_t count, double scale, int64_t dev, c10::optional<at::Tensor> err) {
+          q38::p2p_reduce_scatter(g, rank, start, count, scale, dev, err);
         });
+  m.def("p2p_all_gather(Tensor params, Tensor? shadow, int[] peer_params, int[] peer_shadow, int rank, int start, int count, Tensor? err=None) -> ()",
+        [](const at::Tensor& p, c10::optional<at::Tensor> sh, std::vector<int64_t> pp, std::vector<int64_t> ps, int64_t rank, int64_t start, int64_t count,
+           c10::optional<at::Tensor> err) { q38::p2p_all_gather(p, sh, pp, ps, rank, start, count, err); });
   m.def("p2p_publish_scalar(Tensor value, int[] peer_slots, int rank) -> ()",
         [](const at::Tensor& v, std::vector<int64_t> slots, int64_t rank) { q38::p2p_publish_scalar(v, slots, rank); });
   m.def("ce_inplace(Tensor(a!) logits, Tensor target) -> Tensor", [](at::Tensor& l, const at::Tensor& t) { return q38::ce_inplace(l, t); });
@@ -99,8 +117,8 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
   m.impl("gated_rmsnorm_bwd", &q38::gated_rmsnorm_bwd);
   m.impl("adamw_flat", [](at::Tensor& p, const at::Tensor& g, at::Tensor& mm, at::Tensor& v, c10::optional<at::Tensor> shadow,
                           c10::optional<at::Tensor> gs, int64_t step, double lr, double wd, double b1, double b2, double eps,
-                          c10::optional<at::Tensor> hyper) {
-    q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps, hyper);
+                          c10::optional<at::Tensor> hyper, c10::optional<at::Tensor> err) {
+    q38::adamw_flat(p, g, mm, v, shadow, gs, step, lr, wd, b1, b2, eps, hyper, err);
   });
   m.impl("sum_squares", &q38::sum_squares);
   m.impl("qsa_main_block_stats", &q38::qsa_main_block_stats);

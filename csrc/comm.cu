@@ -29,18 +29,29 @@ __device__ __forceinline__ long long ld_volatile_ll(const long long* p) {
   return v;
 }
 
+// Layout of a rank's flag array (int64 words): [0, MAX_PEERS) arrival slots written by the peers, [MAX_PEERS] the
+// device-side epoch counter, [MAX_PEERS + 1] the abort word.
+constexpr int FLAG_EPOCH = MAX_PEERS, FLAG_ABORT = MAX_PEERS + 1;
+
 // One CTA of 32 threads.  wait_cycles bounds the spin (about a second at 2 GHz by default).
-// epoch < 0: take the next value of the device-side counter own_flags[MAX_PEERS] (all ranks execute the same sequence
+// epoch < 0: take the next value of the device-side counter own_flags[FLAG_EPOCH] (all ranks execute the same sequence
 // of barriers, so the counters stay in lockstep; this form can be captured in a CUDA graph and replayed).
+// A rank whose wait runs out records ERR_PEER_WAIT and raises the abort word of every peer; a rank that finds its abort
+// word raised (on entry or while it waits) records the same error.  Kernels that write parameters, optimizer state or
+// peer memory return without writing once the error word is set, so a late or missing rank cannot make the others step
+// on unreduced gradients or tear a checkpoint that is being written.
 __global__ void p2p_barrier_kernel(long long* __restrict__ own_flags, PeerPtrs peers, int rank, int world, long long epoch,
                                    long long wait_cycles, int* __restrict__ err) {
   const int t = threadIdx.x;
   __shared__ long long next;
+  __shared__ int failed;
+  if (t == 0) failed = 0;
   if (epoch < 0) {
-    if (t == 0) { next = own_flags[MAX_PEERS] + 1; own_flags[MAX_PEERS] = next; }
+    if (t == 0) { next = own_flags[FLAG_EPOCH] + 1; own_flags[FLAG_EPOCH] = next; }
     __syncthreads();
     epoch = next;
   }
+  __syncthreads();
   __threadfence_system();                                  // everything this GPU wrote before the barrier is visible first
   if (t < world) {
     long long* dst = reinterpret_cast<long long*>(peers.p[t]) + rank;
@@ -50,16 +61,31 @@ __global__ void p2p_barrier_kernel(long long* __restrict__ own_flags, PeerPtrs p
     const long long start = clock64();
     bool ok = false;
     while (clock64() - start < wait_cycles) {
+      if (ld_volatile_ll(own_flags + FLAG_ABORT) != 0) break;
       if (ld_volatile_ll(own_flags + t) >= epoch) { ok = true; break; }
       __nanosleep(200);
     }
-    if (!ok) report_error(err, ERR_PEER_WAIT);
+    if (!ok) { report_error(err, ERR_PEER_WAIT); failed = 1; }
+  }
+  __syncthreads();
+  if (failed && t < world) {
+    long long* dst = reinterpret_cast<long long*>(peers.p[t]) + FLAG_ABORT;
+    asm volatile("st.volatile.global.s64 [%0], %1;" ::"l"(dst), "l"(1LL) : "memory");
   }
   __threadfence_system();
 }
 
+__device__ __forceinline__ bool aborted(const int* err) {
+  if (err == nullptr) return false;
+  int v;
+  asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(err) : "memory");
+  return v != 0;
+}
+
 // own[i] = scale * sum_p grads_p[i] for i in [start, start + count); 16-byte loads; count and start multiples of 4.
-__global__ void __launch_bounds__(256) p2p_reduce_scatter_kernel(PeerPtrs grads, int rank, int world, long long start, long long count, float scale) {
+__global__ void __launch_bounds__(256) p2p_reduce_scatter_kernel(PeerPtrs grads, int rank, int world, long long start, long long count, float scale,
+                                                                 const int* __restrict__ err) {
+  if (aborted(err)) return;
   const float4* src[MAX_PEERS];
 #pragma unroll
   for (int p = 0; p < MAX_PEERS; ++p) src[p] = p < world ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + start) : nullptr;
@@ -77,7 +103,9 @@ __global__ void __launch_bounds__(256) p2p_reduce_scatter_kernel(PeerPtrs grads,
 
 // Push segment [start, start + count) of the local fp32 parameters (and bf16 shadow) into every peer's arenas.
 __global__ void __launch_bounds__(256) p2p_all_gather_kernel(const float* __restrict__ params, const __nv_bfloat16* __restrict__ shadow, PeerPtrs peer_params,
-                                                             PeerPtrs peer_shadow, int rank, int world, long long start, long long count) {
+                                                             PeerPtrs peer_shadow, int rank, int world, long long start, long long count,
+                                                             const int* __restrict__ err) {
+  if (aborted(err)) return;
   const long long n4 = count / 4;
   const float4* src = reinterpret_cast<const float4*>(params + start);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
@@ -94,6 +122,21 @@ __global__ void __launch_bounds__(256) p2p_all_gather_kernel(const float* __rest
         if (shadow != nullptr) reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(peer_shadow.p[p]) + start)[i] = packed;
       }
     }
+  }
+}
+
+// shadow[i] = bf16(params[i]) for every i outside [skip_start, skip_start + skip_count): after the all-gather has delivered the
+// peers' fp32 segments, each rank derives their bf16 copies locally instead of receiving them over NVLink.
+__global__ void __launch_bounds__(256) cast_shadow_except_kernel(const float* __restrict__ params, __nv_bfloat16* __restrict__ shadow, long long n4,
+                                                                 long long skip_lo4, long long skip_hi4, const int* __restrict__ err) {
+  if (aborted(err)) return;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    if (i >= skip_lo4 && i < skip_hi4) continue;
+    const float4 v = reinterpret_cast<const float4*>(params)[i];
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo); packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(shadow)[i] = packed;
   }
 }
 
@@ -150,25 +193,41 @@ void p2p_barrier(at::Tensor& own_flags, std::vector<int64_t> peer_flags, int64_t
   count_launch();
 }
 
-void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start, int64_t count, double scale, int64_t device) {
+void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start, int64_t count, double scale, int64_t device,
+                        const c10::optional<at::Tensor>& err) {
   const c10::cuda::CUDAGuard guard((c10::DeviceIndex)device);
   TORCH_CHECK(start % 4 == 0 && count % 4 == 0, "p2p_reduce_scatter: segment must be 16-byte aligned");
   if (count == 0) return;
   const int grid = (int)std::min<int64_t>((count / 4 + 255) / 256, kNumSMs * 8);
-  p2p_reduce_scatter_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(to_ptrs(grads), (int)rank, (int)grads.size(), start, count, (float)scale);
+  p2p_reduce_scatter_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(to_ptrs(grads), (int)rank, (int)grads.size(), start, count, (float)scale,
+                                                                                err.has_value() ? err->data_ptr<int>() : nullptr);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }
 
 void p2p_all_gather(const at::Tensor& params, const c10::optional<at::Tensor>& shadow, std::vector<int64_t> peer_params, std::vector<int64_t> peer_shadow,
-                    int64_t rank, int64_t start, int64_t count) {
+                    int64_t rank, int64_t start, int64_t count, const c10::optional<at::Tensor>& err) {
   const c10::cuda::CUDAGuard guard(params.device());
   TORCH_CHECK(start % 4 == 0 && count % 4 == 0, "p2p_all_gather: segment must be 16-byte aligned");
   if (count == 0) return;
   const int grid = (int)std::min<int64_t>((count / 4 + 255) / 256, kNumSMs * 8);
   p2p_all_gather_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(params.data_ptr<float>(),
       shadow.has_value() ? (const __nv_bfloat16*)shadow->data_ptr() : nullptr, to_ptrs(peer_params), to_ptrs(peer_shadow), (int)rank,
-      (int)peer_params.size(), start, count);
+      (int)peer_params.size(), start, count, err.has_value() ? err->data_ptr<int>() : nullptr);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void cast_shadow_except(const at::Tensor& params, at::Tensor& shadow, int64_t skip_start, int64_t skip_count, const c10::optional<at::Tensor>& err) {
+  TORCH_CHECK(params.is_cuda() && params.scalar_type() == at::kFloat && shadow.scalar_type() == at::kBFloat16 && params.numel() == shadow.numel() &&
+              params.is_contiguous() && shadow.is_contiguous(), "cast_shadow_except: flat fp32 parameters and a bf16 shadow of the same length required");
+  TORCH_CHECK(params.numel() % 4 == 0 && skip_start % 4 == 0 && skip_count % 4 == 0, "cast_shadow_except: lengths must be multiples of 4");
+  const c10::cuda::CUDAGuard guard(params.device());
+  const long long n4 = params.numel() / 4;
+  if (!n4) return;
+  const int grid = (int)std::min<int64_t>((n4 + 255) / 256, kNumSMs * 8);
+  cast_shadow_except_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(params.data_ptr<float>(), (__nv_bfloat16*)shadow.data_ptr(), n4, skip_start / 4,
+                                                                                (skip_start + skip_count) / 4, err.has_value() ? err->data_ptr<int>() : nullptr);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }

@@ -503,7 +503,8 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(float* __restrict__ p, 
                                                           float* __restrict__ v, __nv_bfloat16* __restrict__ shadow,
                                                           const float* __restrict__ grad_scale, size_t n, float lr, float wd, float b1,
                                                           float b2, float eps, float inv_bc1, float inv_sqrt_bc2,
-                                                          const float* __restrict__ hyper) {
+                                                          const float* __restrict__ hyper, const int* __restrict__ err) {
+  if (err != nullptr && *reinterpret_cast<const volatile int*>(err) != 0) return;   // a peer missed a barrier: leave parameters and moments untouched
   const float gs = grad_scale ? *grad_scale : 1.f;
   if (hyper) { lr = hyper[0]; inv_bc1 = hyper[1]; inv_sqrt_bc2 = hyper[2]; }   // step-dependent scalars from device memory (CUDA-graph replay)
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -519,7 +520,7 @@ __global__ void __launch_bounds__(256) adamw_flat_kernel(float* __restrict__ p, 
 
 void adamw_flat(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v, c10::optional<at::Tensor> shadow,
                 c10::optional<at::Tensor> grad_scale, int64_t step, double lr, double wd, double beta1, double beta2, double eps,
-                c10::optional<at::Tensor> hyper) {
+                c10::optional<at::Tensor> hyper, c10::optional<at::Tensor> err) {
   TORCH_CHECK(!hyper.has_value() || (hyper->is_cuda() && hyper->scalar_type() == at::kFloat && hyper->is_contiguous() && hyper->numel() >= 3),
               "adamw_flat: hyper must be a CUDA fp32 tensor {lr, 1/(1-b1^t), 1/sqrt(1-b2^t)}");
   TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kFloat && p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(),
@@ -533,7 +534,7 @@ void adamw_flat(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v
       p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
       shadow.has_value() ? (__nv_bfloat16*)shadow->data_ptr() : nullptr, grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr,
       n, (float)lr, (float)wd, (float)beta1, (float)beta2, (float)eps, (float)(1.0 / bc1), (float)(1.0 / std::sqrt(bc2)),
-      hyper.has_value() ? hyper->data_ptr<float>() : nullptr);
+      hyper.has_value() ? hyper->data_ptr<float>() : nullptr, err.has_value() ? err->data_ptr<int>() : nullptr);
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }

@@ -28,6 +28,10 @@ struct PGemmArgs {
   long long ldc, c_batch_stride;
   float alpha;
   int* err;
+  // optional addend (bf16 outputs): C = alpha * A.B^T + beta * Cin, Cin bf16 with the shape of C and its own strides
+  const __nv_bfloat16* Cin;
+  long long ldcin, cin_batch_stride;
+  float beta;
 };
 
 // TMA_OUT: every epilogue warp stages 32 rows x 32 columns in shared memory (64-byte swizzle for bf16, 128-byte for fp32, both
@@ -150,6 +154,36 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
         uint32_t r[32];
         ptx::tmem_ld_32x32b_x32(t_addr + c0, r);
         ptx::tmem_ld_wait();
+        float alpha = p.alpha;
+        if constexpr (sizeof(OutT) == 2) {
+          if (p.Cin != nullptr) {                              // fold alpha * acc + beta * Cin into the registers
+            if (row < p.M) {
+              const __nv_bfloat16* cin_row = p.Cin + bz * p.cin_batch_stride + (long long)row * p.ldcin;
+              const bool cin_vec = (p.ldcin % 8 == 0) && (p.cin_batch_stride % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.Cin) & 15) == 0);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                const int col = n0 + c0 + v * 8;
+                if (cin_vec && col + 8 <= p.N) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(cin_row + col);
+                  const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qw[e]));
+                    r[v * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * e]) * alpha + p.beta * f.x);
+                    r[v * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * e + 1]) * alpha + p.beta * f.y);
+                  }
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const float c = (col + e < p.N) ? __bfloat162float(cin_row[col + e]) : 0.f;
+                    r[v * 8 + e] = __float_as_uint(__uint_as_float(r[v * 8 + e]) * alpha + p.beta * c);
+                  }
+                }
+              }
+            }
+            alpha = 1.f;
+          }
+        }
         if constexpr (TMA_OUT) {
           uint8_t* buf = stage_out + (quarter * 2 + (chunk & 1)) * 4096;
           if (lane == 0) ptx::bulk_wait_read<1>();               // the store issued two chunks ago has read this buffer
@@ -160,7 +194,7 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
               uint32_t wd[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]) * p.alpha, __uint_as_float(r[v * 8 + 2 * e + 1]) * p.alpha);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]) * alpha, __uint_as_float(r[v * 8 + 2 * e + 1]) * alpha);
                 wd[e] = *reinterpret_cast<uint32_t*>(&h2);
               }
               *reinterpret_cast<uint4*>(buf + lane * 64 + ((v ^ ((lane >> 1) & 3)) << 4)) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
@@ -169,8 +203,8 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
 #pragma unroll
             for (int v = 0; v < 8; ++v)
               *reinterpret_cast<float4*>(buf + lane * 128 + ((v ^ (lane & 7)) << 4)) =
-                  make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha, __uint_as_float(r[v * 4 + 2]) * p.alpha,
-                              __uint_as_float(r[v * 4 + 3]) * p.alpha);
+                  make_float4(__uint_as_float(r[v * 4]) * alpha, __uint_as_float(r[v * 4 + 1]) * alpha, __uint_as_float(r[v * 4 + 2]) * alpha,
+                              __uint_as_float(r[v * 4 + 3]) * alpha);
           }
           ptx::fence_proxy_async();
           __syncwarp();
@@ -193,7 +227,7 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
                 uint32_t wd[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]) * p.alpha, __uint_as_float(r[v * 8 + 2 * e + 1]) * p.alpha);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]) * alpha, __uint_as_float(r[v * 8 + 2 * e + 1]) * alpha);
                   wd[e] = *reinterpret_cast<uint32_t*>(&h2);
                 }
                 *reinterpret_cast<uint4*>(c_row + col0 + v * 8) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
@@ -202,8 +236,8 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
 #pragma unroll
               for (int v = 0; v < 8; ++v) {
                 float4* dst = reinterpret_cast<float4*>(c_row + col0 + v * 4);
-                float4 o = make_float4(__uint_as_float(r[v * 4]) * p.alpha, __uint_as_float(r[v * 4 + 1]) * p.alpha,
-                                       __uint_as_float(r[v * 4 + 2]) * p.alpha, __uint_as_float(r[v * 4 + 3]) * p.alpha);
+                float4 o = make_float4(__uint_as_float(r[v * 4]) * alpha, __uint_as_float(r[v * 4 + 1]) * alpha,
+                                       __uint_as_float(r[v * 4 + 2]) * alpha, __uint_as_float(r[v * 4 + 3]) * alpha);
                 if (ACCUM && p.splits > 1) {
                   float* d = reinterpret_cast<float*>(dst);
                   atomicAdd(d, o.x); atomicAdd(d + 1, o.y); atomicAdd(d + 2, o.z); atomicAdd(d + 3, o.w);
@@ -217,7 +251,7 @@ __global__ void __launch_bounds__(P_THREADS) gemm_persistent_kernel(const __grid
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               if (col0 + e < p.N && c0 + e < p.bn) {
-                float v = __uint_as_float(r[e]) * p.alpha;
+                float v = __uint_as_float(r[e]) * alpha;
                 if constexpr (ACCUM && sizeof(OutT) == 4) {
                   if (p.splits > 1) { atomicAdd(reinterpret_cast<float*>(c_row) + col0 + e, v); continue; }
                 }
@@ -304,7 +338,7 @@ static void launch_p(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
 
 // Same contract as gemm_bf16 (bf16 operands only).
 void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
-                          bool accumulate, at::Tensor& err, int64_t splits) {
+                          bool accumulate, at::Tensor& err, int64_t splits, const c10::optional<at::Tensor>& addend, double beta) {
   const bool tf32 = a.scalar_type() == at::kFloat;
   TORCH_CHECK(a.is_cuda() && (tf32 || a.scalar_type() == at::kBFloat16) && b.scalar_type() == a.scalar_type() && a.dim() == 3 && b.dim() == 3 && c.dim() == 3,
               "gemm_bf16_persistent: bf16 (or fp32 for tf32 math) [batch, rows, cols] operands required");
@@ -342,6 +376,12 @@ void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& 
   p.splits = (p.total_kb + p.kb_per_split - 1) / p.kb_per_split;
   p.work_items = p.tiles_m * p.tiles_n * batch * p.splits;
   p.C = c.data_ptr(); p.ldc = c.stride(1); p.c_batch_stride = c.stride(0); p.alpha = (float)alpha; p.err = err.data_ptr<int>();
+  p.Cin = nullptr; p.ldcin = 0; p.cin_batch_stride = 0; p.beta = 0.f;
+  if (addend.has_value()) {
+    TORCH_CHECK(!out_fp32 && addend->scalar_type() == at::kBFloat16 && addend->dim() == 3 && addend->size(0) == batch && addend->size(1) == M &&
+                addend->size(2) == N && addend->stride(2) == 1, "gemm_bf16_persistent: the addend must be a bf16 tensor of the output's shape (bf16 output only)");
+    p.Cin = (const __nv_bfloat16*)addend->data_ptr(); p.ldcin = addend->stride(1); p.cin_batch_stride = addend->stride(0); p.beta = (float)beta;
+  }
   CUtensorMap ta, tb;
   Q38_TRACE("[gemm_p] args bn=%d tiles=%dx%d splits=%d items=%d\n", bn, p.tiles_m, p.tiles_n, p.splits, p.work_items);
   ta = make_tmap_box(a.data_ptr(), eb, a.size(2), a.size(1), batch, a.stride(1), a.stride(0), a_mn_major ? 64 : P_BM, 128);

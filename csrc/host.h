@@ -21,7 +21,15 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_m
                bool accumulate, at::Tensor& err, int64_t splits);
 
 void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
-                          bool accumulate, at::Tensor& err, int64_t splits);
+                          bool accumulate, at::Tensor& err, int64_t splits, const c10::optional<at::Tensor>& addend = c10::nullopt, double beta = 0.0);
+
+// muon.cu
+void muon_prepass(const at::Tensor& grads, at::Tensor& buf, at::Tensor& work, at::Tensor& sumsq, const at::Tensor& mats, const at::Tensor& tiles,
+                  const c10::optional<at::Tensor>& grad_scale, double momentum, const c10::optional<at::Tensor>& err);
+void muon_normalize(at::Tensor& work, at::Tensor& sumsq, const at::Tensor& mats, const at::Tensor& tiles, double eps, const c10::optional<at::Tensor>& err);
+void muon_apply(at::Tensor& params, const c10::optional<at::Tensor>& shadow, const at::Tensor& work, const at::Tensor& mats, const at::Tensor& tiles,
+                const at::Tensor& scales, const c10::optional<at::Tensor>& hyper, double lr, double wd, const c10::optional<at::Tensor>& err);
+void muon_small_ns(const at::Tensor& src, at::Tensor& dst, int64_t rows, int64_t cols, int64_t steps, const c10::optional<at::Tensor>& err);
 
 // qsa_prep.cu
 std::vector<at::Tensor> qsa_headprep_fwd(const at::Tensor& src, const c10::optional<at::Tensor>& w, const at::Tensor& cosv, const at::Tensor& sinv, double eps,
@@ -56,7 +64,7 @@ at::Tensor gated_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& gate, const 
 std::vector<at::Tensor> gated_rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& gate, const at::Tensor& w, double eps);
 void adamw_flat(at::Tensor& p, const at::Tensor& g, at::Tensor& m, at::Tensor& v, c10::optional<at::Tensor> shadow,
                 c10::optional<at::Tensor> grad_scale, int64_t step, double lr, double wd, double beta1, double beta2, double eps,
-                c10::optional<at::Tensor> hyper);
+                c10::optional<at::Tensor> hyper, c10::optional<at::Tensor> err = c10::nullopt);
 at::Tensor sum_squares(const at::Tensor& x);
 
 // mhc.cu
@@ -121,9 +129,11 @@ at::Tensor p2p_get_handle(const at::Tensor& t);
 int64_t p2p_open_handle(const at::Tensor& handle, int64_t device);
 void p2p_close_handle(int64_t ptr, int64_t device);
 void p2p_barrier(at::Tensor& own_flags, std::vector<int64_t> peer_flags, int64_t rank, int64_t epoch, double wait_seconds, at::Tensor& err);
-void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start, int64_t count, double scale, int64_t device);
+void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start, int64_t count, double scale, int64_t device,
+                        const c10::optional<at::Tensor>& err);
 void p2p_all_gather(const at::Tensor& params, const c10::optional<at::Tensor>& shadow, std::vector<int64_t> peer_params, std::vector<int64_t> peer_shadow,
-                    int64_t rank, int64_t start, int64_t count);
+                    int64_t rank, int64_t start, int64_t count, const c10::optional<at::Tensor>& err);
+void cast_shadow_except(const at::Tensor& params, at::Tensor& shadow, int64_t skip_start, int64_t skip_count, const c10::optional<at::Tensor>& err);
 void p2p_publish_scalar(const at::Tensor& value, std::vector<int64_t> peer_slots, int64_t rank);
 // ce.cu
 at::Tensor ce_inplace(at::Tensor& logits, const at::Tensor& target);
