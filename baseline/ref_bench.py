@@ -112,7 +112,7 @@ def run(a):
             out.append((torch.from_numpy(x).pin_memory(), torch.from_numpy(y).pin_memory()))
         return out
 
-    pool = [host_batches() for _ in range(2)]
+    pool = [host_batches() for _ in range(a.warmup + 2 * a.steps)]          # a fresh batch for every step, as in the repository's arm
     device_pool = [[(x.to(dev), y.to(dev)) for x, y in batches] for batches in pool]
     lr = train["lr"]
     aux_coef, mtp_coef, kl_coef, clip = shape["aux_coef"], train["mtp_coef"], train["kl_coef"], train["clip"]
@@ -142,10 +142,13 @@ def run(a):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    cursor = [0]
+
     def run_steps(steps, batches_pool, read_back):
         last = None
-        for i in range(steps):
-            out = train_step(batches_pool[i % len(batches_pool)])
+        for _ in range(steps):
+            out = train_step(batches_pool[cursor[0] % len(batches_pool)])
+            cursor[0] += 1
             last = out.tolist() if read_back else out
         return last
 
@@ -183,7 +186,7 @@ def run(a):
             "metric": f"train tokens/sec, {a.preset} seq {a.seq}", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms_dev / a.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic packed stream (uniform ids, EOS at geometric(1024) boundaries), random-init weights",
+            "data": "synthetic packed stream (uniform ids, EOS at geometric(1024) boundaries; a fresh batch every step), random-init weights",
             "impl": "reference",
             "config": {"model": a.preset, "global_batch": batch_tokens // a.seq, "seq_len": a.seq, "micro_bs": micro_bs,
                        "accum": accum, "parallelism": f"dp{world}", "phase": a.phase, "grad_sync": "DDP all-reduce (NCCL)",

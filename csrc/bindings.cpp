@@ -91,7 +91,7 @@ TORCH_LIBRARY(q38, m) {
   m.def("gdn_scan_bwd(Tensor w, Tensor P, Tensor qg, Tensor kg, Tensor dch, Tensor vnew, Tensor states, Tensor dout, int B, int H) -> Tensor[]");
   m.def("moe_route_fwd(Tensor logits, int k) -> Tensor[]");
   m.def("moe_route_bwd(Tensor probs, Tensor top_idx, Tensor top_w, Tensor d_top_w, Tensor? d_prob_sum) -> Tensor");
-  m.def("moe_sort(Tensor top_idx, int E) -> Tensor[]");
+  m.def("moe_sort(Tensor top_idx, int E, Tensor? err=None) -> Tensor[]");
   m.def("moe_gather(Tensor x, Tensor perm, int k) -> Tensor");
   m.def("moe_combine_fwd(Tensor y_sorted, Tensor inv_perm, Tensor top_w) -> Tensor");
   m.def("moe_combine_bwd(Tensor dout, Tensor y_sorted, Tensor inv_perm, Tensor top_w) -> Tensor[]");
@@ -140,7 +140,7 @@ TORCH_LIBRARY_IMPL(q38, CUDA, m) {
   m.impl("moe_route_bwd", [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& c, const at::Tensor& d, c10::optional<at::Tensor> e) {
     return q38::moe_route_bwd(a, b, c, d, e);
   });
-  m.impl("moe_sort", &q38::moe_sort);
+  m.impl("moe_sort", [](const at::Tensor& idx, int64_t E, c10::optional<at::Tensor> err) { return q38::moe_sort(idx, E, err); });
   m.impl("moe_gather", &q38::moe_gather);
   m.impl("moe_combine_fwd", &q38::moe_combine_fwd);
   m.impl("moe_combine_bwd", &q38::moe_combine_bwd);

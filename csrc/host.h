@@ -83,7 +83,7 @@ at::Tensor mhc_pre_bwd_c(const at::Tensor& G, const at::Tensor& dXo, const at::T
 std::vector<at::Tensor> moe_route_fwd(const at::Tensor& logits, int64_t k);
 at::Tensor moe_route_bwd(const at::Tensor& probs, const at::Tensor& top_idx, const at::Tensor& top_w, const at::Tensor& d_top_w,
                          const c10::optional<at::Tensor>& d_prob_sum);
-std::vector<at::Tensor> moe_sort(const at::Tensor& top_idx, int64_t E);
+std::vector<at::Tensor> moe_sort(const at::Tensor& top_idx, int64_t E, const c10::optional<at::Tensor>& err = c10::nullopt);
 at::Tensor moe_gather(const at::Tensor& x, const at::Tensor& perm, int64_t k);
 at::Tensor moe_combine_fwd(const at::Tensor& y_sorted, const at::Tensor& inv_perm, const at::Tensor& top_w);
 std::vector<at::Tensor> moe_combine_bwd(const at::Tensor& dout, const at::Tensor& y_sorted, const at::Tensor& inv_perm, const at::Tensor& top_w);

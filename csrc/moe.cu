@@ -114,13 +114,20 @@ __global__ void __launch_bounds__(256) moe_route_bwd_kernel(const float* __restr
 // =====================================================================================================================
 constexpr int SORT_THREADS = 256, SORT_ITERS = 4, SORT_CHUNK = SORT_THREADS * SORT_ITERS;
 
-__global__ void __launch_bounds__(SORT_THREADS) moe_hist_kernel(const int* __restrict__ expert_of_pair, int P, int E, int* __restrict__ block_counts) {
+// A pair whose expert id lies outside [0, E) is skipped by the histogram and the scatter (it is counted nowhere, its
+// inv_perm entry becomes -1 and the tail of perm stays unwritten) and ERR_BOUNDS is recorded when an error word is given.
+__global__ void __launch_bounds__(SORT_THREADS) moe_hist_kernel(const int* __restrict__ expert_of_pair, int P, int E, int* __restrict__ block_counts,
+                                                                int* __restrict__ err) {
   __shared__ int cnt[64];
   if (threadIdx.x < 64) cnt[threadIdx.x] = 0;
   __syncthreads();
   for (int it = 0; it < SORT_ITERS; ++it) {
     const int i = blockIdx.x * SORT_CHUNK + it * SORT_THREADS + threadIdx.x;
-    if (i < P) atomicAdd(&cnt[expert_of_pair[i]], 1);
+    if (i < P) {
+      const int e = expert_of_pair[i];
+      if ((unsigned)e < (unsigned)E) atomicAdd(&cnt[e], 1);
+      else report_error(err, ERR_BOUNDS);
+    }
   }
   __syncthreads();
   if (threadIdx.x < E) block_counts[blockIdx.x * E + threadIdx.x] = cnt[threadIdx.x];
@@ -173,8 +180,12 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_scatter_kernel(const int* __
     for (int i = threadIdx.x; i < (SORT_THREADS / 32) * 64; i += SORT_THREADS) (&warp_cnt[0][0])[i] = 0;
     __syncthreads();
     const int i = blockIdx.x * SORT_CHUNK + it * SORT_THREADS + threadIdx.x;
-    const bool valid = i < P;
-    const int e = valid ? expert_of_pair[i] : -1;
+    int e = i < P ? expert_of_pair[i] : -1;
+    const bool valid = (unsigned)e < (unsigned)E;
+    if (!valid) {
+      if (i < P) inv_perm[i] = -1;
+      e = -1;
+    }
     const unsigned same = __match_any_sync(0xffffffffu, e);
     const int rank = __popc(same & ((1u << lane) - 1));
     if (valid && rank == 0) warp_cnt[warp][e] = __popc(same);
@@ -687,7 +698,7 @@ at::Tensor moe_route_bwd(const at::Tensor& probs, const at::Tensor& top_idx, con
 }
 
 // top_idx [T,k] int32 -> {perm [P], inv_perm [P], offsets [E+1], sched [1 + 3 * max_tiles]}
-std::vector<at::Tensor> moe_sort(const at::Tensor& top_idx, int64_t E) {
+std::vector<at::Tensor> moe_sort(const at::Tensor& top_idx, int64_t E, const c10::optional<at::Tensor>& err) {
   TORCH_CHECK(top_idx.is_cuda() && top_idx.scalar_type() == at::kInt && top_idx.is_contiguous() && E <= 64, "moe_sort: int32 [T,k], at most 64 experts");
   const c10::cuda::CUDAGuard guard(top_idx.device());
   const int P = top_idx.numel();
@@ -697,7 +708,8 @@ std::vector<at::Tensor> moe_sort(const at::Tensor& top_idx, int64_t E) {
   auto block_counts = at::empty({std::max(nblocks, 1) * (int)E}, i32), perm = at::empty({P}, i32), inv = at::empty({P}, i32);
   auto offsets = at::empty({(int)E + 1}, i32), sched = at::empty({1 + 3 * max_tiles}, i32);
   auto stream = at::cuda::getCurrentCUDAStream();
-  if (nblocks) moe_hist_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(top_idx.data_ptr<int>(), P, (int)E, block_counts.data_ptr<int>());
+  if (nblocks) moe_hist_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(top_idx.data_ptr<int>(), P, (int)E, block_counts.data_ptr<int>(),
+                                                                     err.has_value() ? err->data_ptr<int>() : nullptr);
   moe_scan_kernel<<<1, 64, 0, stream>>>(block_counts.data_ptr<int>(), nblocks, (int)E, offsets.data_ptr<int>(), sched.data_ptr<int>(), max_tiles, G_BM);
   if (nblocks) moe_scatter_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(top_idx.data_ptr<int>(), P, (int)E, block_counts.data_ptr<int>(), perm.data_ptr<int>(), inv.data_ptr<int>());
   C10_CUDA_KERNEL_LAUNCH_CHECK();
@@ -789,7 +801,7 @@ extern "C" int q38_moe_sort_static(const int* expert_of_pair, int P, int experts
   int* scratch = sort_static_scratch_for_current_device();
   if (scratch == nullptr) return Q38_NOALLOC_CUDA_ERROR;
   // Every word of the scratch that the scan and scatter kernels read is written by the histogram kernel first.
-  moe_hist_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(expert_of_pair, P, experts, scratch);
+  moe_hist_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(expert_of_pair, P, experts, scratch, nullptr);
   moe_scan_kernel<<<1, 64, 0, stream>>>(scratch, nblocks, experts, offsets, sched, max_tiles, G_BM);
   moe_scatter_kernel<<<nblocks, SORT_THREADS, 0, stream>>>(expert_of_pair, P, experts, scratch, perm, inv_perm);
   if (cudaGetLastError() != cudaSuccess) return Q38_NOALLOC_CUDA_ERROR;

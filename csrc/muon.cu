@@ -48,8 +48,10 @@ __global__ void __launch_bounds__(MUON_THREADS) muon_prepass_kernel(const float*
   float* b = buf + off + first;
   __nv_bfloat16* w = work + woff + first;
   float acc = 0.f;
-  // offsets and tile starts are multiples of 4 elements (arena units are 64-element aligned), so 16-byte accesses are aligned
-  const int n4 = count >> 2;
+  // 16-byte accesses when this tile starts on a 4-element boundary in both buffers (arena units are 64-element aligned and tiles
+  // are 4096 long, so only stacks of matrices whose size is not a multiple of 4 take the scalar path)
+  const bool vec = (((off + first) | (woff + first)) & 3) == 0;
+  const int n4 = vec ? (count >> 2) : 0;
   for (int i = threadIdx.x; i < n4; i += MUON_THREADS) {
     float4 gv = reinterpret_cast<const float4*>(g)[i];
     float4 bv = reinterpret_cast<float4*>(b)[i];

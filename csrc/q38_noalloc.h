@@ -43,7 +43,10 @@ enum {
 extern "C" {
 #endif
 
-// expert_of_pair [P] int32 (device): expert chosen for pair p = token * k + slot.
+// expert_of_pair [P] int32 (device): expert chosen for pair p = token * k + slot.  Precondition: 0 <= id < experts for every
+// pair.  A pair that violates it (for instance a -1 "dropped token" marker) is skipped, not sorted: it is counted in no
+// expert's range, its inv_perm entry is set to -1, and as many entries at the end of perm as there are such pairs are left
+// unwritten.  No out-of-range memory is touched.
 // perm [P], inv_perm [P], offsets [experts + 1], sched [1 + 3 * max_tiles] int32 (device), caller-owned.
 // max_tiles must be at least ceil(P / 128) + experts.
 int q38_moe_sort_static(const int* expert_of_pair, int P, int experts, int* perm, int* inv_perm, int* offsets, int* sched,

@@ -69,8 +69,9 @@ def install(self_check=True):
 
 
 # ---- thin wrappers used outside the model ------------------------------------------------------------------
-def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumulate=False, out_dtype=torch.bfloat16, splits=-1):
-    """``out[b] (+)= alpha * A[b] @ B[b]^T`` on the tcgen05 tensor cores.
+def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumulate=False, out_dtype=torch.bfloat16, splits=-1,
+         addend=None, beta=0.0):
+    """``out[b] (+)= alpha * A[b] @ B[b]^T (+ beta * addend[b])`` on the tcgen05 tensor cores.
 
     a: ``[batch, M, K]`` (K-major) or ``[batch, K, M]`` (``a_mn_major``); b likewise with N.  2-D inputs are treated as batch 1.
     ``splits`` (only with ``accumulate`` into fp32): -1 no split-K, 0 automatic, n > 0 that many K slices whose partial
@@ -86,8 +87,12 @@ def gemm(a, b, out=None, a_mn_major=False, b_mn_major=False, alpha=1.0, accumula
     else:
         out3 = out.unsqueeze(0) if out.dim() == 2 else out
     if PERSISTENT_GEMM:
-        ops.gemm_bf16_persistent(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
+        if addend is not None and addend.dim() == 2:
+            addend = addend.unsqueeze(0)
+        ops.gemm_bf16_persistent(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits), addend, float(beta))
     else:
+        if addend is not None:
+            raise ValueError("the addend epilogue exists in the persistent kernel only")
         ops.gemm_bf16(a, b, out3, a_mn_major, b_mn_major, float(alpha), bool(accumulate), error_flag(a.device), int(splits))
     return out3[0] if squeeze else out3
 
@@ -96,12 +101,12 @@ def sum_squares(x):
     return load().sum_squares(x)
 
 
-def adamw_flat(p, g, m, v, step, lr, wd, beta1, beta2, eps, grad_scale=None, shadow=None, hyper=None):
+def adamw_flat(p, g, m, v, step, lr, wd, beta1, beta2, eps, grad_scale=None, shadow=None, hyper=None, err=None):
     """`hyper`: optional CUDA fp32 tensor {lr, 1/(1-b1^t), 1/sqrt(1-b2^t)} that overrides the step-dependent scalars, so that a
-    captured launch can be replayed with new values."""
+    captured launch can be replayed with new values.  `err`: device error word; when it is non-zero the kernel writes nothing."""
     if grad_scale is not None:
         grad_scale = grad_scale.reshape(1).float()
-    load().adamw_flat(p, g, m, v, shadow, grad_scale, int(step), float(lr), float(wd), float(beta1), float(beta2), float(eps), hyper)
+    load().adamw_flat(p, g, m, v, shadow, grad_scale, int(step), float(lr), float(wd), float(beta1), float(beta2), float(eps), hyper, err)
 
 
 def muon_batched_step(views, per_call, lr, momentum, weight_decay, ns_steps, scale, grad_scale=None):

@@ -4,6 +4,7 @@ Each method is a `torch.autograd.Function` (or a composition of them) over the C
 A method that is absent makes the model use its PyTorch specification for that op; the set of present
 methods is reported by `describe()` so a run records exactly which paths were native.
 """
+import collections
 import os
 
 import torch
@@ -125,6 +126,17 @@ class _SideStream:
 WGRAD_STREAM = _SideStream()
 
 
+# Every product that leaves the hand-written GEMM for a library matmul is counted here by call site (shapes the tensor-core
+# kernel does not take: a reduction dimension that is not a multiple of 8, a layout that failed its start-up self-check, the
+# Q38_MHC_FP32_GEMM switch).  `Backend.describe()` reports the counter, and the benchmark prints it: empty means every product
+# of the run went through the sm_100a kernels.
+LIBRARY_FALLBACKS = collections.Counter()
+
+
+def _fallback(site):
+    LIBRARY_FALLBACKS[site] += 1
+
+
 def _tma_rows(t):
     """A 2-D tensor whose row stride TMA accepts (a multiple of 16 bytes).  A narrow matrix, e.g. the [tokens, 21] gradient of a
     per-head gate projection, is copied into a buffer with padded rows and returned as a view of it; the tensor map still
@@ -146,14 +158,17 @@ def _mm32(a, b, layout, out_dtype=torch.float32):
     tokens) runs on bf16 copies with MN-major operands and fp32 accumulation."""
     a, b = a.float().contiguous(), b.float().contiguous()
     if os.environ.get("Q38_MHC_FP32_GEMM"):
+        _fallback("mhc_fp32_switch")
         return a @ b.t() if layout == "nt" else (a @ b if layout == "nn" else a.t() @ b)
     if layout == "tn":
         if a.shape[1] % 8 or b.shape[1] % 8:
+            _fallback("mhc_tn_unaligned")
             return a.t() @ b
         return gemm(a.to(torch.bfloat16), b.to(torch.bfloat16), a_mn_major=True, b_mn_major=True, out_dtype=torch.float32)
     if layout == "nn":
         b = b.t().contiguous()
     if a.shape[1] % 4 or a.data_ptr() % 16 or b.data_ptr() % 16:
+        _fallback("mhc_tf32_unaligned")
         return (a @ b.t()).to(out_dtype)
     return gemm(a, b, out_dtype=out_dtype)
 
@@ -604,18 +619,21 @@ class Backend:
     def mm_nt(self, a, b, out_dtype=torch.bfloat16):
         """a[M,K] @ b[N,K]^T"""
         if a.shape[1] % 8 or not self.layouts["nt"]:
+            _fallback("mm_nt")
             return (a @ b.t()).to(out_dtype)
         return gemm(a, b, out_dtype=out_dtype)
 
     def mm_nn(self, a, b, out_dtype=torch.bfloat16):
         """a[M,K] @ b[K,N]"""
         if b.shape[1] % 8 or not self.layouts["nn"]:
+            _fallback("mm_nn")
             return (a @ b).to(out_dtype)
         return gemm(_tma_rows(a), b, b_mn_major=True, out_dtype=out_dtype)
 
     def mm_tn(self, a, b, out_dtype=torch.float32):
         """a[K,M]^T @ b[K,N]   (weight gradients: reduction over the token dimension)"""
         if not self.layouts["tn"]:
+            _fallback("mm_tn")
             return (a.t() @ b).to(out_dtype)
         return gemm(_tma_rows(a), _tma_rows(b), a_mn_major=True, b_mn_major=True, out_dtype=out_dtype)
 
@@ -797,7 +815,9 @@ class Backend:
         top_w, top_idx, prob_sum, counts = _Route.apply(logits, block.gate.top_k)
         if block._recording():
             block.stats_sink.add(counts, prob_sum, x2.shape[0])
-        if self.ep is not None:
+        # Expert parallelism is the training path.  Without gradients (validation, export checks) the replicated path runs on
+        # the full expert tensors, which the engine assembles from the ranks' slices first (`GradEngine.gather_experts`).
+        if self.ep is not None and torch.is_grad_enabled():
             from ..parallel.ep import _ExpertsEP
             routed = _ExpertsEP.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj, self.ep, self.ep.layer_index(block))
         else:
@@ -818,7 +838,7 @@ class Backend:
     def describe(self):
         native = sorted(n for n in ("linear", "rmsnorm", "gated_rmsnorm", "mhc_pre_norm", "mhc_post", "gated_deltanet",
                                     "qsa_attention", "moe_block", "ngram_delta", "embedding", "linear_cross_entropy") if hasattr(self, n))
-        return dict(native=native, gemm_layouts=self.layouts)
+        return dict(native=native, gemm_layouts=self.layouts, library_matmul_fallbacks=dict(LIBRARY_FALLBACKS))
 
 
 class _LinearCE(torch.autograd.Function):

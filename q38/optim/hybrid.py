@@ -42,11 +42,13 @@ def split_parameters(model, muon=True):
     return matrices, decay, no_decay
 
 
-def adamw_flat_(p, g, m, v, step, lr, wd, grad_scale=None, betas=ADAM_BETAS, eps=ADAM_EPS, hyper=None):
-    """In-place AdamW on flat fp32 tensors with torch.optim.AdamW's arithmetic (decoupled decay first)."""
+def adamw_flat_(p, g, m, v, step, lr, wd, grad_scale=None, betas=ADAM_BETAS, eps=ADAM_EPS, hyper=None, shadow=None, err=None):
+    """In-place AdamW on flat fp32 tensors with torch.optim.AdamW's arithmetic (decoupled decay first).  On a GPU `shadow`
+    (bf16, same length) receives the rounded parameters and `err` is the device error word: when it is set the kernel
+    returns without writing."""
     if p.is_cuda:
         from ..ops import adamw_flat
-        return adamw_flat(p, g, m, v, step, lr, wd, betas[0], betas[1], eps, grad_scale, hyper=hyper)
+        return adamw_flat(p, g, m, v, step, lr, wd, betas[0], betas[1], eps, grad_scale, shadow=shadow, hyper=hyper, err=err)
     if grad_scale is not None:
         g = g * grad_scale
     b1, b2 = betas
@@ -64,6 +66,7 @@ class HybridOptimizer:
         self.names = dict(muon=[n for n, _ in matrices], decay=[n for n, _ in decay], no_decay=[n for n, _ in no_decay])
         self.arena, self.rank, self.steps_done = arena, rank, 0
         self._graph, self._warmed, self._hyper = None, False, None
+        self._fused_muon = None
         on_gpu = next(model.parameters()).is_cuda
         fused = (on_gpu if fused_adam is None else fused_adam) and arena is None
         self.adam = torch.optim.AdamW(
@@ -116,21 +119,51 @@ class HybridOptimizer:
 
     def _arena_step(self, grad_scale, hyper, lr_tensor):
         """AdamW over this rank's flat ranges, then Muon over the matrices it owns.  With `hyper` / `lr_tensor` the learning
-        rate and the bias corrections are read from device memory."""
+        rate and the bias corrections are read from device memory.  On a GPU both write the bf16 shadow of what they update
+        and both leave everything untouched when the device error word is set."""
         a = self.arena
+        on_gpu = a.device.type == "cuda"
+        err = None
+        if on_gpu:
+            from .. import ops
+            err = ops.error_flag(a.device)
         for group_name, group in zip(("decay", "no_decay"), self.adam.param_groups):
             s, e = a.group_ranges[(self.rank, group_name)]
             if e > s:
                 adamw_flat_(a.params[s:e], a.grads[s:e], a.exp_avg[s:e], a.exp_avg_sq[s:e], self.steps_done,
-                            group["lr"], group["weight_decay"], grad_scale, hyper=hyper)
-        if self.muon:
-            owned = [u.param for u in a.owned(self.rank, "muon")]
-            slices = {}
-            for unit in a.local_units():                     # expert-parallel tensors: this rank updates its own experts only
-                owned.append(unit.param)
+                            group["lr"], group["weight_decay"], grad_scale, hyper=hyper,
+                            shadow=a.shadow[s:e] if (on_gpu and a.shadow is not None) else None, err=err)
+        if not self.muon:
+            return
+        if on_gpu and not os.environ.get("Q38_MUON_BASELINE"):
+            group = self.muon.param_groups[0]
+            self._muon_plan().step(group["lr"], group["momentum"], group["weight_decay"], grad_scale=grad_scale, hyper=hyper, err=err)
+            return
+        owned = [u.param for u in a.owned(self.rank, "muon")]
+        slices = {}
+        for unit in a.local_units():                     # expert-parallel tensors: this rank updates its own experts only
+            owned.append(unit.param)
+            n = unit.param.shape[0] // a.world
+            slices[id(unit.param)] = slice(self.rank * n, (self.rank + 1) * n)
+        self.muon.step(params=owned, grad_scale=grad_scale, slices=slices, lr_tensor=lr_tensor)
+
+    def _muon_plan(self):
+        """Device tables of the matrices this rank updates (built once; the arena layout never changes)."""
+        if self._fused_muon is None:
+            from ..ops.muon_gpu import FusedMuon
+            a = self.arena
+            entries = []
+            for unit in a.owned(self.rank, "muon"):
+                rows, cols = unit.param.shape[-2:]
+                entries.append((unit.offset, unit.numel // (rows * cols), rows, cols))
+            for unit in a.local_units():
+                rows, cols = unit.param.shape[-2:]
                 n = unit.param.shape[0] // a.world
-                slices[id(unit.param)] = slice(self.rank * n, (self.rank + 1) * n)
-            self.muon.step(params=owned, grad_scale=grad_scale, slices=slices, lr_tensor=lr_tensor)
+                per = unit.numel // unit.param.shape[0]
+                entries.append((unit.offset + self.rank * n * per, n * per // (rows * cols), rows, cols))
+            group = self.muon.param_groups[0]
+            self._fused_muon = FusedMuon(a.params, a.grads, a.muon_buf, a.shadow, entries, rms_scale=group["rms_scale"], ns_steps=group["ns_steps"])
+        return self._fused_muon
 
     def _replayed_step(self, grad_scale):
         """The optimizer step as one CUDA graph.  Hundreds of small launches (Newton-Schulz chains per matrix shape) otherwise
@@ -139,13 +172,18 @@ class HybridOptimizer:
         dev = self.arena.device
         if self._hyper is None:
             self._hyper = torch.zeros(4, dtype=torch.float32, device=dev)
-            self._hyper_host = torch.zeros(4, dtype=torch.float32).pin_memory()
+            # A ring of pinned staging buffers: the host may run several steps ahead of the GPU, so a buffer is only
+            # rewritten after the copy that last read it has completed.
+            self._hyper_ring = [(torch.zeros(4, dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(4)]
             self._scale = torch.ones((), dtype=torch.float32, device=dev)
         lr = self.param_groups[0]["lr"]
         b1, b2 = ADAM_BETAS
         t = self.steps_done
-        self._hyper_host[0], self._hyper_host[1], self._hyper_host[2] = lr, 1.0 / (1.0 - b1 ** t), 1.0 / math.sqrt(1.0 - b2 ** t)
-        self._hyper.copy_(self._hyper_host, non_blocking=True)
+        host, copied = self._hyper_ring[t % len(self._hyper_ring)]
+        copied.synchronize()
+        host[0], host[1], host[2] = lr, 1.0 / (1.0 - b1 ** t), 1.0 / math.sqrt(1.0 - b2 ** t)
+        self._hyper.copy_(host, non_blocking=True)
+        copied.record()
         if grad_scale is None:
             self._scale.fill_(1.0)
         else:

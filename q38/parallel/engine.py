@@ -16,7 +16,8 @@ clip -> AdamW -> Muon at q38/train.py:558-559).
 
 Transports
   ``p2p``         hand-written sm_100a kernels reading/writing peer GPUs' arenas over NVLink
-                  (`q38.parallel.p2p`); launched on a side stream so they overlap the tail of backward.
+                  (`q38.parallel.p2p`), launched on the compute stream after the last micro-step.  Only fp32 parameters
+                  cross NVLink in the all-gather; every rank derives the bf16 shadow of the received segments locally.
   ``collective``  `torch.distributed` reduce / broadcast per segment (NCCL on GPUs, gloo on CPU).  This is the
                   baseline transport and the one the CPU multi-process tests exercise.
 """
@@ -54,8 +55,9 @@ class GradEngine:
         if self.transport is not None:
             self.transport.bind(self.arena)
         self._last = True
+        # CUDA events around the phases of `finish_step` (a handful per step; Q38_ENGINE_TIMING=0 turns them off)
         import os
-        self._timing = [] if (os.environ.get("Q38_ENGINE_TIMING") == "1" and self.device.type == "cuda") else None
+        self._timing = [] if (os.environ.get("Q38_ENGINE_TIMING", "1") != "0" and self.device.type == "cuda") else None
 
     # ------------------------------------------------------------------ step protocol
     def set_lr(self, lr):
@@ -80,18 +82,38 @@ class GradEngine:
         s, e = self.arena.segments[self.rank]
         self.arena.grads[s:e].div_(self.world)
 
+    def _fused_updates(self):
+        """True when the update kernels write the bf16 shadow of what they update (GPU, fused optimizer kernels)."""
+        import os
+        return self.device.type == "cuda" and not os.environ.get("Q38_MUON_BASELINE")
+
     def _all_gather(self):
+        fused = self._fused_updates()
         if self.world == 1:
-            self.arena.refresh_shadow()
+            if not fused:
+                self.arena.refresh_shadow()
             return
+        s, e = self.arena.segments[self.rank]
         if self.transport is not None:
-            self.arena.refresh_shadow(self.rank)
+            if not fused:
+                self.arena.refresh_shadow(self.rank)
             self.transport.all_gather_params()
+            self._cast_received(s, e)
             return
-        for owner, (s, e) in enumerate(self.arena.segments):
-            if e > s:
-                dist.broadcast(self.arena.params[s:e], src=owner)
-        self.arena.refresh_shadow()
+        for owner, (s0, e0) in enumerate(self.arena.segments):
+            if e0 > s0:
+                dist.broadcast(self.arena.params[s0:e0], src=owner)
+        if fused:
+            self._cast_received(s, e)
+        else:
+            self.arena.refresh_shadow()
+
+    def _cast_received(self, s, e):
+        """bf16 shadow of every segment except this rank's own (already written by the update kernels)."""
+        from .. import ops
+        local = self.arena.local_range
+        end = local[0] if local[1] > local[0] else self.arena.numel
+        ops.load().cast_shadow_except(self.arena.params[:end], self.arena.shadow[:end], s, e - s, ops.error_flag(self.device))
 
     def _local_grad_slices(self):
         """This rank's slices of the expert-parallel gradient tensors."""
@@ -147,8 +169,8 @@ class GradEngine:
         self._timing.append((name, event))
 
     def phase_times(self):
-        """Median milliseconds per phase of `finish_step` over the steps recorded so far (Q38_ENGINE_TIMING=1); the median
-        ignores the first steps, whose device timeline contains host-side lazy initialisation and graph capture."""
+        """Median milliseconds per phase of `finish_step` over the steps recorded so far; the median ignores the first
+        steps, whose device timeline contains host-side lazy initialisation and graph capture."""
         if not self._timing:
             return {}
         torch.cuda.synchronize(self.device)
@@ -156,7 +178,26 @@ class GradEngine:
         for (_, e0), (name, e1) in zip(self._timing, self._timing[1:]):
             if name != "start":
                 samples.setdefault(name, []).append(e0.elapsed_time(e1))
+        self._timing = self._timing[-64:]
         return {k: round(sorted(v)[len(v) // 2], 3) for k, v in samples.items()}
+
+    def comm_report(self, link_gbs=770.0):
+        """Exposed communication of a step and how close it runs to the NVLink roofline.
+
+        Nothing of `finish_step` overlaps with compute, so the exposed communication time is the sum of the reduce-scatter
+        and all-gather phases (barriers included).  Bytes over NVLink per rank: the reduce-scatter reads this rank's segment
+        from every peer, the all-gather writes it to every peer, both in fp32.  `link_gbs` is the measured peer-copy
+        bandwidth per direction."""
+        times = self.phase_times()
+        if self.world == 1 or not times:
+            return {"exposed_comm_ms": 0.0, "comm_roofline_fraction": None}
+        s, e = self.arena.segments[self.rank]
+        one_way = (self.world - 1) * (e - s) * 4
+        rs, ag = times.get("reduce_scatter", 0.0), times.get("all_gather", 0.0)
+        frac = lambda ms: round(one_way / (link_gbs * 1e9 * ms * 1e-3), 3) if ms > 0 else None
+        return {"exposed_comm_ms": round(rs + ag, 3), "nvlink_bytes_per_phase": one_way, "reduce_scatter_roofline_fraction": frac(rs),
+                "all_gather_roofline_fraction": frac(ag), "comm_roofline_fraction": frac((rs + ag) / 2) if rs + ag > 0 else None,
+                "link_gbs_per_direction_measured": link_gbs}
 
     def average_metrics(self, values):
         """Mean over ranks of the loss terms; the last entry (gradient norm) is already global."""
@@ -186,6 +227,19 @@ class GradEngine:
             if self.arena.local_units():
                 self.arena.refresh_shadow()
         return self.model.state_dict(), self.optimizer.state_dict()
+
+    def gather_experts(self):
+        """Expert parallelism: make every rank's copy of the expert tensors complete (each rank trains only its slice), so that
+        code that runs the replicated expert path (evaluation under `no_grad`, export) sees the whole model.  Collective."""
+        units = self.arena.local_units()
+        if self.world == 1 or not units:
+            return
+        for unit in units:
+            n = unit.param.shape[0] // self.world
+            full = self.arena.view(self.arena.params, unit)
+            for owner in range(self.world):
+                dist.broadcast(full[owner * n:(owner + 1) * n], src=owner)
+        self.arena.refresh_shadow()
 
     def load_checkpoint(self, model_state, opt_state):
         self.model.load_state_dict(model_state)

@@ -9,10 +9,13 @@ flag barriers; NCCL is only used for the bootstrap and for the few-byte metric a
     reduce_scatter_mean           rank r: grads_r[seg r] = mean_p grads_p[seg r]          (peer loads, scale fused)
     allreduce_sum_scalar          squared gradient norm: publish to peers, barrier, sum in rank order
     (owner-computes optimizer step on segment r)
-    all_gather_params + barrier   rank r stores params/shadow[seg r] into every peer      (peer stores)
+    all_gather_params + barrier   rank r stores its fp32 params[seg r] into every peer    (peer stores)
 
 Waits inside the barrier kernel are bounded (`wait_seconds`); a missing peer surfaces as a `RuntimeError` from
-`q38.ops.check_errors()` instead of a hang.
+`q38.ops.check_errors()` instead of a hang.  The rank whose wait ran out also raises an abort word in every peer's flag
+array, and every kernel of the step that writes parameters, optimizer state or peer memory returns without writing once
+the error word is set: a late rank cannot push parameters into a rank that has given up, and nobody steps on gradients
+that were never reduced.
 """
 import torch
 import torch.distributed as dist
@@ -24,7 +27,8 @@ class PeerTransport:
     def __init__(self, device, rank, world, wait_seconds=20.0):
         self.device, self.rank, self.world = torch.device(device), rank, world
         self.ops = ops.load()
-        self.wait_seconds = wait_seconds
+        import os
+        self.wait_seconds = float(os.environ.get("Q38_PEER_WAIT_SECONDS", wait_seconds))
         self.local = {}          # name -> uint8 tensor owning the allocation
         self.peers = {}          # name -> list of device pointers (own pointer at index rank)
         self.epoch = 0
@@ -82,7 +86,7 @@ class PeerTransport:
     def reduce_scatter_mean(self):
         self.barrier()
         s, e = self.arena.segments[self.rank]
-        self.ops.p2p_reduce_scatter(self.peers["grads"], self.rank, s, e - s, 1.0 / self.world, self.device.index)
+        self.ops.p2p_reduce_scatter(self.peers["grads"], self.rank, s, e - s, 1.0 / self.world, self.device.index, ops.error_flag(self.device))
 
     def allreduce_sum_scalar(self, value):
         """`value`: 0-dim float64 device tensor.  Returns the sum over ranks, added in rank order on every rank."""
@@ -92,8 +96,13 @@ class PeerTransport:
 
     def all_gather_params(self):
         s, e = self.arena.segments[self.rank]
-        self.ops.p2p_all_gather(self.arena.params, self.arena.shadow, self.peers["params"], self.peers.get("shadow", []), self.rank, s, e - s)
+        # fp32 only: the receivers derive the bf16 shadow themselves, a third fewer bytes over NVLink
+        self.ops.p2p_all_gather(self.arena.params, None, self.peers["params"], [], self.rank, s, e - s, ops.error_flag(self.device))
         self.barrier()
+
+    def reset_abort(self):
+        """Clear the abort word after the host has handled a failed barrier (all ranks, between steps)."""
+        self.flags[17] = 0
 
     def close(self):
         if not self.peers:

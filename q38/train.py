@@ -23,6 +23,7 @@ parameters it owns and the updated parameters are all-gathered by peer stores (`
 ``--grad_sync collective`` selects the library path (NCCL or gloo all-reduce), which is also what CPU runs use.
 """
 import argparse
+import contextlib
 import csv
 import gc
 import hashlib
@@ -259,16 +260,14 @@ def evaluate(model, eval_data, seq, dev, sampling="random", distributed=False):
     if sampling == "sequential":
         windows = sequential_windows(len(eval_data), seq)
     else:
-        windows = [(None, seq)] * (len(eval_data) // seq)
+        # every rank draws the whole list, so a distributed evaluation scores exactly the windows a single rank would
+        windows = [(int(rng.integers(0, len(eval_data) - seq - 1, 1)[0]), seq) for _ in range(len(eval_data) // seq)]
     rank, world = (dist.get_rank(), dist.get_world_size()) if distributed else (0, 1)
     total, scored = 0.0, 0
     try:
         for start, size in windows[rank::world]:
-            if start is None:
-                x, y = sample_batch(rng, eval_data, 1, size, dev)
-            else:
-                x = torch.from_numpy(np.asarray(eval_data[start:start + size], dtype=np.int64)[None].copy()).to(dev)
-                y = torch.from_numpy(np.asarray(eval_data[start + 1:start + size + 1], dtype=np.int64)[None].copy()).to(dev)
+            x = torch.from_numpy(np.asarray(eval_data[start:start + size], dtype=np.int64)[None].copy()).to(dev)
+            y = torch.from_numpy(np.asarray(eval_data[start + 1:start + size + 1], dtype=np.int64)[None].copy()).to(dev)
             logits = model(input_ids=x, use_cache=False).logits
             flat, target = logits.view(-1, logits.size(-1)), y.view(-1)
             rows = max(256, (8192 * 32768) // logits.size(-1))
@@ -429,6 +428,21 @@ class Trainer:
         grad_norm = self.engine.finish_step(self.a.clip)
         return self.engine.average_metrics(torch.cat([totals, grad_norm.detach().reshape(1).float()]))
 
+    def read_step(self, result):
+        """Host values ``[ce, aux, mtp, kl, grad_norm]`` of a step.  The device error word rides along in the same transfer:
+        when a kernel reported a problem during the step (a peer that missed a barrier, a bounded wait that ran out) this
+        raises `RuntimeError`; the update kernels have then left parameters and optimizer state untouched."""
+        if self.dev.type != "cuda":
+            return result.tolist()
+        from . import ops
+        flag = ops.error_flag(self.dev)
+        values = torch.cat([result.float(), flag.float()]).tolist()
+        code = int(values[-1])
+        if code:
+            flag.zero_()
+            raise RuntimeError(f"q38 kernel error {code}: {ops.ERROR_NAMES.get(code, 'unknown')}; the step was not applied")
+        return values[:-1]
+
 
 def probe_micro_bs(trainer, train_data, a, log0):
     """Largest micro batch (a divisor of the per-rank sequences, at most ``--micro_bs``) whose
@@ -480,6 +494,19 @@ def probe_micro_bs(trainer, train_data, a, log0):
     if not chosen:
         raise RuntimeError("micro_bs=1 does not fit in GPU memory")
     return chosen, trials
+
+
+def write_checkpoint(state, path):
+    """Atomic checkpoint write: serialise to ``<path>.tmp``, then rename.  A crash or a failed write leaves the previous
+    checkpoint in place; a leftover ``.tmp`` file is never read by a resume."""
+    tmp = f"{path}.tmp"
+    try:
+        torch.save(state, tmp)
+    except BaseException:
+        with contextlib.suppress(OSError):
+            os.remove(tmp)
+        raise
+    os.replace(tmp, path)
 
 
 def export_hf(model, tokenizer, out_dir):
@@ -632,9 +659,12 @@ def main(argv=None):
             states[0] = state
         model_state, opt_state = trainer.engine.checkpoint_state()      # collective: owners publish their optimizer shards
         if rank == 0:
-            torch.save({"model": model_state, "opt": opt_state, "step": step, "tok_seen": tok_seen,
-                        "rng": rng.bit_generator.state, "rank_rng": states, "world": world}, ckpt_path + ".tmp")
-            os.replace(ckpt_path + ".tmp", ckpt_path)
+            write_checkpoint({"model": model_state, "opt": opt_state, "step": step, "tok_seen": tok_seen,
+                              "rng": rng.bit_generator.state, "rank_rng": states, "world": world}, ckpt_path)
+        if ddp:
+            # Serialising tens of GB takes longer than the bounded waits of the peer-memory barriers: nobody starts the next
+            # step (and pushes parameters into rank 0's arena) before the file is complete.
+            dist.barrier()
 
     log0(f"steps {steps} accum {accum} micro_bs {a.micro_bs} warmup {a.warmup} lr {a.lr}")
     pinned = dev.type == "cuda"
@@ -645,18 +675,24 @@ def main(argv=None):
             batches.append(host_batch(rng, train_data, a.micro_bs, a.seq, offsets, pinned=pinned))
         result = trainer.train_step(batches, lr=lr_at(step), dense=bool(a.dense_warmup and step < a.warmup))
         tok_seen += accum * per_micro
-        loss_acc, aux_acc, mtp_acc, kl_acc, gn = result.tolist()        # the only host sync of the step
+        loss_acc, aux_acc, mtp_acc, kl_acc, gn = trainer.read_step(result)   # the only host sync of the step; raises on a device error
         if tb:
             for name, value in (("loss", loss_acc), ("aux", aux_acc), ("mtp_loss", mtp_acc), ("indexer_kl", kl_acc),
                                 ("lr", lr_at(step)), ("grad_norm", gn), ("tokens", tok_seen)):
                 tb.add_scalar(f"train/{name}", value, step)
         if a.ckpt_every and step > 0 and step % a.ckpt_every == 0:
             save_ckpt(step)
-        if (step % a.log_every == 0 or step == stop_step - 1) and rank == 0:
+        logging_step = step % a.log_every == 0 or step == stop_step - 1
+        due = logging_step and ((step % a.eval_every == 0 and step > 0) or step == stop_step - 1)
+        vl = ""
+        if due:
+            # Every rank takes part (disjoint windows, one all-reduce): no rank runs ahead into the next step's peer-memory
+            # barriers while another is still scoring, and expert-parallel runs evaluate with every rank's experts.
+            trainer.engine.gather_experts()
+            vl = evaluate(model, eval_data, a.seq, dev, a.eval_sampling, distributed=ddp)
+        if logging_step and rank == 0:
             now = time.time()
             tps = min(a.log_every, step - start_step + 1) * accum * per_micro / max(1e-6, now - t_last)
-            due = (step % a.eval_every == 0 and step > 0) or step == stop_step - 1
-            vl = evaluate(model, eval_data, a.seq, dev, a.eval_sampling) if due else ""
             metrics.writerow([step, tok_seen, f"{loss_acc:.8f}", f"{aux_acc:.8f}", f"{lr_at(step):.8e}", f"{gn:.6f}", f"{tps:.0f}",
                               f"{now - t0:.3f}", f"{vl:.8f}" if vl != "" else "", n_active_nv, n_total_nv,
                               f"{mtp_acc:.8f}", f"{kl_acc:.8f}"])
@@ -677,6 +713,7 @@ def main(argv=None):
         save_ckpt(stop_step - 1)
     final_loss = None
     if final_data is not None:
+        trainer.engine.gather_experts()
         final_loss = evaluate(model, final_data, a.seq, dev, "sequential", distributed=ddp)
         if rank == 0:
             with open(f"{a.run_dir}/final_eval.json", "w") as f:

@@ -37,6 +37,8 @@ def main():
         y = x.roll(-1, 1).pin_memory()
         losses = [trainer.train_step([(x, y)], lr=3e-3, dense=(i == 0)).tolist() for i in range(5)]
         ops.check_errors()
+        if mode == "ep_graph":
+            assert trainer.use_graphs and trainer._graphs and trainer.replayed_launches > 0, "the expert-parallel micro-step was not replayed from a CUDA graph"
         state, _ = trainer.engine.checkpoint_state()           # assembles expert slices when the experts are split over ranks
         params = torch.cat([v.detach().float().reshape(-1) for k, v in sorted(state.items())])
         gathered = [torch.empty_like(params) for _ in range(world)]

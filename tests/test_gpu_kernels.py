@@ -550,3 +550,105 @@ def test_gdn_gates(ops):
     got, ref = run(True), run(False)
     for x, y, tol in zip(got, ref, (1e-2, 1e-5, 2e-2, 2e-2, 1e-3, 1e-3)):
         assert rel_err(x, y) < tol
+
+
+def _masked_attention_reference(q, k, v, count, index, scale):
+    """fp32 masked-softmax attention over the selected blocks (dense causal when count is None): q [B,nq,S,64], k/v [B,nkv,S,64]."""
+    from q38.models import modeling
+    B, nq, S, _ = q.shape
+    rep = nq // k.shape[1]
+    kf, vf = k.float().repeat_interleave(rep, 1), v.float().repeat_interleave(rep, 1)
+    s = (q.float() @ kf.transpose(-1, -2)) * scale
+    if count is None:
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()[None].expand(B, -1, -1)
+    else:
+        mask = modeling.block_sparse_mask(count, index, S)
+    s = s.masked_fill(~mask[:, None], float("-inf"))
+    return (s.softmax(-1) @ vf).transpose(1, 2)           # [B,S,nq,64]
+
+
+@pytest.mark.parametrize("B,S,nq,nkv,budget", [(1, 256, 4, 2, None), (2, 512, 22, 2, None), (2, 512, 22, 2, 1), (1, 1024, 6, 2, 3),
+                                                (1, 1024, 4, 2, 8), (1, 256, 4, 1, 8)])
+def test_block_attention_forward_and_gradients(ops, B, S, nq, nkv, budget):
+    """Isolated check of the block-sparse / dense attention kernels: dense, budgets 1 / 3 / 8, fewer blocks than the budget, GQA 11:1."""
+    from q38.models import modeling
+    from q38.ops.backend import _BlockAttention
+    torch.manual_seed(31)
+    q = torch.randn(B, nq, S, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    k = torch.randn(B, nkv, S, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    v = torch.randn(B, nkv, S, 64, device="cuda").to(torch.bfloat16).requires_grad_()
+    do = torch.randn(B, S, nq, 64, device="cuda").to(torch.bfloat16)
+    count = index = None
+    if budget is not None:
+        nb = S // 64
+        lp = torch.randn(B, nb, nb, device="cuda").log_softmax(-1)
+        count, index = modeling.select_blocks(lp, budget)
+        count, index = count.contiguous(), index.contiguous()
+    out = _BlockAttention.apply(q, k, v, count, index, 0.125)
+    out.backward(do)
+    ops.check_errors()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = _masked_attention_reference(qr, kr, vr, count, index, 0.125)
+    ref.backward(do.float())
+    assert rel_err(out, ref) < 2e-2
+    assert rel_err(q.grad, qr.grad) < 2e-2 and rel_err(k.grad, kr.grad) < 2e-2 and rel_err(v.grad, vr.grad) < 2e-2
+
+
+def test_elementwise_gates_match_specification(ops):
+    from q38.ops.backend import _GateAdd, _SigmoidMul, _SwiGLU
+    torch.manual_seed(32)
+    T, h = 777, 576
+    bf = lambda *shape: torch.randn(*shape, device="cuda").to(torch.bfloat16).requires_grad_()
+    fp = lambda t: t.detach().float().requires_grad_()
+    dy = torch.randn(T, h, device="cuda").to(torch.bfloat16)
+    g, u = bf(T, h), bf(T, h)
+    _SwiGLU.apply(g, u).backward(dy)
+    gr, ur = fp(g), fp(u)
+    ref = torch.nn.functional.silu(gr) * ur
+    ref.backward(dy.float())
+    assert rel_err(_SwiGLU.apply(g, u), ref) < 1e-2 and rel_err(g.grad, gr.grad) < 1e-2 and rel_err(u.grad, ur.grad) < 1e-2
+    x, gate = bf(T, h), bf(T, h)
+    _SigmoidMul.apply(x, gate).backward(dy)
+    xr, gater = fp(x), fp(gate)
+    ref = xr * torch.sigmoid(gater)
+    ref.backward(dy.float())
+    assert rel_err(_SigmoidMul.apply(x, gate), ref) < 1e-2 and rel_err(x.grad, xr.grad) < 1e-2 and rel_err(gate.grad, gater.grad) < 1e-2
+    routed, shared, logit = bf(T, h), bf(T, h), bf(T, 1)
+    _GateAdd.apply(routed, shared, logit).backward(dy)
+    rr, sr, lr_ = fp(routed), fp(shared), fp(logit)
+    ref = rr + torch.sigmoid(lr_) * sr
+    ref.backward(dy.float())
+    assert rel_err(_GateAdd.apply(routed, shared, logit), ref) < 1e-2
+    assert rel_err(routed.grad, rr.grad) < 1e-2 and rel_err(shared.grad, sr.grad) < 1e-2 and rel_err(logit.grad, lr_.grad) < 2e-2
+
+
+def test_embedding_gradient_scatter(ops):
+    torch.manual_seed(33)
+    V, h = 1000, 96
+    ids = torch.randint(0, V, (4, 300), device="cuda")
+    ids[0, :50] = 5                                           # many hits on one row
+    dout = torch.randn(4, 300, h, device="cuda")
+    grad = torch.ones(V, h, device="cuda")                    # accumulates into what is there
+    ops.load().embed_bwd(ids.contiguous(), dout.contiguous(), grad)
+    ref = torch.ones(V, h, device="cuda").index_add_(0, ids.view(-1), dout.view(-1, h))
+    torch.testing.assert_close(grad, ref, rtol=1e-5, atol=1e-4)
+
+
+def test_cross_entropy_kernel_with_ignored_rows(ops):
+    torch.manual_seed(34)
+    rows, V = 300, 10112
+    logits = torch.randn(rows, V, device="cuda").to(torch.bfloat16)
+    target = torch.randint(0, V, (rows,), device="cuda")
+    target[::3] = -100
+    for all_ignored in (False, True):
+        t = torch.full_like(target, -100) if all_ignored else target
+        work = logits.clone()
+        loss = ops.load().ce_inplace(work, t)
+        ref = torch.nn.functional.cross_entropy(logits.float(), t, ignore_index=-100, reduction="none")
+        torch.testing.assert_close(loss.float(), ref, rtol=2e-3, atol=2e-3)
+        grad_ref = torch.softmax(logits.float(), -1)
+        valid = t != -100
+        grad_ref[valid, t[valid]] -= 1.0
+        grad_ref[~valid] = 0.0
+        assert (work.float() - grad_ref).abs().max() < 1e-2
+        assert work[~valid].abs().max() == 0                  # ignored rows contribute neither loss nor gradient

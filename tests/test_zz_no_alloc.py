@@ -41,6 +41,26 @@ def test_static_scratch_sort_matches_operator():
         r_perm, r_inv, r_offsets, r_sched = lib_ops.moe_sort(idx, E)
         assert torch.equal(perm, r_perm) and torch.equal(inv, r_inv) and torch.equal(offsets, r_offsets)
         assert torch.equal(sched[:r_sched.numel()], r_sched)
+    # expert ids outside [0, experts) are skipped: inv_perm -1, not counted, the remaining pairs sorted as usual
+    T, k, E = 300, 2, 8
+    idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).to(torch.int32).contiguous()
+    bad = torch.tensor([3, 77, 410], device=dev)
+    flat = idx.view(-1)
+    flat[bad] = torch.tensor([-1, 64, 8], dtype=torch.int32, device=dev)
+    P = T * k
+    max_tiles = (P + 127) // 128 + E
+    perm = torch.full((P,), -7, dtype=torch.int32, device=dev)
+    inv = torch.full((P,), -7, dtype=torch.int32, device=dev)
+    offsets = torch.full((E + 1,), -7, dtype=torch.int32, device=dev)
+    sched = torch.full((1 + 3 * max_tiles,), -7, dtype=torch.int32, device=dev)
+    assert fn(idx.data_ptr(), P, E, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(), sched.data_ptr(), max_tiles, ctypes.c_void_p(stream.cuda_stream)) == 0
+    torch.cuda.synchronize(dev)
+    good = torch.ones(P, dtype=torch.bool, device=dev)
+    good[bad] = False
+    assert int(offsets[E]) == P - 3 and torch.equal(inv[bad], torch.full((3,), -1, dtype=torch.int32, device=dev))
+    order = torch.sort(flat[good].long(), stable=True).indices
+    assert torch.equal(perm[:P - 3].long(), torch.nonzero(good).view(-1)[order])
+    assert torch.equal(perm[P - 3:], torch.full((3,), -7, dtype=torch.int32, device=dev))
     # sizes beyond the static scratch are refused and nothing is launched
     big = 1024 * 1024 + 1
     assert fn(idx.data_ptr(), big, 64, perm.data_ptr(), inv.data_ptr(), offsets.data_ptr(), sched.data_ptr(), big, ctypes.c_void_p(stream.cuda_stream)) == 1
