@@ -178,7 +178,7 @@ def main():
             "vs_baseline": published, "dtype": "bf16", "data": "synthetic packed stream (uniform ids, EOS at geometric(1024) boundaries; a fresh batch every step), random-init weights",
             "impl": "ours",
             "config": {"model": a.preset, "global_batch": batch_tokens // a.seq, "seq_len": a.seq, "micro_bs": micro_bs,
-                       "accum": accum, "parallelism": f"dp{world}" + (f"+ep{world}" if a.expert_parallel and world > 1 else ""), "phase": a.phase, "grad_sync": trainer.engine.mode,
+                       "accum": accum, "parallelism": f"dp{world}" + (f"+ep{world}" if a.expert_parallel and world > 1 else ""), "phase": a.phase, "grad_sync": trainer.engine.describe_transport(),
                        "grad_ckpt": int(args.grad_ckpt), "zipf": a.zipf,
                        "l2": "no flush: one step streams >10 GB of activations and 1.3 GB of fp32 weights, far above the 126 MB L2",
                        "train_flops_per_token": fc["train_flops_per_token"]},

@@ -80,6 +80,17 @@ TORCH_LIBRARY(q38, m) {
   m.def("p2p_all_gather(Tensor params, Tensor? shadow, int[] peer_params, int[] peer_shadow, int rank, int start, int count, Tensor? err=None) -> ()",
         [](const at::Tensor& p, c10::optional<at::Tensor> sh, std::vector<int64_t> pp, std::vector<int64_t> ps, int64_t rank, int64_t start, int64_t count,
            c10::optional<at::Tensor> err) { q38::p2p_all_gather(p, sh, pp, ps, rank, start, count, err); });
+  m.def("nvls_reduce_scatter(int mc_grads, Tensor(a!) grads, int start, int count, float scale, Tensor? err=None) -> ()",
+        [](int64_t mc, at::Tensor& g, int64_t start, int64_t count, double scale, c10::optional<at::Tensor> err) { q38::nvls_reduce_scatter(mc, g, start, count, scale, err); });
+  m.def("nvls_all_gather(Tensor params, int mc_params, int start, int count, Tensor? err=None) -> ()",
+        [](const at::Tensor& p, int64_t mc, int64_t start, int64_t count, c10::optional<at::Tensor> err) { q38::nvls_all_gather(p, mc, start, count, err); });
+  m.def("p2p_push_segments(Tensor grads, int[] peer_staging, int[] starts, int[] counts, int slot_stride, int rank, Tensor? err=None) -> ()",
+        [](const at::Tensor& g, std::vector<int64_t> st, std::vector<int64_t> starts, std::vector<int64_t> counts, int64_t stride, int64_t rank,
+           c10::optional<at::Tensor> err) { q38::p2p_push_segments(g, st, starts, counts, stride, rank, err); });
+  m.def("p2p_reduce_staged(Tensor(a!) grads, Tensor staging, int slot_stride, int rank, int world, int start, int count, float scale, Tensor? err=None) -> ()",
+        [](at::Tensor& g, const at::Tensor& st, int64_t stride, int64_t rank, int64_t world, int64_t start, int64_t count, double scale, c10::optional<at::Tensor> err) {
+          q38::p2p_reduce_staged(g, st, stride, rank, world, start, count, scale, err);
+        });
   m.def("p2p_publish_scalar(Tensor value, int[] peer_slots, int rank) -> ()",
         [](const at::Tensor& v, std::vector<int64_t> slots, int64_t rank) { q38::p2p_publish_scalar(v, slots, rank); });
   m.def("ce_inplace(Tensor(a!) logits, Tensor target) -> Tensor", [](at::Tensor& l, const at::Tensor& t) { return q38::ce_inplace(l, t); });

@@ -8,8 +8,14 @@
 //   p2p_all_gather       rank r stores its updated fp32 parameters and bf16 shadow of segment r into every peer's arenas.
 //   p2p_publish_scalar   writes one double into slot r of every peer's scalar array (global gradient norm).
 //
+//   *_nvls               the same two transfers through the NVSwitch: `multimem.ld_reduce` sums the segment over all GPUs
+//                        inside the switch (each rank receives one copy instead of world - 1), `multimem.st` writes the
+//                        updated parameters to every GPU with one store.  They need a multicast mapping of the arenas.
+//   p2p_push_segments /  push variant of the reduce-scatter: every rank stores its contribution to segment r into a
+//   p2p_reduce_staged    staging slot on rank r (posted writes), then rank r sums the slots locally in rank order.
+//
 // Every wait is bounded by a clock budget; on expiry the kernel records ERR_PEER_WAIT and returns, the context stays
-// usable and the host raises.  Loads from peers are plain (no TMA, no multicast); NVLS multimem is not used.
+// usable and the host raises.  Loads from peers are plain or multimem (no TMA, no cluster multicast).
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -125,6 +131,68 @@ __global__ void __launch_bounds__(256) p2p_all_gather_kernel(const float* __rest
   }
 }
 
+// ---- NVLS: reductions and broadcasts performed by the NVSwitch on a multicast address ------------------------------------------
+__device__ __forceinline__ float4 multimem_ld_reduce_add(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st(float* mc, const float4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// own[i] = scale * (sum over all GPUs of grads[i]) for i in [start, start + count), the sum taken by the switch.
+__global__ void __launch_bounds__(256) nvls_reduce_scatter_kernel(const float* __restrict__ mc_grads, float* __restrict__ own, long long start, long long count,
+                                                                  float scale, const int* __restrict__ err) {
+  if (aborted(err)) return;
+  const long long n4 = count / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 v = multimem_ld_reduce_add(mc_grads + start + 4 * i);
+    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    reinterpret_cast<float4*>(own + start)[i] = v;
+  }
+}
+
+// Every GPU's params[i] = this rank's params[i] for i in [start, start + count): one multicast store per 16 bytes.
+__global__ void __launch_bounds__(256) nvls_all_gather_kernel(const float* __restrict__ params, float* __restrict__ mc_params, long long start, long long count,
+                                                              const int* __restrict__ err) {
+  if (aborted(err)) return;
+  const long long n4 = count / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x)
+    multimem_st(mc_params + start + 4 * i, reinterpret_cast<const float4*>(params + start)[i]);
+}
+
+// ---- push variant of the reduce-scatter --------------------------------------------------------------------------------------------
+struct SegmentTable { long long start[MAX_PEERS]; long long count[MAX_PEERS]; long long slot_stride; };
+
+// For every peer p != rank: staging_p[rank * slot_stride + i] = grads[start_p + i], i < count_p.  blockIdx.y walks the peers.
+__global__ void __launch_bounds__(256) p2p_push_segments_kernel(const float* __restrict__ grads, PeerPtrs staging, SegmentTable seg, int rank, int world,
+                                                                const int* __restrict__ err) {
+  if (aborted(err)) return;
+  const int p = blockIdx.y;
+  if (p >= world || p == rank) return;
+  const float4* src = reinterpret_cast<const float4*>(grads + seg.start[p]);
+  float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(staging.p[p]) + (long long)rank * seg.slot_stride);
+  const long long n4 = seg.count[p] / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// own[start + i] = scale * (sum over ranks q in rank order of (q == rank ? own[start + i] : staging[q * slot_stride + i]))
+__global__ void __launch_bounds__(256) p2p_reduce_staged_kernel(float* __restrict__ own, const float* __restrict__ staging, long long slot_stride, int rank, int world,
+                                                                long long start, long long count, float scale, const int* __restrict__ err) {
+  if (aborted(err)) return;
+  const long long n4 = count / 4;
+  float4* dst = reinterpret_cast<float4*>(own + start);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < world; ++q) {
+      const float4 v = q == rank ? dst[i] : reinterpret_cast<const float4*>(staging + (long long)q * slot_stride)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    dst[i] = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+  }
+}
+
 // shadow[i] = bf16(params[i]) for every i outside [skip_start, skip_start + skip_count): after the all-gather has delivered the
 // peers' fp32 segments, each rank derives their bf16 copies locally instead of receiving them over NVLink.
 __global__ void __launch_bounds__(256) cast_shadow_except_kernel(const float* __restrict__ params, __nv_bfloat16* __restrict__ shadow, long long n4,
@@ -214,6 +282,66 @@ void p2p_all_gather(const at::Tensor& params, const c10::optional<at::Tensor>& s
   p2p_all_gather_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(params.data_ptr<float>(),
       shadow.has_value() ? (const __nv_bfloat16*)shadow->data_ptr() : nullptr, to_ptrs(peer_params), to_ptrs(peer_shadow), (int)rank,
       (int)peer_params.size(), start, count, err.has_value() ? err->data_ptr<int>() : nullptr);
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+static int stream_grid(long long count) { return (int)std::min<int64_t>((count / 4 + 255) / 256, kNumSMs * 8); }
+static const int* err_or_null(const c10::optional<at::Tensor>& err) { return err.has_value() ? err->data_ptr<int>() : nullptr; }
+
+void nvls_reduce_scatter(int64_t mc_grads, at::Tensor& grads, int64_t start, int64_t count, double scale, const c10::optional<at::Tensor>& err) {
+  TORCH_CHECK(mc_grads != 0 && (mc_grads & 15) == 0, "nvls_reduce_scatter: a 16-byte aligned multicast address is required");
+  TORCH_CHECK(grads.is_cuda() && grads.scalar_type() == at::kFloat && grads.is_contiguous() && start % 4 == 0 && count % 4 == 0 && start + count <= grads.numel(),
+              "nvls_reduce_scatter: flat fp32 arena and a 16-byte aligned segment inside it required");
+  if (count == 0) return;
+  const c10::cuda::CUDAGuard guard(grads.device());
+  nvls_reduce_scatter_kernel<<<stream_grid(count), 256, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<const float*>(mc_grads), grads.data_ptr<float>(), start,
+                                                                                                 count, (float)scale, err_or_null(err));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void nvls_all_gather(const at::Tensor& params, int64_t mc_params, int64_t start, int64_t count, const c10::optional<at::Tensor>& err) {
+  TORCH_CHECK(mc_params != 0 && (mc_params & 15) == 0, "nvls_all_gather: a 16-byte aligned multicast address is required");
+  TORCH_CHECK(params.is_cuda() && params.scalar_type() == at::kFloat && params.is_contiguous() && start % 4 == 0 && count % 4 == 0 && start + count <= params.numel(),
+              "nvls_all_gather: flat fp32 arena and a 16-byte aligned segment inside it required");
+  if (count == 0) return;
+  const c10::cuda::CUDAGuard guard(params.device());
+  nvls_all_gather_kernel<<<stream_grid(count), 256, 0, at::cuda::getCurrentCUDAStream()>>>(params.data_ptr<float>(), reinterpret_cast<float*>(mc_params), start, count,
+                                                                                             err_or_null(err));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void p2p_push_segments(const at::Tensor& grads, std::vector<int64_t> peer_staging, std::vector<int64_t> starts, std::vector<int64_t> counts, int64_t slot_stride,
+                       int64_t rank, const c10::optional<at::Tensor>& err) {
+  const int world = (int)peer_staging.size();
+  TORCH_CHECK(world <= MAX_PEERS && (int)starts.size() == world && (int)counts.size() == world && slot_stride % 4 == 0, "p2p_push_segments: bad segment table");
+  SegmentTable seg{};
+  long long longest = 0;
+  for (int p = 0; p < world; ++p) {
+    TORCH_CHECK(starts[p] % 4 == 0 && counts[p] % 4 == 0 && counts[p] <= slot_stride, "p2p_push_segments: segments must be 16-byte aligned and fit a staging slot");
+    seg.start[p] = starts[p]; seg.count[p] = counts[p];
+    longest = std::max<long long>(longest, counts[p]);
+  }
+  seg.slot_stride = slot_stride;
+  if (longest == 0) return;
+  const c10::cuda::CUDAGuard guard(grads.device());
+  const int gx = std::max(1, std::min<int>((int)((longest / 4 + 255) / 256), kNumSMs * 8 / std::max(1, world - 1)));
+  p2p_push_segments_kernel<<<dim3(gx, world), 256, 0, at::cuda::getCurrentCUDAStream()>>>(grads.data_ptr<float>(), to_ptrs(peer_staging), seg, (int)rank, world,
+                                                                                            err_or_null(err));
+  C10_CUDA_KERNEL_LAUNCH_CHECK();
+  count_launch();
+}
+
+void p2p_reduce_staged(at::Tensor& grads, const at::Tensor& staging, int64_t slot_stride, int64_t rank, int64_t world, int64_t start, int64_t count, double scale,
+                       const c10::optional<at::Tensor>& err) {
+  TORCH_CHECK(grads.scalar_type() == at::kFloat && staging.scalar_type() == at::kFloat && staging.numel() >= world * slot_stride && start % 4 == 0 && count % 4 == 0 &&
+              count <= slot_stride, "p2p_reduce_staged: fp32 arena, staging of world slots and an aligned segment required");
+  if (count == 0) return;
+  const c10::cuda::CUDAGuard guard(grads.device());
+  p2p_reduce_staged_kernel<<<stream_grid(count), 256, 0, at::cuda::getCurrentCUDAStream()>>>(grads.data_ptr<float>(), staging.data_ptr<float>(), slot_stride, (int)rank,
+                                                                                               (int)world, start, count, (float)scale, err_or_null(err));
   C10_CUDA_KERNEL_LAUNCH_CHECK();
   count_launch();
 }

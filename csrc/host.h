@@ -133,6 +133,12 @@ void p2p_reduce_scatter(std::vector<int64_t> grads, int64_t rank, int64_t start,
                         const c10::optional<at::Tensor>& err);
 void p2p_all_gather(const at::Tensor& params, const c10::optional<at::Tensor>& shadow, std::vector<int64_t> peer_params, std::vector<int64_t> peer_shadow,
                     int64_t rank, int64_t start, int64_t count, const c10::optional<at::Tensor>& err);
+void nvls_reduce_scatter(int64_t mc_grads, at::Tensor& grads, int64_t start, int64_t count, double scale, const c10::optional<at::Tensor>& err);
+void nvls_all_gather(const at::Tensor& params, int64_t mc_params, int64_t start, int64_t count, const c10::optional<at::Tensor>& err);
+void p2p_push_segments(const at::Tensor& grads, std::vector<int64_t> peer_staging, std::vector<int64_t> starts, std::vector<int64_t> counts, int64_t slot_stride,
+                       int64_t rank, const c10::optional<at::Tensor>& err);
+void p2p_reduce_staged(at::Tensor& grads, const at::Tensor& staging, int64_t slot_stride, int64_t rank, int64_t world, int64_t start, int64_t count, double scale,
+                       const c10::optional<at::Tensor>& err);
 void cast_shadow_except(const at::Tensor& params, at::Tensor& shadow, int64_t skip_start, int64_t skip_count, const c10::optional<at::Tensor>& err);
 void p2p_publish_scalar(const at::Tensor& value, std::vector<int64_t> peer_slots, int64_t rank);
 // ce.cu

@@ -246,6 +246,12 @@ class GradEngine:
         self.optimizer.load_state_dict(opt_state)
         self.arena.refresh_shadow()
 
+    def describe_transport(self):
+        """'collective', or 'p2p' with the reduce-scatter algorithm and the allocation back end of the peer arenas."""
+        if self.transport is None:
+            return self.mode
+        return f"{self.mode}:{self.transport.rs_algo}:{self.transport.alloc_backend}"
+
     def describe(self):
         info = self.arena.describe()
         return f"{self.mode} world={self.world} arena={info['numel'] / 1e6:.1f}M elements owner_numel={info['owner_numel']}"

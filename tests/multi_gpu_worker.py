@@ -26,12 +26,18 @@ def main():
                  ngram_rows=1024, mhc_iters=5, qsa_blocks=2)
     cfg = model_config(shape, 512, 256, eos_token_id=7, pad_token_id=0)
     results = {}
-    for mode in ("p2p", "collective", "ep", "ep_graph"):
+    for mode in ("p2p", "p2p_pull", "p2p_push", "collective", "ep", "ep_graph"):
+        # "p2p" takes the default reduce-scatter (the NVSwitch multimem kernels when a multicast mapping exists); the other
+        # two force the peer-load and the push variants on CUDA IPC allocations
+        os.environ["Q38_RS_ALGO"] = {"p2p_pull": "pull", "p2p_push": "push"}.get(mode, "auto")
+        os.environ["Q38_PEER_ALLOC"] = "ipc" if mode in ("p2p_pull", "p2p_push") else "auto"
         torch.manual_seed(0)
         args = SimpleNamespace(**{**TRAIN_DEFAULTS, "aux_coef": 0.001, "lr": 3e-3, "grad_sync": "collective" if mode == "collective" else "p2p",
                                   "cuda_graphs": int(mode == "ep_graph"), "expert_parallel": int(mode.startswith("ep")), "micro_bs": 2, "seq": 256})
         trainer = Trainer(cfg, args, dev, rank, world)
         assert trainer.engine.mode == args.grad_sync
+        if rank == 0 and trainer.engine.transport is not None:
+            print(f"[{mode}] peer allocations: {trainer.engine.transport.alloc_backend}, reduce-scatter: {trainer.engine.transport.rs_algo}", flush=True)
         gen = torch.Generator().manual_seed(100 + rank)
         x = torch.randint(1, 512, (2, 256), generator=gen).pin_memory()
         y = x.roll(-1, 1).pin_memory()
@@ -57,6 +63,9 @@ def main():
         assert losses[-1][0] < losses[0][0], (mode, losses)
         results[mode] = (params, losses)
         trainer.close()
+    for variant in ("p2p_pull", "p2p_push"):
+        rel_v = ((results[variant][0] - results["collective"][0]).norm() / results["collective"][0].norm()).item()
+        assert rel_v < 1e-2, f"{variant} disagrees with the collective transport: {rel_v}"
     a, b = results["p2p"][0], results["collective"][0]
     rel = ((a - b).norm() / b.norm()).item()
     first = abs(results["p2p"][1][0][0] - results["collective"][1][0][0])

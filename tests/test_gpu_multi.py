@@ -42,7 +42,8 @@ def test_peer_memory_gradient_path_matches_collectives():
 def test_late_rank_aborts_the_step_cleanly():
     """A rank that stalls on the host for longer than the bounded barrier wait: every rank raises, nothing is updated."""
     world = min(torch.cuda.device_count(), 4)
-    env = {**os.environ, "NCCL_NVLS_ENABLE": "0", "Q38_PEER_WAIT_SECONDS": "1"}
+    # plain peer loads and IPC allocations: a failure test must not run with memory bound to an NVLink multicast object
+    env = {**os.environ, "NCCL_NVLS_ENABLE": "0", "Q38_PEER_WAIT_SECONDS": "1", "Q38_PEER_ALLOC": "ipc", "Q38_RS_ALGO": "pull"}
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", "29657", str(ROOT / "tests" / "late_rank_worker.py")]
     done = subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=600)
