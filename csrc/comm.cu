@@ -97,13 +97,22 @@ __global__ void __launch_bounds__(256) p2p_reduce_scatter_kernel(PeerPtrs grads,
   for (int p = 0; p < MAX_PEERS; ++p) src[p] = p < world ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[p]) + start) : nullptr;
   float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(grads.p[rank]) + start);
   const long long n4 = count / 4;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  // two 16-byte elements per thread and step: twice the loads in flight per thread on a path whose latency is a NVLink round trip
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += 2 * stride) {
+    const long long j = i + stride;
+    const bool second = j < n4;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
 #pragma unroll
     for (int p = 0; p < MAX_PEERS; ++p) {
-      if (p < world) { const float4 v = src[p][i]; acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+      if (p < world) {
+        const float4 v = src[p][i];
+        a0.x += v.x; a0.y += v.y; a0.z += v.z; a0.w += v.w;
+        if (second) { const float4 w = src[p][j]; a1.x += w.x; a1.y += w.y; a1.z += w.z; a1.w += w.w; }
+      }
     }
-    dst[i] = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+    dst[i] = make_float4(a0.x * scale, a0.y * scale, a0.z * scale, a0.w * scale);
+    if (second) dst[j] = make_float4(a1.x * scale, a1.y * scale, a1.z * scale, a1.w * scale);
   }
 }
 
@@ -145,11 +154,15 @@ __device__ __forceinline__ void multimem_st(float* mc, const float4& v) {
 __global__ void __launch_bounds__(256) nvls_reduce_scatter_kernel(const float* __restrict__ mc_grads, float* __restrict__ own, long long start, long long count,
                                                                   float scale, const int* __restrict__ err) {
   if (aborted(err)) return;
-  const long long n4 = count / 4;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+  const long long n4 = count / 4, stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += 2 * stride) {
+    const long long j = i + stride;
     float4 v = multimem_ld_reduce_add(mc_grads + start + 4 * i);
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j < n4) w = multimem_ld_reduce_add(mc_grads + start + 4 * j);
     v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
     reinterpret_cast<float4*>(own + start)[i] = v;
+    if (j < n4) { w.x *= scale; w.y *= scale; w.z *= scale; w.w *= scale; reinterpret_cast<float4*>(own + start)[j] = w; }
   }
 }
 

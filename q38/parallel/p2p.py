@@ -10,8 +10,8 @@ the other GPUs can address.  Two allocation back ends:
             Selected with ``Q38_PEER_ALLOC=ipc`` and used by the failure tests (a rank must not disappear while its
             memory is bound to a multicast object).
 
-Reduce-scatter algorithms (``Q38_RS_ALGO`` = auto | nvls | pull | push; auto = nvls when a multicast address exists,
-else pull):
+Reduce-scatter algorithms (``Q38_RS_ALGO`` = auto | nvls | pull | push; auto = nvls when a multicast address exists
+and there are at least four ranks, else pull):
   ``pull``  one shot: rank r loads segment r from every peer and sums                 (world - 1 segments in over NVLink)
   ``push``  two shots: every rank stores its part of segment r into a slot on rank r, rank r sums its slots locally
   ``nvls``  the switch sums: rank r issues `multimem.ld_reduce` over segment r        (one segment in over NVLink)
@@ -103,7 +103,10 @@ class PeerTransport:
         self.arena = arena
         self.exchange()
         if self.rs_algo == "auto":
-            self.rs_algo = "nvls" if self.multicast.get("grads") and self.multicast.get("params") else "pull"
+            # with two ranks a peer load moves one segment, exactly what the switch reduction would deliver; the switch pays
+            # off from four ranks on, where it replaces world - 1 incoming copies by one
+            have_mc = bool(self.multicast.get("grads") and self.multicast.get("params"))
+            self.rs_algo = "nvls" if (have_mc and self.world >= 4) else "pull"
         if self.rs_algo == "nvls" and not (self.multicast.get("grads") and self.multicast.get("params")):
             raise RuntimeError("Q38_RS_ALGO=nvls needs multicast addresses of the arenas (symmetric-memory allocations on an NVSwitch system)")
         if self.rs_algo == "push":
