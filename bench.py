@@ -41,6 +41,7 @@ def parse():
     ap.add_argument("--grad_ckpt", type=int, default=-1)
     ap.add_argument("--expert_parallel", type=int, default=0, help="1: split the experts over the GPUs (needs --gpus > 1)")
     ap.add_argument("--ep_capacity", type=float, default=4.0)
+    ap.add_argument("--fp8_ffn", type=int, default=0, help="1: routed experts on block-scaled MXFP8 GEMMs (bf16 master weights, bf16 weight gradients)")
     ap.add_argument("--overlap_wgrad", type=int, default=1, help="0: weight-gradient GEMMs on the main stream instead of a second one")
     ap.add_argument("--cuda_graphs", type=int, default=1)
     return ap.parse_args()
@@ -90,7 +91,7 @@ def main():
     cfg = model_config(preset["model"], vocab, a.seq, bos_token_id=1, eos_token_id=eos, pad_token_id=0)
     fc = count(cfg.to_dict(), a.seq)
     args = SimpleNamespace(**{**train, "aux_coef": preset["model"]["aux_coef"], "grad_sync": a.grad_sync, "micro_bs": micro_bs, "seq": a.seq,
-                              "expert_parallel": a.expert_parallel, "ep_capacity": a.ep_capacity, "overlap_wgrad": a.overlap_wgrad, "cuda_graphs": a.cuda_graphs,
+                              "expert_parallel": a.expert_parallel, "fp8_ffn": a.fp8_ffn, "ep_capacity": a.ep_capacity, "overlap_wgrad": a.overlap_wgrad, "cuda_graphs": a.cuda_graphs,
                               "grad_ckpt": train.get("grad_ckpt", 0) if a.grad_ckpt < 0 else a.grad_ckpt})
     torch.manual_seed(0)
     trainer = Trainer(cfg, args, dev, rank, world)
@@ -179,7 +180,7 @@ def main():
             "impl": "ours",
             "config": {"model": a.preset, "global_batch": batch_tokens // a.seq, "seq_len": a.seq, "micro_bs": micro_bs,
                        "accum": accum, "parallelism": f"dp{world}" + (f"+ep{world}" if a.expert_parallel and world > 1 else ""), "phase": a.phase, "grad_sync": trainer.engine.describe_transport(),
-                       "grad_ckpt": int(args.grad_ckpt), "zipf": a.zipf,
+                       "grad_ckpt": int(args.grad_ckpt), "zipf": a.zipf, "fp8_ffn": int(a.fp8_ffn),
                        "l2": "no flush: one step streams >10 GB of activations and 1.3 GB of fp32 weights, far above the 126 MB L2",
                        "train_flops_per_token": fc["train_flops_per_token"]},
             "mfu_of_measured_sustained_peak": value * fc["train_flops_per_token"] / (world * peak_tflops * 1e12),

@@ -14,6 +14,14 @@ TORCH_LIBRARY(q38, m) {
            c10::optional<at::Tensor> addend, double beta) {
           q38::gemm_bf16_persistent(a, b, c, amn, bmn, alpha, acc, err, splits, addend, beta);
         });
+  m.def("mxfp8_pick_bn(int N) -> int", &q38::mxfp8_pick_bn);
+  m.def("mxfp8_quantize_rows(Tensor src, Tensor? perm, int topk, Tensor sched, int P) -> Tensor[]",
+        [](const at::Tensor& src, c10::optional<at::Tensor> perm, int64_t topk, const at::Tensor& sched, int64_t P) { return q38::mxfp8_quantize_rows(src, perm, topk, sched, P); });
+  m.def("mxfp8_quantize_weight(Tensor w, int bn) -> Tensor[]", &q38::mxfp8_quantize_weight);
+  m.def("mxfp8_grouped_gemm(Tensor aq, Tensor sfa, Tensor wq, Tensor sfw, Tensor(a!) out, Tensor sched, int bn, Tensor(b!) err) -> ()",
+        [](const at::Tensor& aq, const at::Tensor& sfa, const at::Tensor& wq, const at::Tensor& sfw, at::Tensor& out, const at::Tensor& sched, int64_t bn, at::Tensor& err) {
+          q38::mxfp8_grouped_gemm(aq, sfa, wq, sfw, out, sched, bn, err);
+        });
   m.def("muon_prepass(Tensor grads, Tensor(a!) buf, Tensor(b!) work, Tensor(c!) sumsq, Tensor mats, Tensor tiles, Tensor? grad_scale, float momentum, Tensor? err) -> ()",
         [](const at::Tensor& g, at::Tensor& b, at::Tensor& w, at::Tensor& s, const at::Tensor& mats, const at::Tensor& tiles, c10::optional<at::Tensor> gs, double mom,
            c10::optional<at::Tensor> err) { q38::muon_prepass(g, b, w, s, mats, tiles, gs, mom, err); });

@@ -232,7 +232,7 @@ static CUtensorMap make_tmap(const void* base, int elem_bytes, int64_t inner, in
   cuuint32_t box[3] = {(cuuint32_t)(box_inner_bytes / elem_bytes), (cuuint32_t)box_rows, 1};
   cuuint32_t elem[3] = {1, 1, 1};
   auto encode = [&] {
-    return encode_fn()(&m, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
+    return encode_fn()(&m, elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, box_inner_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };

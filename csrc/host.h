@@ -23,6 +23,13 @@ void gemm_bf16(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_m
 void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
                           bool accumulate, at::Tensor& err, int64_t splits, const c10::optional<at::Tensor>& addend = c10::nullopt, double beta = 0.0);
 
+// mxfp8.cu
+int64_t mxfp8_pick_bn(int64_t N);
+std::vector<at::Tensor> mxfp8_quantize_rows(const at::Tensor& src, const c10::optional<at::Tensor>& perm, int64_t topk, const at::Tensor& sched, int64_t P);
+std::vector<at::Tensor> mxfp8_quantize_weight(const at::Tensor& w, int64_t bn);
+void mxfp8_grouped_gemm(const at::Tensor& aq, const at::Tensor& sfa, const at::Tensor& wq, const at::Tensor& sfw, at::Tensor& out, const at::Tensor& sched, int64_t bn,
+                        at::Tensor& err);
+
 // muon.cu
 void muon_prepass(const at::Tensor& grads, at::Tensor& buf, at::Tensor& work, at::Tensor& sumsq, const at::Tensor& mats, const at::Tensor& tiles,
                   const c10::optional<at::Tensor>& grad_scale, double momentum, const c10::optional<at::Tensor>& err);

@@ -612,6 +612,7 @@ class Backend:
         # True: no atomically accumulated split-K; weight gradients are then bitwise reproducible from run to run
         self.deterministic = bool(int(os.environ.get("Q38_DETERMINISTIC", "0")))
         self.ep = None            # an `ExpertParallel` context when the experts are split over ranks
+        self.fp8_ffn = False      # routed experts on block-scaled MXFP8 GEMMs (`q38.ops.fp8`); set by the trainer from --fp8_ffn
         if self_check:
             self._self_check()
 
@@ -820,6 +821,9 @@ class Backend:
         if self.ep is not None and torch.is_grad_enabled():
             from ..parallel.ep import _ExpertsEP
             routed = _ExpertsEP.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj, self.ep, self.ep.layer_index(block))
+        elif self.fp8_ffn:
+            from .fp8 import ExpertsFP8
+            routed = ExpertsFP8.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj, _bf16_weight, WGRAD_STREAM)
         else:
             routed = _Experts.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj)
         shared = block.shared_expert
@@ -838,7 +842,7 @@ class Backend:
     def describe(self):
         native = sorted(n for n in ("linear", "rmsnorm", "gated_rmsnorm", "mhc_pre_norm", "mhc_post", "gated_deltanet",
                                     "qsa_attention", "moe_block", "ngram_delta", "embedding", "linear_cross_entropy") if hasattr(self, n))
-        return dict(native=native, gemm_layouts=self.layouts, library_matmul_fallbacks=dict(LIBRARY_FALLBACKS))
+        return dict(native=native, gemm_layouts=self.layouts, library_matmul_fallbacks=dict(LIBRARY_FALLBACKS), fp8_ffn=bool(self.fp8_ffn))
 
 
 class _LinearCE(torch.autograd.Function):

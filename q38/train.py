@@ -119,7 +119,8 @@ def parse_args(argv=None):
          "Invalid training or evaluation sampling mode"),
         (a.data_seed >= -1, "data_seed must be -1 (use model seed) or nonnegative"),
         (a.grad_sync in ("auto", "p2p", "collective"), "--grad_sync must be auto, p2p or collective"),
-        (a.fp8_ffn == 0, "--fp8_ffn 1 is not available: the routed experts run in bf16 (no block-scaled FP8 grouped GEMM in this build)"),
+        (a.fp8_ffn in (0, 1) and not (a.fp8_ffn and a.expert_parallel), "--fp8_ffn must be 0 or 1 and cannot be combined with --expert_parallel 1"),
+        (not a.fp8_ffn or (a.hidden % 16 == 0 and a.moe_ffn % 16 == 0), "--fp8_ffn 1 needs hidden and moe_ffn to be multiples of 16"),
     ]
     for ok, message in checks:
         if not ok:
@@ -330,6 +331,9 @@ class Trainer:
             modeling.get_backend().ep = ExpertParallel(
                 self.engine.transport, rank, world, cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts, cfg.num_experts_per_tok,
                 tokens=a.micro_bs * a.seq, layers=layers, capacity_factor=float(getattr(a, "ep_capacity", 4.0)))
+        if dev.type == "cuda":
+            from .models import modeling
+            modeling.get_backend().fp8_ffn = bool(getattr(a, "fp8_ffn", 0))      # routed experts on block-scaled MXFP8 GEMMs
         self.model.train()
         # One CUDA graph per (micro-batch shape, accumulation count, attention phase) replays forward + backward of a
         # micro-step without any per-kernel host work; the optimizer step stays eager.
@@ -350,6 +354,8 @@ class Trainer:
             WGRAD_STREAM.enabled = False
         if backend is not None and getattr(backend, "ep", None) is not None:
             backend.ep = None
+        if backend is not None:
+            backend.fp8_ffn = False
         self._graphs = {}
         self.engine.close()
 
