@@ -117,6 +117,7 @@ def dump_ops(out):
 def dump_curve(out, spec):
     cfg, model = build(spec)
     shape = spec["shape"]
+    torch.save({k: v.detach().clone() for k, v in model.state_dict().items()}, str(out) + ".init.pt")     # the other side starts from the same weights
     wrapped = LossModel(model, shape["experts"], shape["topk"], ce=PlainCE())
     opt = HybridOptimizer(model, lr=spec["lr"], weight_decay=spec.get("wd", 0.1))
     coef = (1.0, shape.get("aux_coef", 0.001), spec.get("mtp_coef", 0.3), spec.get("kl_coef", 0.05))

@@ -55,6 +55,47 @@ class _Linear(torch.autograd.Function):
         return dx, dw, None
 
 
+class _MultiLinear(torch.autograd.Function):
+    """Several projections of one input: ``y_i = x W_i^T``.  The point is the backward pass: the input gradient
+    ``dx = sum_i dy_i W_i`` is built by a chain of GEMMs whose epilogue adds the running sum (addend with beta = 1), so autograd
+    never launches elementwise additions of ``[tokens, hidden]`` tensors for an activation that feeds several projections."""
+
+    @staticmethod
+    def forward(ctx, x, backend, *weights):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        x2 = x2.contiguous()
+        outs = tuple(backend.mm_nt(x2, _bf16_weight(w)).view(*x.shape[:-1], w.shape[0]) for w in weights)
+        ctx.save_for_backward(x2, *weights)
+        ctx.backend, ctx.in_shape, ctx.in_dtype = backend, x.shape, x.dtype
+        return outs
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x2, *weights = ctx.saved_tensors
+        backend = ctx.backend
+        dx = None
+        dws = []
+        for i, (dy, weight) in enumerate(zip(dys, weights)):
+            if dy is None:
+                dws.append(None)
+                continue
+            dy2 = dy.reshape(-1, dy.shape[-1]).to(torch.bfloat16).contiguous()
+            if ctx.needs_input_grad[0]:
+                w = _bf16_weight(weight)
+                if dx is None:
+                    dx = backend.mm_nn(dy2, w)
+                elif w.shape[1] % 8 == 0 and backend.layouts["nn"]:
+                    dx = gemm(_tma_rows(dy2), w, b_mn_major=True, addend=dx, beta=1.0)        # dx <- dy_i W_i + dx, one kernel
+                else:
+                    dx = dx + backend.mm_nn(dy2, w)
+            dws.append(backend.weight_grad(dy2, x2, weight) if ctx.needs_input_grad[2 + i] else None)
+        if dx is not None:
+            dx = dx.view(ctx.in_shape).to(ctx.in_dtype)
+        return (dx, None, *dws)
+
+
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, eps, out_dtype):
@@ -676,6 +717,10 @@ class Backend:
     def linear(self, x, weight):
         return _Linear.apply(x, weight, self)
 
+    def linears(self, x, *weights):
+        """Projections of one input by several weights (tuple of outputs); their input gradients are summed inside the GEMMs."""
+        return _MultiLinear.apply(x, self, *weights)
+
     def rmsnorm(self, x, weight, eps, out_dtype):
         return _RMSNorm.apply(x, weight, eps, out_dtype)
 
@@ -715,9 +760,9 @@ class Backend:
             return None
         from ..models import modeling
         F = torch.nn.functional
-        qkv = _ConvSilu.apply(self.linear(x, m.in_proj_qkv.weight), m.conv1d.weight)
-        z = self.linear(x, m.in_proj_z.weight)
-        beta, g = _GdnGates.apply(self.linear(x, m.in_proj_b.weight), self.linear(x, m.in_proj_a.weight), m.A_log, m.dt_bias)
+        p_qkv, z, p_b, p_a = self.linears(x, m.in_proj_qkv.weight, m.in_proj_z.weight, m.in_proj_b.weight, m.in_proj_a.weight)
+        qkv = _ConvSilu.apply(p_qkv, m.conv1d.weight)
+        beta, g = _GdnGates.apply(p_b, p_a, m.A_log, m.dt_bias)
         if self.hybrid_delta_rule:
             q, k, v = qkv.split([m.key_dim, m.key_dim, m.value_dim], dim=-1)
             o = self.delta_rule(q.reshape(B, S, -1, 64), k.reshape(B, S, -1, 64), v.reshape(B, S, -1, 64), g, beta)
@@ -752,15 +797,16 @@ class Backend:
         hd = attn.head_dim
         if x.dtype != torch.bfloat16 or hd != 64 or S % 64 or S > 8192 or (indexer is not None and (indexer.d_ih != 64 or indexer.n_ih > 4)):
             return None
-        qg = self.linear(x, attn.q_proj.weight).view(B, S, -1, 2 * hd)
+        p_q, p_k, p_v = self.linears(x, attn.q_proj.weight, attn.k_proj.weight, attn.v_proj.weight)
+        qg = p_q.view(B, S, -1, 2 * hd)
         if cos.shape[-1] == 16:
             q, gate = _head_prep(qg, attn.q_norm, cos, sin)
-            k = _head_prep(self.linear(x, attn.k_proj.weight).view(B, S, -1, hd), attn.k_norm, cos, sin)[0]
+            k = _head_prep(p_k.view(B, S, -1, hd), attn.k_norm, cos, sin)[0]
         else:
             q, gate = qg[..., :hd], qg[..., hd:].reshape(B, S, -1)
             q = modeling.apply_rope(attn.q_norm(q).transpose(1, 2), cos, sin).contiguous()
-            k = modeling.apply_rope(attn.k_norm(self.linear(x, attn.k_proj.weight).view(B, S, -1, hd)).transpose(1, 2), cos, sin).contiguous()
-        v = self.linear(x, attn.v_proj.weight).view(B, S, -1, hd).transpose(1, 2)
+            k = modeling.apply_rope(attn.k_norm(p_k.view(B, S, -1, hd)).transpose(1, 2), cos, sin).contiguous()
+        v = p_v.view(B, S, -1, hd).transpose(1, 2)
         kl = lp_blk = None
         if indexer is not None and (want_kl or not dense):
             if want_kl:
@@ -801,8 +847,10 @@ class Backend:
         else:
             eos = -1 if m.eos_id is None else int(m.eos_id)
             e = _NGramEmbed.apply(ids, w2, w3, m.norm.weight, int(m.vocab), eos, float(m.norm.eps if m.norm.eps is not None else 1e-6))
-        gate = torch.sigmoid(self.linear(h, m.gate.weight) + m.gate.bias.to(h.dtype))
-        return gate * e
+        logit = self.linear(h, m.gate.weight) + m.gate.bias.to(h.dtype)
+        if e.dtype == torch.bfloat16 and logit.dtype == torch.bfloat16 and e.shape == logit.shape and e.numel() % 8 == 0:
+            return _SigmoidMul.apply(e, logit)                   # e * sigmoid(logit), one kernel each way
+        return torch.sigmoid(logit) * e
 
     @_nvtx("q38.moe_block")
     def moe_block(self, block, x):
@@ -812,7 +860,8 @@ class Backend:
             return None
         shape = x.shape
         x2 = x.reshape(-1, h)
-        logits = self.linear(x2, block.gate.weight)
+        shared = block.shared_expert
+        logits, sg, su, gate_logit = self.linears(x2, block.gate.weight, shared.gate_proj.weight, shared.up_proj.weight, block.shared_expert_gate.weight)
         top_w, top_idx, prob_sum, counts = _Route.apply(logits, block.gate.top_k)
         if block._recording():
             block.stats_sink.add(counts, prob_sum, x2.shape[0])
@@ -826,10 +875,7 @@ class Backend:
             routed = ExpertsFP8.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj, _bf16_weight, WGRAD_STREAM)
         else:
             routed = _Experts.apply(x2, top_w, top_idx, experts.gate_up_proj, experts.down_proj)
-        shared = block.shared_expert
-        sg, su = self.linear(x2, shared.gate_proj.weight), self.linear(x2, shared.up_proj.weight)
         mid = _SwiGLU.apply(sg, su) if sg.numel() % 8 == 0 else torch.nn.functional.silu(sg) * su
-        gate_logit = self.linear(x2, block.shared_expert_gate.weight)
         if h % 8 == 0 and gate_logit.shape[1] == 1:
             return _GateAdd.apply(routed, self.linear(mid, shared.down_proj.weight), gate_logit).reshape(shape)
         return (routed + torch.sigmoid(gate_logit) * self.linear(mid, shared.down_proj.weight)).reshape(shape)

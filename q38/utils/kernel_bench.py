@@ -192,6 +192,64 @@ def bench_conv(rows, shape, T, iters, pk, seq=4096):
 BENCHES = dict(gemm=bench_gemm, moe=bench_moe, mhc=bench_mhc, gdn=bench_gdn, qsa=bench_qsa, conv=bench_conv)
 
 
+def bench_fp8(rows, shape, T, iters, pk):
+    """Block-scaled MXFP8 expert products (csrc/mxfp8.cu): quantisation kernels and the grouped mxf8f6f4 GEMM."""
+    from .. import ops
+    h, f, E, k = shape["hidden"], shape["moe_ffn"], shape["experts"], shape["topk"]
+    lib, err = ops.load(), ops.error_flag()
+    P = T * k
+    x = torch.randn(T, h, device="cuda").to(torch.bfloat16)
+    wgu = (0.05 * torch.randn(E, 2 * f, h, device="cuda")).to(torch.bfloat16)
+    wd = (0.05 * torch.randn(E, h, f, device="cuda")).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    perm, inv, offsets, sched = lib.moe_sort(idx, E)
+    t = timeit(lambda: lib.mxfp8_quantize_rows(x, perm, k, sched, P), iters)
+    report(rows, f"mxfp8_quantize_rows (gather) {P}x{h}", t, bytes_=P * h * 3.0 + P * h / 32, pk=pk)
+    xq, sfx = lib.mxfp8_quantize_rows(x, perm, k, sched, P)
+    bn = int(lib.mxfp8_pick_bn(2 * f))
+    t = timeit(lambda: lib.mxfp8_quantize_weight(wgu, bn), iters)
+    report(rows, f"mxfp8_quantize_weight {E}x{2 * f}x{h}", t, bytes_=3.0 * wgu.numel(), pk=pk)
+    q, sf = lib.mxfp8_quantize_weight(wgu, bn)
+    gu = torch.empty(P, 2 * f, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: lib.mxfp8_grouped_gemm(xq, sfx, q, sf, gu, sched, bn, err), iters)
+    report(rows, f"mxfp8_grouped_gemm gate_up {P}x{2 * f}x{h}", t, flops=2.0 * P * 2 * f * h, bytes_=P * h + 2.0 * P * 2 * f + E * 2 * f * h, pk=pk)
+    hmid = torch.randn(P, f, device="cuda").to(torch.bfloat16)
+    hq, sfh = lib.mxfp8_quantize_rows(hmid, None, 1, sched, P)
+    bn = int(lib.mxfp8_pick_bn(h))
+    q, sf = lib.mxfp8_quantize_weight(wd, bn)
+    ys = torch.empty(P, h, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: lib.mxfp8_grouped_gemm(hq, sfh, q, sf, ys, sched, bn, err), iters)
+    report(rows, f"mxfp8_grouped_gemm down {P}x{h}x{f}", t, flops=2.0 * P * h * f, bytes_=P * f + 2.0 * P * h + E * h * f, pk=pk)
+
+
+def bench_muon(rows, shape, T, iters, pk):
+    """Fused Muon step (csrc/muon.cu + Newton-Schulz on the persistent GEMM) on the expert matrices of 4 layers."""
+    from .. import ops
+    from ..ops.muon_gpu import FusedMuon
+    h, f, E = shape["hidden"], shape["moe_ffn"], shape["experts"]
+    entries, cursor = [], 0
+    for _ in range(4):
+        for r, c in ((2 * f, h), (h, f)):
+            entries.append((cursor, E, r, c))
+            cursor += E * r * c
+    params, grads, buf = (torch.randn(cursor, device="cuda") for _ in range(3))
+    shadow = torch.zeros(cursor, device="cuda", dtype=torch.bfloat16)
+    plan = FusedMuon(params, grads, buf, shadow, entries)
+    err = ops.error_flag()
+    lib = ops.load()
+    t = timeit(lambda: lib.muon_prepass(grads, buf, plan.work, plan.sumsq, plan.mats, plan.tiles, None, 0.95, err), iters)
+    report(rows, f"muon_prepass {cursor / 1e6:.1f}M elements", t, bytes_=14.0 * cursor, pk=pk)
+    lib.muon_normalize(plan.work, plan.sumsq, plan.mats, plan.tiles, 1e-7, err)
+    t = timeit(lambda: lib.muon_apply(params, shadow, plan.work, plan.mats, plan.tiles, plan.scales, None, 1e-3, 0.1, err), iters)
+    report(rows, f"muon_apply {cursor / 1e6:.1f}M elements", t, bytes_=12.0 * cursor, pk=pk)
+    flops = 0.0
+    for _, n, r, c in entries:
+        m, kk = min(r, c), max(r, c)
+        flops += n * 5 * (4.0 * m * m * kk + 2.0 * m ** 3)
+    t = timeit(lambda: plan.step(1e-3, 0.95, 0.1, err=err), max(3, iters // 4), warmup=2)
+    report(rows, f"muon step (prepass + 5 NS iterations + apply), {len(entries) * E} matrices", t, flops=flops, bytes_=26.0 * cursor, pk=pk)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--preset", default="q38_c2")
@@ -207,6 +265,7 @@ def main(argv=None):
     pk = peaks()
     rows = []
     torch.manual_seed(0)
+    BENCHES.update(fp8=bench_fp8, muon=bench_muon)
     for name in a.kernels.split(","):
         BENCHES[name](rows, shape, a.tokens, a.iters, pk)
     ops.check_errors()
