@@ -653,6 +653,7 @@ class Backend:
         # True: no atomically accumulated split-K; weight gradients are then bitwise reproducible from run to run
         self.deterministic = bool(int(os.environ.get("Q38_DETERMINISTIC", "0")))
         self.ep = None            # an `ExpertParallel` context when the experts are split over ranks
+        self.selection_override = None   # optional iterator of (count, index) pairs that replaces the block selection (tests)
         self.fp8_ffn = False      # routed experts on block-scaled MXFP8 GEMMs (`q38.ops.fp8`); set by the trainer from --fp8_ffn
         if self_check:
             self._self_check()
@@ -825,7 +826,10 @@ class Backend:
         if dense or indexer is None:
             o = _BlockAttention.apply(q, k, v, None, None, attn.scaling)
         else:
-            count, index = load().qsa_select(lp_blk, budget)
+            if self.selection_override is not None:              # numerics tests: attend to the blocks an fp32 run selected
+                count, index = (t.to(q.device).contiguous() for t in next(self.selection_override))
+            else:
+                count, index = load().qsa_select(lp_blk, budget)
             o = _BlockAttention.apply(q, k, v, count, index, attn.scaling)
         o = o.reshape(B, S, -1)
         o = _SigmoidMul.apply(o, gate) if (o.numel() % 8 == 0 and o.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16) else o * torch.sigmoid(gate)

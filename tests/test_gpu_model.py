@@ -28,8 +28,9 @@ def losses(model, ids, dense):
 
 
 @pytest.mark.parametrize("dense", [True, False])
-def test_backend_matches_cpu_specification(dense):
+def test_backend_matches_cpu_specification(dense, monkeypatch):
     from q38 import ops
+    from q38.models import modeling
     ops.install()
     cfg, cpu_model = build()
     gpu_model = copy.deepcopy(cpu_model).cuda()
@@ -37,24 +38,42 @@ def test_backend_matches_cpu_specification(dense):
     gpu_model.model.compute_dtype = torch.bfloat16
     ids = torch.randint(1, 512, (2, 256))
     ids[0, 100] = 7
+    # In the sparse phase a bf16 score may rank two nearly tied blocks the other way round than fp32 does, which changes what
+    # the attention reads: the kernels are therefore checked on the selection the fp32 run made.
+    selections = []
+    original_select = modeling.select_blocks
+
+    def recording_select(lp_blk, budget):
+        out = original_select(lp_blk, budget)
+        selections.append(tuple(t.detach().clone() for t in out))
+        return out
+
+    monkeypatch.setattr(modeling, "select_blocks", recording_select)
     ref = losses(cpu_model, ids, dense)
-    got = losses(gpu_model, ids.cuda(), dense)
+    monkeypatch.setattr(modeling, "select_blocks", original_select)
+    backend = modeling.get_backend()
+    backend.selection_override = iter(selections) if selections else None
+    try:
+        got = losses(gpu_model, ids.cuda(), dense)
+    finally:
+        backend.selection_override = None
     ops.check_errors()
     for name, r, g in zip(("ce", "aux", "mtp", "kl"), ref, got):
         assert abs(g.item() - r.item()) <= 0.03 * abs(r.item()) + 2e-3, (name, g.item(), r.item())
     (ref[0] + 0.3 * ref[2] + 0.05 * ref[3] + 0.001 * ref[1]).backward()
     (got[0] + 0.3 * got[2] + 0.05 * got[3] + 0.001 * got[1]).backward()
     ops.check_errors()
+    largest = max(p.grad.norm().item() for p in cpu_model.parameters())
     worst = []
     for (name, p), q in zip(cpu_model.named_parameters(), gpu_model.parameters()):
         assert q.grad is not None and torch.isfinite(q.grad).all(), name
         denom = p.grad.norm().item()
-        if denom > 1e-6:
+        if denom > 1e-4 * largest:            # gradients far below the largest one are cancellation noise even in fp32
             worst.append(((q.grad.cpu().float() - p.grad).norm().item() / denom, name))
     worst.sort(reverse=True)
-    # bf16 activations against an fp32 oracle: gradients agree in direction and scale
-    assert worst[0][0] < 0.35, worst[:5]
-    assert sum(w for w, _ in worst) / len(worst) < 0.08, worst[:5]
+    # bf16 activations against an fp32 oracle, per parameter: relative error of the gradient in Frobenius norm
+    assert worst[0][0] < 0.1, worst[:6]
+    assert sum(w for w, _ in worst) / len(worst) < 0.03, (sum(w for w, _ in worst) / len(worst), worst[:6])
 
 
 def test_public_training_step_reduces_loss():
