@@ -185,7 +185,7 @@ def main():
                        "train_flops_per_token": fc["train_flops_per_token"]},
             "mfu_of_measured_sustained_peak": value * fc["train_flops_per_token"] / (world * peak_tflops * 1e12),
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 5 * 4},
-            "gpu_launches": launches, "clocks": clocks.summary(), "losses_last_step": last, "losses_last_step_e2e": last_host,
+            "gpu_launches": launches, "peak_mem_gib": round(torch.cuda.max_memory_allocated(dev) / 2**30, 2), "clocks": clocks.summary(), "losses_last_step": last, "losses_last_step_e2e": last_host,
             "backend": modeling_backend_report(), "timed_wall_s": wall, "finish_step_phase_ms": phases, **comm,
         }), flush=True)
     trainer.close()

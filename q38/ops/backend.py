@@ -720,6 +720,11 @@ class Backend:
 
     def linears(self, x, *weights):
         """Projections of one input by several weights (tuple of outputs); their input gradients are summed inside the GEMMs."""
+        # Default: one autograd node per projection and autograd's own additions of the input gradients.  Q38_MULTI_LINEAR=1
+        # sums them in the GEMM epilogue instead; measured 1 % slower on q38_c2 (745 vs 737 ms per step): the epilogue reads the
+        # running sum row by row, which costs more than a separate, fully coalesced addition kernel saves.
+        if os.environ.get("Q38_MULTI_LINEAR", "0") != "1":
+            return tuple(self.linear(x, w) for w in weights)
         return _MultiLinear.apply(x, self, *weights)
 
     def rmsnorm(self, x, weight, eps, out_dtype):
