@@ -58,6 +58,8 @@ TORCH_LIBRARY(q38, m) {
   m.def("adamw_flat(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor? shadow, Tensor? grad_scale, int step, float lr, float wd, float beta1, float beta2, float eps, Tensor? hyper, Tensor? err=None) -> ()");
   m.def("sum_squares(Tensor x) -> Tensor");
   m.def("qsa_main_block_stats(Tensor q, Tensor k, float scale) -> Tensor");
+  m.def("qsa_block_stats_tc(Tensor q, Tensor k, float scale, Tensor(a!) err) -> Tensor",
+        [](const at::Tensor& q, const at::Tensor& k, double scale, at::Tensor& err) { return q38::qsa_block_stats_tc(q, k, scale, err); });
   m.def("qsa_indexer_fwd(Tensor qi, Tensor ki, Tensor wi, float scale) -> Tensor");
   m.def("qsa_kl_combine(Tensor? stats, Tensor blse, int nq) -> Tensor[]");
   m.def("qsa_select(Tensor lp_blk, int budget) -> Tensor[]");

@@ -117,6 +117,8 @@ std::vector<at::Tensor> qsa_kl_combine(const c10::optional<at::Tensor>& stats, c
 std::vector<at::Tensor> qsa_select(const at::Tensor& lp_blk, int64_t budget);
 std::vector<at::Tensor> qsa_indexer_bwd(const at::Tensor& qi, const at::Tensor& ki, const at::Tensor& wi, const at::Tensor& blse, const at::Tensor& dblse,
                                         double gscale, double scale);
+// qsa_tc.cu
+at::Tensor qsa_block_stats_tc(const at::Tensor& q, const at::Tensor& k, double scale, at::Tensor& err);
 // qsa_attn.cu
 std::vector<at::Tensor> qsa_attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const c10::optional<at::Tensor>& count,
                                      const c10::optional<at::Tensor>& index, double scale);

@@ -108,7 +108,22 @@ __global__ void __launch_bounds__(MUON_THREADS) muon_apply_kernel(float* __restr
   float* p = params + off + first;
   const __nv_bfloat16* x = work + woff + first;
   __nv_bfloat16* s = shadow ? shadow + off + first : nullptr;
-  for (int i = threadIdx.x; i < count; i += MUON_THREADS) {
+  const bool vec = (((off + first) | (woff + first)) & 3) == 0;
+  const int n4 = vec ? (count >> 2) : 0;
+  for (int i = threadIdx.x; i < n4; i += MUON_THREADS) {
+    float4 v = reinterpret_cast<float4*>(p)[i];
+    const uint2 raw = reinterpret_cast<const uint2*>(x)[i];
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v.x = v.x * decay - step * lo.x; v.y = v.y * decay - step * lo.y; v.z = v.z * decay - step * hi.x; v.w = v.w * decay - step * hi.y;
+    reinterpret_cast<float4*>(p)[i] = v;
+    if (s) {
+      const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<const uint32_t*>(&a); packed.y = *reinterpret_cast<const uint32_t*>(&b);
+      reinterpret_cast<uint2*>(s)[i] = packed;
+    }
+  }
+  for (int i = (n4 << 2) + threadIdx.x; i < count; i += MUON_THREADS) {
     const float v = p[i] * decay - step * __bfloat162float(x[i]);
     p[i] = v;
     if (s) s[i] = __float2bfloat16_rn(v);

@@ -379,7 +379,10 @@ class _IndexerKL(torch.autograd.Function):
     @staticmethod
     def forward(ctx, qi, ki, wi, q_main, k_main, main_scale, idx_scale):
         ops = load()
-        stats = ops.qsa_main_block_stats(q_main, k_main, main_scale)
+        if q_main.shape[2] % 128 == 0 and q_main.is_contiguous() and k_main.is_contiguous() and os.environ.get("Q38_QSA_TC", "1") != "0":
+            stats = ops.qsa_block_stats_tc(q_main, k_main, main_scale, error_flag(q_main.device))      # tcgen05 kernel (csrc/qsa_tc.cu)
+        else:
+            stats = ops.qsa_main_block_stats(q_main, k_main, main_scale)
         blse = ops.qsa_indexer_fwd(qi, ki, wi, idx_scale)
         P, lp_blk, kl_tok, dblse = ops.qsa_kl_combine(stats, blse, q_main.shape[1])
         ctx.save_for_backward(qi, ki, wi, blse, dblse)

@@ -161,6 +161,11 @@ def bench_qsa(rows, shape, T, iters, pk, seq=4096):
     causal_tiles = B * (seq // 64) * (seq // 64 + 1) // 2
     t = timeit(lambda: lib.qsa_main_block_stats(q, k, 0.125), iters)
     report(rows, f"qsa_main_block_stats B={B} nq={nq}", t, flops=nq * causal_tiles * 2.0 * 64 ** 3, bytes_=8.0 * B * nq * seq * (seq // 64) / 2, pk=pk)
+    if seq % 128 == 0:
+        from .. import ops as ops_module
+        err = ops_module.error_flag()
+        t = timeit(lambda: lib.qsa_block_stats_tc(q, k, 0.125, err), iters)
+        report(rows, f"qsa_block_stats_tc (tcgen05) B={B} nq={nq}", t, flops=nq * causal_tiles * 2.0 * 64 ** 3, bytes_=8.0 * B * nq * seq * (seq // 64) / 2, pk=pk)
     qi = torch.randn(B, 4, seq, 64, device="cuda").to(torch.bfloat16)
     ki = torch.randn(B, seq, 64, device="cuda").to(torch.bfloat16)
     wi = torch.rand(B, seq, 4, device="cuda")

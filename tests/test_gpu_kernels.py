@@ -652,3 +652,26 @@ def test_cross_entropy_kernel_with_ignored_rows(ops):
         grad_ref[~valid] = 0.0
         assert (work.float() - grad_ref).abs().max() < 1e-2
         assert work[~valid].abs().max() == 0                  # ignored rows contribute neither loss nor gradient
+
+
+@pytest.mark.parametrize("B,S,nq,nkv", [(1, 128, 2, 1), (2, 512, 6, 2), (1, 1024, 22, 2), (1, 384, 4, 2)])
+def test_block_statistics_on_tcgen05_match_fp32(ops, B, S, nq, nkv):
+    """Per (query, key block) max and sum-exp of the main attention scores from the tcgen05 kernel against an fp32 evaluation
+    and against the warp-MMA kernel it replaces."""
+    torch.manual_seed(35)
+    q = (2.0 * torch.randn(B, nq, S, 64, device="cuda")).to(torch.bfloat16)
+    k = torch.randn(B, nkv, S, 64, device="cuda").to(torch.bfloat16)
+    lib = ops.load()
+    got = lib.qsa_block_stats_tc(q, k, 0.125, ops.error_flag(q.device))
+    old = lib.qsa_main_block_stats(q, k, 0.125)
+    ops.check_errors()
+    nb = S // 64
+    scores = (q.float() @ k.float().repeat_interleave(nq // nkv, 1).transpose(-1, -2)) * 0.125
+    pos = torch.arange(S, device="cuda")
+    scores = scores.masked_fill(pos[None, :] > pos[:, None], float("-inf")).view(B, nq, S, nb, 64)
+    ref_max = scores.max(-1).values
+    ref_sum = (scores - ref_max.clamp_min(-1e30)[..., None]).exp().sum(-1)
+    causal = (torch.arange(nb, device="cuda")[None, :] <= (pos // 64)[:, None]).expand(B, nq, S, nb)
+    for name, stats in (("tcgen05", got), ("warp", old)):
+        assert (stats[..., 0] - ref_max)[causal].abs().max() < 2e-3, name
+        assert ((stats[..., 1] - ref_sum)[causal].abs() / ref_sum[causal]).max() < 2e-3, name
