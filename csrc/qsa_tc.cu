@@ -19,7 +19,7 @@
 
 namespace q38 {
 
-constexpr int QT_ROWS = 128, QT_KEYS = 256, QT_STAGES = 2, QT_THREADS = 192;
+constexpr int QT_ROWS = 128, QT_KEYS = 256, QT_STAGES = 2, QT_THREADS = 320;     // TMA warp, MMA warp, two epilogue warpgroups
 
 struct QsaTcArgs {
   float2* stats;
@@ -99,37 +99,53 @@ __global__ void __launch_bounds__(QT_THREADS) qsa_block_stats_tc_kernel(const __
       }
     }
   } else {
-    const int quarter = warp & 3, r = quarter * 32 + lane;
+    // Two epilogue warpgroups (warps 2-5 and 6-9): group g is read out by warpgroup g & 1, which owns accumulator g & 1, so two
+    // groups' exponentials are in flight per SM.  A warp may read the TMEM lanes 32 (warp % 4) .. + 31.
+    const int wg = (warp - 2) >> 2, quarter = warp & 3, r = quarter * 32 + lane;
     const int t = row0 + r, own = t >> 6, tin = t & 63;
     float2* out_row = p.stats + ((long long)q_batch * p.S + t) * p.nb;
     const float c = p.scale * 1.4426950408889634f;            // scores to log2 units
     bool ok = true;
-    for (int g = 0; g < groups && ok; ++g) {
+    for (int g = wg; g < groups && ok; g += 2) {
       const int acc = g & 1;
       if (!ptx::mbar_wait(&acc_full[acc], (g >> 1) & 1, 1u << 22)) { report_error(p.err, ERR_EPILOGUE_WAIT); ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t t_addr = tmem_base + acc * QT_KEYS + (uint32_t(quarter * 32) << 16);
+      uint32_t nxt_lo[32], nxt_hi[32];
+      ptx::tmem_ld_32x32b_x32(t_addr, nxt_lo);
+      ptx::tmem_ld_32x32b_x32(t_addr + 32, nxt_hi);
 #pragma unroll 1
       for (int jb4 = 0; jb4 < 4; ++jb4) {
         const int jb = g * 4 + jb4;
-        uint32_t lo[32], hi[32];
-        ptx::tmem_ld_32x32b_x32(t_addr + jb4 * 64, lo);
-        ptx::tmem_ld_32x32b_x32(t_addr + jb4 * 64 + 32, hi);
+        float v[64];
         ptx::tmem_ld_wait();
-        if (jb > own) continue;                              // a key block after the query's own block: not causal, never read
-        const int limit = jb == own ? tin : 63;              // last visible key of the block
-        float m = -INFINITY;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          if (e <= limit) m = fmaxf(m, __uint_as_float(lo[e]));
-          if (e + 32 <= limit) m = fmaxf(m, __uint_as_float(hi[e]));
+        for (int e = 0; e < 32; ++e) { v[e] = __uint_as_float(nxt_lo[e]); v[32 + e] = __uint_as_float(nxt_hi[e]); }
+        if (jb4 < 3) {                                       // the next block's columns load while this block is reduced
+          ptx::tmem_ld_32x32b_x32(t_addr + (jb4 + 1) * 64, nxt_lo);
+          ptx::tmem_ld_32x32b_x32(t_addr + (jb4 + 1) * 64 + 32, nxt_hi);
         }
-        float sum = 0.f;
-        const float mc = m * c;
+        if (jb > own) continue;                              // a key block after the query's own block: not causal, never read
+        float m, sum = 0.f;
+        if (jb < own) {                                      // every key of the block is visible
+          float m0 = v[0], m1 = v[1], m2 = v[2], m3 = v[3];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          if (e <= limit) sum += fast_exp2(__uint_as_float(lo[e]) * c - mc);
-          if (e + 32 <= limit) sum += fast_exp2(__uint_as_float(hi[e]) * c - mc);
+          for (int e = 4; e < 64; e += 4) { m0 = fmaxf(m0, v[e]); m1 = fmaxf(m1, v[e + 1]); m2 = fmaxf(m2, v[e + 2]); m3 = fmaxf(m3, v[e + 3]); }
+          m = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+          const float mc = m * c;
+          float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+          for (int e = 0; e < 64; e += 4) {
+            s0 += fast_exp2(v[e] * c - mc); s1 += fast_exp2(v[e + 1] * c - mc); s2 += fast_exp2(v[e + 2] * c - mc); s3 += fast_exp2(v[e + 3] * c - mc);
+          }
+          sum = (s0 + s1) + (s2 + s3);
+        } else {                                             // the diagonal block: keys up to the query's own position
+          m = -INFINITY;
+#pragma unroll
+          for (int e = 0; e < 64; ++e) if (e <= tin) m = fmaxf(m, v[e]);
+          const float mc = m * c;
+#pragma unroll
+          for (int e = 0; e < 64; ++e) if (e <= tin) sum += fast_exp2(v[e] * c - mc);
         }
         out_row[jb] = make_float2(m * p.scale, sum);
       }
