@@ -356,6 +356,9 @@ class Trainer:
             backend.ep = None
         if backend is not None:
             backend.fp8_ffn = False
+            if self.dev.type == "cuda":
+                from .ops import fp8
+                fp8.drop_weights()
         self._graphs = {}
         self.engine.close()
 
@@ -422,6 +425,10 @@ class Trainer:
         if lr is not None:
             self.engine.set_lr(lr)
         totals = torch.zeros(4, dtype=torch.float32, device=self.dev)
+        if self.dev.type == "cuda" and getattr(self.a, "fp8_ffn", 0):
+            from .ops import fp8
+            from .ops.backend import _bf16_weight
+            fp8.refresh_weights(self.model, _bf16_weight)          # MXFP8 copies of the expert weights, once per optimizer step
         for i, (x, y) in enumerate(batches):
             self.engine.begin_micro_step(last=i == accum - 1)
             parts = self._captured_micro_step(x, y, accum, dense) if self.use_graphs else None
