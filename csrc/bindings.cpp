@@ -103,6 +103,7 @@ TORCH_LIBRARY(q38, m) {
         });
   m.def("p2p_publish_scalar(Tensor value, int[] peer_slots, int rank) -> ()",
         [](const at::Tensor& v, std::vector<int64_t> slots, int64_t rank) { q38::p2p_publish_scalar(v, slots, rank); });
+  m.def("moe_set_persistent(int mode) -> ()", [](int64_t mode) { q38::moe_set_persistent(mode); });
   m.def("ce_inplace(Tensor(a!) logits, Tensor target) -> Tensor", [](at::Tensor& l, const at::Tensor& t) { return q38::ce_inplace(l, t); });
   m.def("conv_silu_fwd(Tensor x, Tensor w) -> Tensor");
   m.def("conv_silu_bwd(Tensor x, Tensor w, Tensor dy) -> Tensor[]");

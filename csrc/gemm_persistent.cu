@@ -319,7 +319,7 @@ static void launch_p(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
     else if (tma_out) { if (accum) Q38_LAUNCH(float, true, true) else Q38_LAUNCH(float, false, true) }
     else { if (accum) Q38_LAUNCH(float, true, false) else Q38_LAUNCH(float, false, false) }
   } else if (tma_out) {
-    if (!out_fp32) Q38_LAUNCH(__nv_bfloat16, false, true)
+    if (!out_fp32) { if (accum) Q38_LAUNCH(__nv_bfloat16, true, true) else Q38_LAUNCH(__nv_bfloat16, false, true) }
     else if (accum) Q38_LAUNCH(float, true, true)
     else Q38_LAUNCH(float, false, true)
   } else {
@@ -352,9 +352,10 @@ void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& 
   TORCH_CHECK(K == Kb && b.size(0) == batch && c.size(0) == batch && c.size(1) == M && c.size(2) == N, "gemm_bf16_persistent: shape mismatch");
   const bool out_fp32 = c.scalar_type() == at::kFloat;
   TORCH_CHECK(out_fp32 || c.scalar_type() == at::kBFloat16, "gemm_bf16_persistent: output must be bf16 or fp32");
-  TORCH_CHECK(!accumulate || out_fp32, "accumulating epilogue requires an fp32 output");
   const int c_eb = out_fp32 ? 4 : 2, c_vec = 16 / c_eb;
   const bool tma_out = c.stride(1) % c_vec == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15) == 0 && (batch == 1 || c.stride(0) % c_vec == 0);
+  // bf16 outputs accumulate through the TMA unit only (cp.reduce.async.bulk.tensor adds in the tensor's element type)
+  TORCH_CHECK(!accumulate || out_fp32 || (tma_out && !tf32 && !addend.has_value()), "accumulating into a bf16 output requires a TMA-storable output and no addend");
   int bn = pick_bn(N, tma_out ? 32 : 16);
   if (b_mn_major) bn = (bn + 63) / 64 * 64;                    // MN-major B is loaded in 64-wide boxes
   bn = std::min(bn, 256);

@@ -100,6 +100,13 @@ void moe_grouped_swiglu(const at::Tensor& rows, const at::Tensor& weight, at::Te
 void moe_grouped_dswiglu(const at::Tensor& dy, const at::Tensor& w_down, const at::Tensor& gu, at::Tensor& dgu, const at::Tensor& sched, at::Tensor& err);
 void moe_grouped_wgrad(const at::Tensor& a, const at::Tensor& b, at::Tensor& grad, const at::Tensor& offsets, at::Tensor& err);
 
+// moe_persistent.cu
+bool moe_persistent_enabled();
+void moe_set_persistent(int64_t mode);
+void moe_grouped_gemm_p(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err);
+void moe_grouped_swiglu_p(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& hmid, at::Tensor& gu, const at::Tensor& sched, at::Tensor& err);
+void moe_grouped_dswiglu_p(const at::Tensor& dy, const at::Tensor& w_down, const at::Tensor& gu, at::Tensor& dgu, const at::Tensor& sched, at::Tensor& err);
+
 // gdn.cu
 std::vector<at::Tensor> gdn_scan_fwd(const at::Tensor& w, const at::Tensor& u, const at::Tensor& P, const at::Tensor& qg, const at::Tensor& kg,
                                      const at::Tensor& dch, int64_t B, int64_t H);

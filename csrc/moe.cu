@@ -586,6 +586,7 @@ void moe_grouped_gemm_impl(const at::Tensor& rows, const at::Tensor& weight, at:
                            const int* ret_rank, const int* ret_row, const std::vector<int64_t>& peer_out);
 
 void moe_grouped_gemm(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& out, const at::Tensor& sched, bool b_mn_major, at::Tensor& err) {
+  if (moe_persistent_enabled()) return moe_grouped_gemm_p(rows, weight, out, sched, b_mn_major, err);      // persistent kernel (moe_persistent.cu)
   moe_grouped_gemm_impl(rows, weight, out, sched, b_mn_major, err, nullptr, nullptr, {});
 }
 
@@ -623,6 +624,7 @@ void moe_grouped_gemm_impl(const at::Tensor& rows, const at::Tensor& weight, at:
 
 // rows [P, h], gate_up weight [E, 2f, h] -> hmid [P, f], gu [P, 2f]
 void moe_grouped_swiglu(const at::Tensor& rows, const at::Tensor& weight, at::Tensor& hmid, at::Tensor& gu, const at::Tensor& sched, at::Tensor& err) {
+  if (moe_persistent_enabled()) return moe_grouped_swiglu_p(rows, weight, hmid, gu, sched, err);
   check_bf16_2d(rows, "moe_grouped_swiglu rows"); check_bf16_2d(hmid, "hmid"); check_bf16_2d(gu, "gu");
   const c10::cuda::CUDAGuard guard(rows.device());
   const int P = rows.size(0), K = rows.size(1), E = weight.size(0), f = weight.size(1) / 2;
@@ -638,6 +640,7 @@ void moe_grouped_swiglu(const at::Tensor& rows, const at::Tensor& weight, at::Te
 
 // d(hmid) = dy_sorted [P, h] . W_down[e] ([h, f], MN-major B), fused SwiGLU backward -> dgu [P, 2f]
 void moe_grouped_dswiglu(const at::Tensor& dy, const at::Tensor& w_down, const at::Tensor& gu, at::Tensor& dgu, const at::Tensor& sched, at::Tensor& err) {
+  if (moe_persistent_enabled()) return moe_grouped_dswiglu_p(dy, w_down, gu, dgu, sched, err);
   check_bf16_2d(dy, "dy"); check_bf16_2d(gu, "gu"); check_bf16_2d(dgu, "dgu");
   const c10::cuda::CUDAGuard guard(dy.device());
   const int P = dy.size(0), K = dy.size(1), E = w_down.size(0), f = w_down.size(2);

@@ -86,6 +86,8 @@ class _MultiLinear(torch.autograd.Function):
                 w = _bf16_weight(weight)
                 if dx is None:
                     dx = backend.mm_nn(dy2, w)
+                elif w.shape[1] % 8 == 0 and backend.layouts["nn"] and os.environ.get("Q38_MULTI_LINEAR") == "2":
+                    gemm(_tma_rows(dy2), w, out=dx, b_mn_major=True, accumulate=True)          # dx += dy_i W_i: the TMA unit adds the tile
                 elif w.shape[1] % 8 == 0 and backend.layouts["nn"]:
                     dx = gemm(_tma_rows(dy2), w, b_mn_major=True, addend=dx, beta=1.0)        # dx <- dy_i W_i + dx, one kernel
                 else:
@@ -726,7 +728,7 @@ class Backend:
         # Default: one autograd node per projection and autograd's own additions of the input gradients.  Q38_MULTI_LINEAR=1
         # sums them in the GEMM epilogue instead; measured 1 % slower on q38_c2 (745 vs 737 ms per step): the epilogue reads the
         # running sum row by row, which costs more than a separate, fully coalesced addition kernel saves.
-        if os.environ.get("Q38_MULTI_LINEAR", "0") != "1":
+        if os.environ.get("Q38_MULTI_LINEAR", "0") not in ("1", "2"):
             return tuple(self.linear(x, w) for w in weights)
         return _MultiLinear.apply(x, self, *weights)
 

@@ -244,6 +244,47 @@ def test_moe_block_matches_specification(ops, T, h, f, E, k):
         assert rel_err(pa[name], pb[name]) < 5e-2, name
 
 
+@pytest.mark.parametrize("T,h,f,E,k", [(700, 128, 32, 8, 2), (4096, 576, 144, 64, 5), (3000, 320, 208, 16, 3)])
+def test_persistent_grouped_kernels_match_the_one_tile_kernels(ops, T, h, f, E, k):
+    """The persistent grouped expert GEMM (one CTA per SM, two TMEM accumulator sets) against the one-tile-per-CTA kernels and
+    against an fp32 per-expert product, for the three epilogues."""
+    raw = ops.load()
+    torch.manual_seed(31)
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    perm, inv, offsets, sched = raw.moe_sort(idx, E)[:4]
+    P = T * k
+    rows = torch.randn(P, h, device="cuda").to(torch.bfloat16)
+    wgu = (0.05 * torch.randn(E, 2 * f, h, device="cuda")).to(torch.bfloat16)
+    wd = (0.05 * torch.randn(E, h, f, device="cuda")).to(torch.bfloat16)
+    dy = torch.randn(P, h, device="cuda").to(torch.bfloat16)
+    err = ops.error_flag()
+    got = {}
+    try:
+        for mode in (1, 0):
+            raw.moe_set_persistent(mode)
+            hmid = torch.zeros(P, f, device="cuda", dtype=torch.bfloat16); gu = torch.zeros(P, 2 * f, device="cuda", dtype=torch.bfloat16)
+            raw.moe_grouped_swiglu(rows, wgu, hmid, gu, sched, err)
+            y = torch.zeros(P, h, device="cuda", dtype=torch.bfloat16)
+            raw.moe_grouped_gemm(hmid, wd, y, sched, False, err)
+            dgu = torch.zeros(P, 2 * f, device="cuda", dtype=torch.bfloat16)
+            raw.moe_grouped_dswiglu(dy, wd, gu, dgu, sched, err)
+            dx = torch.zeros(P, h, device="cuda", dtype=torch.bfloat16)
+            raw.moe_grouped_gemm(dgu, wgu, dx, sched, True, err)
+            got[mode] = (hmid, gu, y, dgu, dx)
+    finally:
+        raw.moe_set_persistent(-1)
+    ops.check_errors()
+    for a, b, name in zip(got[1], got[0], ("hmid", "gu", "y", "dgu", "dx")):
+        assert rel_err(a, b) < 1e-6, name
+    off = offsets.tolist()
+    ref_gu = torch.zeros(P, 2 * f, device="cuda")
+    for e in range(E):
+        ref_gu[off[e]:off[e + 1]] = rows[off[e]:off[e + 1]].float() @ wgu[e].float().T
+    assert rel_err(got[1][1], ref_gu) < 1e-2
+    ref_h = torch.nn.functional.silu(ref_gu[:, :f]) * ref_gu[:, f:]
+    assert rel_err(got[1][0], ref_h) < 2e-2
+
+
 def test_moe_weight_gradients_accumulate_in_place(ops):
     from q38.ops.backend import _Experts
     torch.manual_seed(11)
@@ -675,3 +716,15 @@ def test_block_statistics_on_tcgen05_match_fp32(ops, B, S, nq, nkv):
     for name, stats in (("tcgen05", got), ("warp", old)):
         assert (stats[..., 0] - ref_max)[causal].abs().max() < 2e-3, name
         assert ((stats[..., 1] - ref_sum)[causal].abs() / ref_sum[causal]).max() < 2e-3, name
+
+
+def test_gemm_accumulates_into_bf16_output(ops):
+    """`out += A B^T` with a bf16 output: the epilogue hands the tile to the TMA unit, which adds it in bf16."""
+    torch.manual_seed(36)
+    a = (0.1 * torch.randn(1000, 288, device="cuda")).to(torch.bfloat16)
+    w = (0.1 * torch.randn(288, 576, device="cuda")).to(torch.bfloat16)            # [K, N]: MN-major B, as in an input-gradient product
+    out = torch.randn(1000, 576, device="cuda").to(torch.bfloat16)
+    before = out.clone()
+    ops.gemm(a, w, out=out, b_mn_major=True, accumulate=True)
+    ref = before.float() + a.float() @ w.float()
+    assert rel_err(out, ref) < 1e-2
