@@ -3,19 +3,27 @@
 One architecture rule maps a hidden width on the 64-grid to every other dimension; the compute budget
 fixes the global batch (DeepSeek-style power law rounded to a power-of-two number of sequences), the
 learning rate ``0.3118 * C**-0.125`` and, with 0.5 % of the budget held back, the whole-batch token count.
-The widths per budget are pinned (448 / 576 / 768 / 1024): the reference selected them by fitting its
-Q35 IsoFLOPs runs (scripts/make_q38_configs.py:81-148), data that is not part of this repository, so
-this generator reproduces the rule and the accounting, not the fit.
+The width per budget comes from the Q35 IsoFLOPs sweep (``configs/q35_isoflops/results.json``, 19 completed
+runs): per sweep budget a parabola of bits-per-byte over log10(active parameters) gives the optimal model and
+data size, two power laws in the compute extrapolate them to the four Q38 budgets, and of all widths on the
+64-grid the one whose (active parameters, tokens) lies nearest the prediction in log distance is taken -
+448 / 576 / 768 / 1024 (the reference does the same in scripts/make_q38_configs.py:46-110; the fitted slopes
+0.777 and 0.436 and the chosen widths are checked in tests/test_accounting.py).  The Q35 prior transfers to a
+different architecture and, beyond 3e17, extrapolates: it selects a starting point, it predicts no Q38 loss.
 """
 import argparse
 import json
 import math
+from functools import lru_cache
+
+import numpy as np
 
 from .flops import count, sparse_keys_per_query
-from .presets import CKPT_ROOT, MODEL_DEFAULTS, PRESET_DIR, budget_tokens, model_config
+from .presets import CKPT_ROOT, MODEL_DEFAULTS, PRESET_DIR, ROOT, budget_tokens, model_config
 
 SEQ, VOCAB, RESERVE = 4096, 10112, 0.005
-BUDGETS = {"c1": (3e17, 448), "c2": (1e18, 576), "c3": (3e18, 768), "c4": (1e19, 1024)}
+BUDGETS = {"c1": 3 * 10 ** 17, "c2": 10 ** 18, "c3": 3 * 10 ** 18, "c4": 10 ** 19}
+SWEEP_RESULTS = ROOT / "configs" / "q35_isoflops" / "results.json"
 POOL = "/home/shared/qwen35_moe_sparse/cache/isoflops-gzy10k-16b-v1"
 # Frozen validation partitions of the shared pool: (offset, targets) of the dev and the final curve split.
 DEV_SPLIT, FINAL_SPLIT = (0, 2002535), (2002536, 16001875)
@@ -34,6 +42,65 @@ def batch_for(compute):
     return SEQ * max(8, 2 ** round(math.log2(0.2920 * compute ** 0.3271 / SEQ)))
 
 
+def fit_sweep(rows):
+    """Scaling prior from completed IsoFLOPs runs.
+
+    ``rows``: dicts with budget, compute, active_params, train_tokens, bpb.  Per budget (three or more runs) the loss is fitted
+    as a parabola in x = log10(active parameters); its vertex is the optimal size, and the tokens at that size are read from a
+    polynomial of log10(tokens) over x through the same runs.  Returns (per-budget fits, line of log10 N_opt over log10 C,
+    line of log10 D_opt over log10 C, leave-one-budget-out slopes with the size each predicts at 1e19 FLOPs).
+    """
+    fits = []
+    for budget in sorted({r["budget"] for r in rows}, key=float):
+        runs = sorted((r for r in rows if r["budget"] == budget), key=lambda r: r["active_params"])
+        if len(runs) < 3:
+            raise ValueError(f"budget {budget}: a parabola needs three completed runs, found {len(runs)}")
+        x, y = np.log10([r["active_params"] for r in runs]), np.array([r["bpb"] for r in runs])
+        curve = np.polyfit(x, y, 2)
+        if curve[0] <= 0:
+            raise ValueError(f"budget {budget}: the fitted parabola has no minimum")
+        x_opt = -curve[1] / (2 * curve[0])
+        tokens_curve = np.polyfit(x, np.log10([r["train_tokens"] for r in runs]), min(2, len(runs) - 1))
+        fits.append(dict(budget=budget, compute=float(np.mean([r["compute"] for r in runs])), parabola=curve.tolist(),
+                         active_opt=float(10 ** x_opt), tokens_opt=float(10 ** np.polyval(tokens_curve, x_opt)),
+                         bpb_opt=float(np.polyval(curve, x_opt)), inside_grid=bool(x.min() <= x_opt <= x.max()),
+                         residual_rmse=float(np.sqrt(np.mean((np.polyval(curve, x) - y) ** 2))),
+                         measured_best=min(runs, key=lambda r: r["bpb"])["model"]))
+    log_c = np.log10([f["compute"] for f in fits])
+    log_n, log_d = np.log10([f["active_opt"] for f in fits]), np.log10([f["tokens_opt"] for f in fits])
+    size_law, data_law = np.polyfit(log_c, log_n, 1), np.polyfit(log_c, log_d, 1)
+    left_out = []
+    for i, f in enumerate(fits):
+        keep = [j for j in range(len(fits)) if j != i]
+        law = np.polyfit(log_c[keep], log_n[keep], 1)
+        left_out.append(dict(omitted_budget=f["budget"], active_exponent=float(law[0]), c4_active_prediction=float(10 ** np.polyval(law, 19))))
+    return fits, size_law, data_law, left_out
+
+
+@lru_cache(maxsize=None)
+def sweep_prior():
+    return fit_sweep(json.loads(SWEEP_RESULTS.read_text())["runs"])
+
+
+def ranked_widths(compute, batch):
+    """Every admissible width on the 64-grid with its ledger, nearest the prior's (N_opt, D_opt) for `compute` first."""
+    _, size_law, data_law, _ = sweep_prior()
+    n_target, d_target = 10 ** np.polyval(size_law, math.log10(compute)), 10 ** np.polyval(data_law, math.log10(compute))
+    ranked = []
+    for hidden in range(128, 1601, 64):
+        shape = shape_for(hidden)
+        cfg = model_config(shape, VOCAB, SEQ)
+        shape["ngram_rows"] = cfg.ngram_rows
+        ledger = count(cfg.to_dict(), SEQ)
+        tokens = budget_tokens(ledger["train_flops_per_token"], int(compute * (1 - RESERVE)), batch)
+        if tokens == 0 or ledger["active_nonvocab_params"] / ledger["total_nonvocab_params"] <= 0.10:
+            continue
+        distance = math.log(ledger["active_nonvocab_params"] / n_target) ** 2 + math.log(tokens / d_target) ** 2
+        ranked.append(dict(distance=distance, hidden=hidden, shape=shape, ledger=ledger, tokens=tokens))
+    ranked.sort(key=lambda r: r["distance"])
+    return ranked, float(n_target), float(d_target)
+
+
 def omitted_bounds(shape, ledger, steps, warmup):
     """Upper bounds on work the ledger leaves out: dense warm-up attention and mHC pointwise/Sinkhorn math."""
     h, L, n = shape["hidden"], shape["layers"], shape["n_branch"]
@@ -49,14 +116,10 @@ def omitted_bounds(shape, ledger, steps, warmup):
 
 
 def build(name):
-    compute, hidden = BUDGETS[name]
-    compute = int(compute)
-    shape = shape_for(hidden)
-    cfg = model_config(shape, VOCAB, SEQ)
-    shape["ngram_rows"] = cfg.ngram_rows
-    ledger = count(cfg.to_dict(), SEQ)
+    compute = BUDGETS[name]
     batch = batch_for(compute)
-    tokens = budget_tokens(ledger["train_flops_per_token"], int(compute * (1 - RESERVE)), batch)
+    best = ranked_widths(compute, batch)[0][0]
+    shape, ledger, tokens = best["shape"], best["ledger"], best["tokens"]
     steps = tokens // batch
     warmup = min(steps, max(10, round(steps * 0.01)))
     train = dict(run_dir=str(CKPT_ROOT / name), data=f"{POOL}/train.bin", val_data=f"{POOL}/valid.bin",
@@ -91,7 +154,23 @@ def build(name):
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--check", action="store_true", help="recompute and compare with the files on disk")
+    ap.add_argument("--plan", default="", help="also write the scaling fit behind the widths (per-budget optima, power laws, leave-one-out, targets) to this JSON file")
     a = ap.parse_args(argv)
+    if a.plan:
+        fits, size_law, data_law, left_out = sweep_prior()
+        targets = {}
+        for name, compute in BUDGETS.items():
+            ranked, n_target, d_target = ranked_widths(compute, batch_for(compute))
+            targets[name] = dict(compute=compute, active_target=n_target, tokens_target=d_target,
+                                 nearest_widths=[dict(hidden=r["hidden"], log_distance_squared=r["distance"]) for r in ranked[:3]])
+        plan = dict(source=str(SWEEP_RESULTS.relative_to(ROOT)), budget_fits=fits,
+                    power_laws=dict(active_log10_slope=float(size_law[0]), active_log10_intercept=float(size_law[1]),
+                                    tokens_log10_slope=float(data_law[0]), tokens_log10_intercept=float(data_law[1])),
+                    leave_one_budget_out=left_out, targets=targets,
+                    limitations=["The Q35 sweep is a prior for a different architecture.", "Only c1 lies at a measured budget; c2-c4 extrapolate.",
+                                 "No Q38 loss is predicted."])
+        with open(a.plan, "w") as f:
+            f.write(json.dumps(plan, indent=2) + "\n")
     for name in BUDGETS:
         preset, path = build(name), PRESET_DIR / f"q38_{name}.json"
         if a.check:

@@ -12,8 +12,12 @@ owner, and inside an owner by optimizer group (Muon matrices, AdamW with decay, 
 * AdamW runs as a flat elementwise kernel over (at most) two contiguous ranges per owner,
 * the parameter all-gather is "rank r publishes segment r".
 
-Ownership balances the estimated Newton-Schulz FLOPs of the Muon matrices first (they dominate the
-optimizer cost) and the byte count of the AdamW tensors second, with a longest-processing-time greedy.
+Ownership balances one estimate of the time a tensor costs its owner after the last micro-step, with a
+longest-processing-time greedy: the Newton-Schulz FLOPs of a Muon matrix at the rate those small products
+reach, plus, for every tensor, the bytes its owner moves for it in the gradient reduce-scatter, the elementwise
+update and the parameter all-gather.  Balancing the Newton-Schulz work alone left the two n-gram tables (AdamW,
+a quarter of the q38_c2 parameters) on two ranks whose segments were twice the mean, and the reduce-scatter and
+the all-gather end when the largest segment is through.
 Muon needs whole matrices, which is why the unit of ownership is a parameter tensor and not a byte range.
 With ``world == 1`` there is a single segment and the layout degenerates to one flat buffer.
 """
@@ -53,19 +57,28 @@ def newton_schulz_flops(shape, steps=5):
     return stack * steps * (4 * m * m * n + 2 * m ** 3)
 
 
+NS_FLOPS_PER_SECOND = 180e12      # measured rate of the batched Newton-Schulz chain on the expert matrices
+LINK_BYTES_PER_SECOND = 770e9      # measured peer-copy bandwidth per direction
+HBM_BYTES_PER_SECOND = 6.5e12
+
+
+def owner_seconds(unit, world):
+    """Estimated time a tensor costs its owner between the last backward and the next forward."""
+    comm = 2 * (world - 1) * 4 / LINK_BYTES_PER_SECOND          # fp32 in from every peer, fp32 out to every peer
+    update = 16 / HBM_BYTES_PER_SECOND                          # parameter, gradient and moments
+    seconds = unit.numel * (comm + update)
+    if unit.group == "muon":
+        seconds += newton_schulz_flops(tuple(unit.param.shape)) / NS_FLOPS_PER_SECOND
+    return seconds
+
+
 def assign_owners(units, world):
-    """Longest-processing-time greedy; deterministic, so every rank derives the same map."""
+    """Longest-processing-time greedy over `owner_seconds`; deterministic, so every rank derives the same map."""
     load = [0.0] * world
-
-    def place(batch, cost):
-        for unit in sorted(batch, key=lambda u: (-cost(u), u.index)):
-            owner = min(range(world), key=lambda r: (load[r], r))
-            unit.owner = owner
-            load[owner] += cost(unit)
-
-    place([u for u in units if u.group == "muon"], lambda u: float(newton_schulz_flops(tuple(u.param.shape))))
-    # AdamW is bandwidth bound: ~16 bytes per element; scale so that it only breaks ties between Muon loads.
-    place([u for u in units if u.group != "muon"], lambda u: 16.0 * u.numel)
+    for unit in sorted(units, key=lambda u: (-owner_seconds(u, world), u.index)):
+        owner = min(range(world), key=lambda r: (load[r], r))
+        unit.owner = owner
+        load[owner] += owner_seconds(unit, world)
     return load
 
 

@@ -185,18 +185,24 @@ class GradEngine:
         """Exposed communication of a step and how close it runs to the NVLink roofline.
 
         Nothing of `finish_step` overlaps with compute, so the exposed communication time is the sum of the reduce-scatter
-        and all-gather phases (barriers included).  Bytes over NVLink per rank: the reduce-scatter reads this rank's segment
-        from every peer, the all-gather writes it to every peer, both in fp32.  `link_gbs` is the measured peer-copy
-        bandwidth per direction."""
+        and all-gather phases (barriers included).  Both phases end when the busiest link direction of any rank is through,
+        so the byte counts are maxima over ranks: the reduce-scatter brings the largest segment in from every peer (with the
+        in-switch reduction the same bytes leave the peers); the all-gather brings every other segment into each rank and
+        sends the largest segment out, once through the switch's multicast or once per peer with plain stores.
+        `link_gbs` is the measured peer-copy bandwidth per direction."""
         times = self.phase_times()
         if self.world == 1 or not times:
             return {"exposed_comm_ms": 0.0, "comm_roofline_fraction": None}
-        s, e = self.arena.segments[self.rank]
-        one_way = (self.world - 1) * (e - s) * 4
+        sizes = [e - s for s, e in self.arena.segments]
+        multicast = "nvls" in self.describe_transport()
+        rs_bytes = (self.world - 1) * max(sizes) * 4
+        ag_bytes = max((sum(sizes) - min(sizes)) * 4, max(sizes) * 4 * (1 if multicast else self.world - 1))
         rs, ag = times.get("reduce_scatter", 0.0), times.get("all_gather", 0.0)
-        frac = lambda ms: round(one_way / (link_gbs * 1e9 * ms * 1e-3), 3) if ms > 0 else None
-        return {"exposed_comm_ms": round(rs + ag, 3), "nvlink_bytes_per_phase": one_way, "reduce_scatter_roofline_fraction": frac(rs),
-                "all_gather_roofline_fraction": frac(ag), "comm_roofline_fraction": frac((rs + ag) / 2) if rs + ag > 0 else None,
+        frac = lambda nbytes, ms: round(nbytes / (link_gbs * 1e9 * ms * 1e-3), 3) if ms > 0 else None
+        return {"exposed_comm_ms": round(rs + ag, 3), "nvlink_bytes_reduce_scatter": rs_bytes, "nvlink_bytes_all_gather": ag_bytes,
+                "largest_segment_over_mean": round(max(sizes) * self.world / max(1, sum(sizes)), 3),
+                "reduce_scatter_roofline_fraction": frac(rs_bytes, rs), "all_gather_roofline_fraction": frac(ag_bytes, ag),
+                "comm_roofline_fraction": frac(rs_bytes + ag_bytes, rs + ag) if rs + ag > 0 else None,
                 "link_gbs_per_direction_measured": link_gbs}
 
     def average_metrics(self, values):

@@ -42,6 +42,25 @@ def test_preset_generator_reproduces_files():
         assert json.loads((ROOT / f"configs/q38_{name}.json").read_text()) == make_configs.build(name)
 
 
+def test_widths_come_from_the_isoflops_fit(tmp_path):
+    """The scaling fit over the 19 completed Q35 runs: slopes and per-budget optima as published with the reference
+    (audits/q38_config_plan.json there), and the nearest width per Q38 budget."""
+    import json
+    from q38 import make_configs
+    fits, size_law, data_law, left_out = make_configs.sweep_prior()
+    assert [f["budget"] for f in fits] == ["1e16", "3e16", "1e17", "3e17"] and all(f["inside_grid"] for f in fits)
+    assert abs(size_law[0] - 0.7767049) < 1e-6 and abs(data_law[0] - 0.4360745) < 1e-6
+    assert abs(fits[0]["active_opt"] - 1651930.3) < 1.0 and abs(fits[3]["tokens_opt"] - 1235554175.5) < 1e3
+    assert abs(left_out[3]["active_exponent"] - 0.8093009) < 1e-6
+    chosen = {name: make_configs.ranked_widths(c, make_configs.batch_for(c))[0][0]["hidden"] for name, c in make_configs.BUDGETS.items()}
+    assert chosen == {"c1": 448, "c2": 576, "c3": 768, "c4": 1024}
+    with pytest.raises(ValueError, match="three completed runs"):
+        make_configs.fit_sweep([dict(budget="1e16", compute=1e16, active_params=1e6 * (i + 1), train_tokens=1e8, bpb=1.4) for i in range(2)])
+    make_configs.main(["--check", "--plan", str(tmp_path / "plan.json")])
+    plan = json.loads((tmp_path / "plan.json").read_text())
+    assert plan["targets"]["c2"]["nearest_widths"][0]["hidden"] == 576
+
+
 def test_backbone_terms():
     c = small()
     r = _count_backbone(c, 8192)
@@ -89,6 +108,30 @@ def test_flops_audit_agrees_with_instantiated_models():
         report = audit(name, 4096)
         assert report["failures"] == [], report["failures"]
         assert report["weight_gemm_flops_per_token"] < report["fwd_flops_per_token"]
+
+
+def test_backbone_ledger_equals_the_pinned_megatron_formula(tmp_path):
+    """Counterpart of the reference's tests/test_flops_audit.py: the hand expansion of the pinned Megatron formula equals the
+    ledger's Megatron component for the 19 archived configs and the 24 widths of the family; a source file with another hash
+    is refused; a stand-in function is extracted by AST and compared."""
+    import hashlib
+    from q38.utils import audit_flops
+    report = audit_flops.backbone_report()
+    assert report["failures"] == [] and len(report["archived_configs"]) == 19 and len(report["canonical_family"]) == 24
+    first = report["archived_configs"][0]
+    assert (first["shape"], first["megatron_train_flops_per_token"], first["router_and_shared_gate_train_flops_per_token"]) == ("h128_L4", 27580416, 199680)
+    assert report["delta_rule_kernels"]["products_64x64x64_per_chunk_and_value_head"] == {
+        "gdn_scan_fwd_kernel": 4, "gdn_scan_bwd_kernel": 8, "gdn_prep_fwd_kernel": 4, "gdn_prep_bwd_kernel": 12}
+    fake = tmp_path / "training.py"
+    fake.write_text("import os\n\ndef num_floating_point_operations(args, batch_size):\n"
+                    "    assert is_gated_delta_net_variant(args.experimental_attention_variant) and not is_hybrid_model(args)\n"
+                    "    return 123 * batch_size * args.seq_length\n")
+    with pytest.raises(ValueError, match="not the pinned Megatron revision"):
+        audit_flops.load_megatron_function(fake)
+    function = audit_flops.load_megatron_function(fake, hashlib.sha256(fake.read_bytes()).hexdigest())
+    row = audit_flops.audit_backbone(small(), 8192, function)
+    assert row["megatron_function_evaluated"] == 123 and any("pinned Megatron function gives" in f for f in row["failures"])
+    assert audit_flops.main(["--backbone", "--output", str(tmp_path / "audit.json")]) == 0
 
 
 def test_launcher_builds_loopback_torchrun_command():
