@@ -840,6 +840,13 @@ class Backend:
                 count, index = (t.to(q.device).contiguous() for t in next(self.selection_override))
             else:
                 count, index = load().qsa_select(lp_blk, budget)
+            if want_kl and modeling.QSA_STAT.get("on"):
+                # debug statistic (reference: modeling_qwen3_8_moe.py:1136-1142): share of the dense attention mass that falls into
+                # the selected blocks.  The kernels never form the block masses, so this recomputes them the slow way.
+                with torch.no_grad():
+                    P = modeling.block_mass(q.detach(), k.detach(), attn.scaling)
+                    chosen = modeling.block_sparse_mask(count, index, S)[:, ::modeling.BLK, ::modeling.BLK].float()
+                    modeling.QSA_STAT.setdefault("recall", []).append((P.view(B, S // modeling.BLK, modeling.BLK, -1) * chosen[:, :, None, :]).sum(-1).mean().item())
             o = _BlockAttention.apply(q, k, v, count, index, attn.scaling)
         o = o.reshape(B, S, -1)
         o = _SigmoidMul.apply(o, gate) if (o.numel() % 8 == 0 and o.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16) else o * torch.sigmoid(gate)

@@ -152,6 +152,32 @@ def test_select_blocks_rules():
     assert mask[0, 200, 200] and not mask[0, 200, 201] and mask.sum(-1).min() >= 1
 
 
+def test_qsa_recall_statistic(tiny_config):
+    """QSA_STAT["on"] records, per QSA layer and training forward of the sparse phase, the share of the dense attention mass that
+    lies in the selected blocks: within (0, 1] for a budget of one block, exactly 1 when the budget covers every causal block
+    (reference: modeling_qwen3_8_moe.py:1114,1136-1142)."""
+    torch.manual_seed(0)
+    ids = torch.randint(1, 128, (1, 128))
+    recalls = {}
+    for budget in (1, 2):
+        tiny_config.qsa_blocks = budget
+        model = Q38ForCausalLM(tiny_config).train()
+        model.model.qsa_dense = False
+        modeling.QSA_STAT.clear()
+        modeling.QSA_STAT["on"] = True
+        try:
+            LossModel(model, 8, 2, ce=CE())(ids, ids.roll(-1, 1))
+            recalls[budget] = list(modeling.QSA_STAT["recall"])
+        finally:
+            modeling.QSA_STAT.clear()
+    assert len(recalls[1]) == 1 and 0.0 < recalls[1][0] < 1.0                       # one QSA layer in four; 128 tokens = two blocks
+    assert abs(recalls[2][0] - 1.0) < 1e-5
+    model.eval()
+    with torch.no_grad():
+        model(input_ids=ids, use_cache=False)
+    assert "recall" not in modeling.QSA_STAT                                        # off: nothing recorded
+
+
 def test_mhc_initialisation_is_a_residual_connection():
     torch.manual_seed(0)
     mhc = modeling.MHC(32, 4, 4, slot=1, iters=20)
