@@ -336,8 +336,9 @@ __global__ void __launch_bounds__(128) gdn_prep_fwd_kernel(const bf16* __restric
   bf16* sm = reinterpret_cast<bf16*>(smem_bytes);
   PrepSmem s;
   s.Qn = sm; s.Kn = sm + TILE_ELEMS; s.KBG = sm + 2 * TILE_ELEMS; s.VB = sm + 3 * TILE_ELEMS; s.Tm = sm + 4 * TILE_ELEMS;
-  float* L = reinterpret_cast<float*>(sm + 5 * TILE_ELEMS);          // [64][65]
-  s.gc = L + 64 * 65; s.beta = s.gc + 64; s.rq = s.beta + 64; s.rk = s.rq + 64;
+  constexpr int LSTRIDE = 68;                                        // rows 16-byte aligned for float4 reads
+  float* L = reinterpret_cast<float*>(sm + 5 * TILE_ELEMS);          // [64][68]
+  s.gc = L + 64 * LSTRIDE; s.beta = s.gc + 64; s.rq = s.beta + 64; s.rk = s.rq + 64;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, bh = blockIdx.y, b = bh / Hv, hv = bh % Hv, hk = hv / (Hv / Hk);
   const int NT = gridDim.x;
@@ -372,21 +373,29 @@ __global__ void __launch_bounds__(128) gdn_prep_fwd_kernel(const bf16* __restric
   float acc[8][4];
   zero_acc(acc);
   mma64<false, true>(s.Kn, s.Kn, acc, warp, lane);                    // k_i . k_j
-  FRAG_LOOP(nt, e, row, col) { L[row * 65 + col] = col < row ? s.beta[row] * acc[nt][e] * __expf(s.gc[row] - s.gc[col]) : 0.f; }
+  FRAG_LOOP(nt, e, row, col) { L[row * LSTRIDE + col] = col < row ? s.beta[row] * acc[nt][e] * __expf(s.gc[row] - s.gc[col]) : 0.f; }
   zero_acc(acc);
   mma64<false, true>(s.Qn, s.Kn, acc, warp, lane);                    // q_i . k_j
   FRAG_LOOP(nt, e, row, col) { acc[nt][e] = col <= row ? acc[nt][e] * __expf(s.gc[row] - s.gc[col]) : 0.f; }
   acc_to_global(acc, P_out + tile_off, 64, warp, lane);
   __syncthreads();
   if (tid < 64) {
-    // column `tid` of (I + L)^-1 by forward substitution; L[i][j] reads are warp broadcasts
+    // column `tid` of (I + L)^-1 by forward substitution; L[i][j] reads are warp broadcasts, four at a time.  The dot product of
+    // row i runs as four independent chains so that its length, not the FMA latency times i, bounds the step.
     float x[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) {
-      float a = (i == tid) ? 1.f : 0.f;
+      float a0 = (i == tid) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      const float4* Lrow = reinterpret_cast<const float4*>(L + i * LSTRIDE);
 #pragma unroll
-      for (int j = 0; j < i; ++j) a -= L[i * 65 + j] * x[j];
-      x[i] = a;
+      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+        const float4 l = Lrow[j4];                      // entries at or right of the diagonal are zero
+        a0 -= l.x * x[4 * j4];
+        if (4 * j4 + 1 < i) a1 -= l.y * x[4 * j4 + 1];
+        if (4 * j4 + 2 < i) a2 -= l.z * x[4 * j4 + 2];
+        if (4 * j4 + 3 < i) a3 -= l.w * x[4 * j4 + 3];
+      }
+      x[i] = (a0 + a1) + (a2 + a3);
     }
 #pragma unroll
     for (int i = 0; i < 64; ++i) s.Tm[i * LDS + tid] = __float2bfloat16_rn(x[i]);
@@ -679,7 +688,7 @@ std::vector<at::Tensor> gdn_prep_fwd(const at::Tensor& q, const at::Tensor& k, c
   for (int i = 0; i < 6; ++i) out.push_back(at::empty({BH, NT, 64, 64}, opts));
   out.push_back(at::empty({BH, NT}, opts.dtype(at::kFloat)));
   out.push_back(at::empty({BH, NT, 64}, opts.dtype(at::kFloat)));
-  const int smem = 5 * TILE_ELEMS * 2 + (64 * 65 + 256) * 4;
+  const int smem = 5 * TILE_ELEMS * 2 + (64 * 68 + 256) * 4;
   static bool configured = false;
   if (!configured) { C10_CUDA_CHECK(cudaFuncSetAttribute(gdn_prep_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); configured = true; }
   gdn_prep_fwd_kernel<<<dim3((int)NT, (int)BH), 128, smem, at::cuda::getCurrentCUDAStream()>>>(

@@ -656,7 +656,10 @@ void moe_grouped_dswiglu(const at::Tensor& dy, const at::Tensor& w_down, const a
 }
 
 // grad[e][m, n] += sum_{rows of expert e} a[row, m] * b[row, n]      a [P, M], b [P, N] bf16, grad [E, M, N] fp32
+void moe_grouped_wgrad_p(const at::Tensor& a, const at::Tensor& b, at::Tensor& grad, const at::Tensor& offsets, at::Tensor& err);   // moe_persistent.cu
+
 void moe_grouped_wgrad(const at::Tensor& a, const at::Tensor& b, at::Tensor& grad, const at::Tensor& offsets, at::Tensor& err) {
+  if (moe_persistent_enabled()) return moe_grouped_wgrad_p(a, b, grad, offsets, err);
   check_bf16_2d(a, "wgrad a"); check_bf16_2d(b, "wgrad b");
   TORCH_CHECK(grad.is_cuda() && grad.scalar_type() == at::kFloat && grad.dim() == 3 && grad.is_contiguous(), "moe_grouped_wgrad: grad must be contiguous fp32 [E,M,N]");
   const c10::cuda::CUDAGuard guard(a.device());

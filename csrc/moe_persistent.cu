@@ -14,7 +14,9 @@
 //   PE_STORE    C[row, n] = A[row, :] . B_e[n, :]                                   (down projection, input gradients)
 //   PE_SWIGLU   gate and up accumulators -> gu[row, 2f] and hmid[row, f] = silu(g) * u
 //   PE_DSWIGLU  accumulator = d(hmid); reads gu, writes d(gu)[row, 2f]
-// The weight-gradient product and the expert-parallel return epilogue stay in moe.cu.
+//   PE_WGRAD    C_e[m, n] += sum over the expert's rows of A[row, m] B[row, n]: both operands MN-major, K = the expert's rows
+//               (the ragged last K block is cleared in shared memory), fp32 read-modify-write of C fetched one chunk ahead
+// The expert-parallel return epilogue stays in moe.cu.
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -24,7 +26,7 @@
 
 namespace q38 {
 
-enum { PE_STORE = 0, PE_SWIGLU = 1, PE_DSWIGLU = 2 };
+enum { PE_STORE = 0, PE_SWIGLU = 1, PE_DSWIGLU = 2, PE_WGRAD = 3 };
 constexpr int PG_BM = 128, PG_BK = 64, PG_STAGES = 4, PG_THREADS = 320, PG_ACC_COLS = 256;
 
 struct PGroupedArgs {
@@ -33,7 +35,11 @@ struct PGroupedArgs {
   void* out0; long long ld0;
   void* out1; long long ld1;
   int* err;
+  // PE_WGRAD: expert row offsets [E + 1], experts, M tiles and rows of C per expert, elements between experts in C
+  const int* offsets; int experts, tiles_m, M; long long c_expert_stride;
 };
+
+struct PGWork { int expert, row0, rows, n0, m0, k_begin, num_kb; };
 
 __device__ __forceinline__ void pg_store16(__nv_bfloat16* dst, const float (&v)[16]) {
   uint32_t w[8];
@@ -46,7 +52,7 @@ __device__ __forceinline__ void pg_store16(__nv_bfloat16* dst, const float (&v)[
   reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-template <int EPI, bool B_MN>
+template <int EPI, bool B_MN, bool A_MN = false>
 __global__ void __launch_bounds__(PG_THREADS) grouped_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                                                                         PGroupedArgs p) {
   extern __shared__ uint8_t smem_raw[];
@@ -60,7 +66,7 @@ __global__ void __launch_bounds__(PG_THREADS) grouped_persistent_kernel(const __
   uint64_t* acc_empty = acc_full + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int work_items = p.sched[0] * p.tiles_n, num_kb = (p.K + PG_BK - 1) / PG_BK;
+  const int work_items = EPI == PE_WGRAD ? p.experts * p.tiles_m * p.tiles_n : p.sched[0] * p.tiles_n;
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tmA);
@@ -75,11 +81,26 @@ __global__ void __launch_bounds__(PG_THREADS) grouped_persistent_kernel(const __
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // work item -> (expert, first row, valid rows, first output column); N tiles of one row tile are consecutive (A reuse from L2)
-  auto decode = [&](int w, int& expert, int& row0, int& rows, int& n0) {
-    const int tile = w / p.tiles_n;
-    n0 = (w % p.tiles_n) * p.bn;
-    expert = p.sched[1 + 3 * tile]; row0 = p.sched[2 + 3 * tile]; rows = p.sched[3 + 3 * tile];
+  // work item -> tile.  Grouped products: (schedule tile, N tile), the N tiles of one row tile consecutive (A reuse from L2).
+  // Weight gradients: (expert, M tile, N tile), the tiles of one expert consecutive; an expert without rows has num_kb = 0 and is
+  // skipped by all three roles alike.
+  auto decode = [&](int w) {
+    PGWork k;
+    if (EPI == PE_WGRAD) {
+      const int per_expert = p.tiles_m * p.tiles_n, in_expert = w % per_expert;
+      k.expert = w / per_expert;
+      k.m0 = (in_expert / p.tiles_n) * PG_BM; k.n0 = (in_expert % p.tiles_n) * p.bn;
+      k.k_begin = p.offsets[k.expert];
+      k.rows = p.offsets[k.expert + 1] - k.k_begin;
+      k.row0 = 0;
+      k.num_kb = k.rows > 0 ? (k.rows + PG_BK - 1) / PG_BK : 0;
+    } else {
+      const int tile = w / p.tiles_n;
+      k.n0 = (w % p.tiles_n) * p.bn; k.m0 = 0; k.k_begin = 0;
+      k.expert = p.sched[1 + 3 * tile]; k.row0 = p.sched[2 + 3 * tile]; k.rows = p.sched[3 + 3 * tile];
+      k.num_kb = (p.K + PG_BK - 1) / PG_BK;
+    }
+    return k;
   };
 
   if (warp == 0) {
@@ -87,46 +108,69 @@ __global__ void __launch_bounds__(PG_THREADS) grouped_persistent_kernel(const __
       uint32_t it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
-        int expert, row0, rows, n0;
-        decode(w, expert, row0, rows, n0);
-        const int b_row_base = expert * p.b_rows_per_expert;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const PGWork k = decode(w);
+        const int b_row_base = k.expert * p.b_rows_per_expert;
+        for (int kb = 0; kb < k.num_kb; ++kb, ++it) {
           const int s = it % PG_STAGES;
           if (!ptx::mbar_wait(&empty[s], ((it / PG_STAGES) & 1) ^ 1, 1u << 20)) { report_error(p.err, ERR_MMA_WAIT); ok = false; break; }
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           uint8_t* b_dst = a_dst + A_BYTES;
           ptx::mbar_expect_tx(&full[s], STAGE_BYTES);
-          const int k0 = kb * PG_BK;
-          ptx::tma_load_3d(a_dst, &tmA, &full[s], k0, row0, 0);
-          if (B_MN) {                         // B_e stored [K, N]: row = expert * K + k, boxes of 64 columns
-            for (int i = 0; i < p.bn_alloc / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], n0 + 64 * i, b_row_base + k0, 0);
-          } else if (EPI == PE_SWIGLU) {      // gate rows [n0, n0 + bn) and up rows [f + n0, f + n0 + bn) of expert e
-            ptx::tma_load_3d(b_dst, &tmB, &full[s], k0, b_row_base + n0, 0);
-            ptx::tma_load_3d(b_dst + p.bn * PG_BK * 2, &tmB, &full[s], k0, b_row_base + p.N + n0, 0);
+          const int k0 = k.k_begin + kb * PG_BK;
+          if (A_MN) {                         // A stored [rows, M]: boxes of 64 columns
+#pragma unroll
+            for (int i = 0; i < PG_BM / 64; ++i) ptx::tma_load_3d(a_dst + i * 8192, &tmA, &full[s], k.m0 + 64 * i, k0, 0);
           } else {
-            ptx::tma_load_3d(b_dst, &tmB, &full[s], k0, b_row_base + n0, 0);
+            ptx::tma_load_3d(a_dst, &tmA, &full[s], k0, k.row0, 0);
+          }
+          if (EPI == PE_WGRAD) {              // B stored [rows, N], the same sorted rows as A
+            for (int i = 0; i < p.bn_alloc / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], k.n0 + 64 * i, k0, 0);
+          } else if (B_MN) {                  // B_e stored [K, N]: row = expert * K + k, boxes of 64 columns
+            for (int i = 0; i < p.bn_alloc / 64; ++i) ptx::tma_load_3d(b_dst + i * 8192, &tmB, &full[s], k.n0 + 64 * i, b_row_base + k0, 0);
+          } else if (EPI == PE_SWIGLU) {      // gate rows [n0, n0 + bn) and up rows [f + n0, f + n0 + bn) of expert e
+            ptx::tma_load_3d(b_dst, &tmB, &full[s], k0, b_row_base + k.n0, 0);
+            ptx::tma_load_3d(b_dst + p.bn * PG_BK * 2, &tmB, &full[s], k0, b_row_base + p.N + k.n0, 0);
+          } else {
+            ptx::tma_load_3d(b_dst, &tmB, &full[s], k0, b_row_base + k.n0, 0);
           }
         }
       }
     }
   } else if (warp == 1) {
-    if (ptx::elect_one()) {
-      const uint32_t idesc = ptx::umma_idesc_bf16(PG_BM, p.bn, false, B_MN);
-      uint32_t it = 0, item = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x, ++item) {
-        const int acc = item & 1;
-        if (!ptx::mbar_wait(&acc_empty[acc], ((item >> 1) & 1) ^ 1, 1u << 22)) { report_error(p.err, ERR_EPILOGUE_WAIT); ok = false; break; }
+    const uint32_t idesc = ptx::umma_idesc_bf16(PG_BM, p.bn, A_MN, B_MN);
+    uint32_t it = 0, item = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+      const PGWork k = decode(w);
+      if (k.num_kb == 0) continue;
+      const int acc = item & 1;
+      if (!ptx::mbar_wait(&acc_empty[acc], ((item >> 1) & 1) ^ 1, 1u << 22)) { if (lane == 0) report_error(p.err, ERR_EPILOGUE_WAIT); ok = false; break; }
+      ptx::tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * PG_ACC_COLS;
+      for (int kb = 0; kb < k.num_kb; ++kb, ++it) {
+        const int s = it % PG_STAGES;
+        if (!ptx::mbar_wait(&full[s], (it / PG_STAGES) & 1, 1u << 20)) { if (lane == 0) report_error(p.err, ERR_TMA_WAIT); ok = false; break; }
+        uint8_t* a_tile = smem + s * STAGE_BYTES;
+        if (EPI == PE_WGRAD) {
+          const int valid = k.rows - kb * PG_BK;            // K rows of this block that belong to the expert
+          if (valid < PG_BK) {
+            // an MN-major box is 64 K-rows of 128 bytes; rows past the expert's range hold another expert's rows or memory
+            // never written, in both operands (the B boxes follow the A boxes in the stage): clear them
+            const int boxes = PG_BM / 64 + p.bn_alloc / 64, per_box = (PG_BK - valid) * 8;
+            for (int i = lane; i < per_box * boxes; i += 32) {
+              const int box = i / per_box, rem = i % per_box;
+              *reinterpret_cast<uint4*>(a_tile + box * 8192 + (valid + rem / 8) * 128 + (rem % 8) * 16) = make_uint4(0, 0, 0, 0);
+            }
+            ptx::fence_proxy_async();
+          }
+          __syncwarp();
+        }
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * PG_ACC_COLS;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % PG_STAGES;
-          if (!ptx::mbar_wait(&full[s], (it / PG_STAGES) & 1, 1u << 20)) { report_error(p.err, ERR_TMA_WAIT); ok = false; break; }
-          ptx::tc_fence_after();
-          const uint32_t a_base = ptx::smem_u32(smem + s * STAGE_BYTES), b_base = a_base + A_BYTES;
+        if (ptx::elect_one()) {
+          const uint32_t a_base = ptx::smem_u32(a_tile), b_base = a_base + A_BYTES;
 #pragma unroll
           for (int j = 0; j < PG_BK / 16; ++j) {
-            const uint64_t a_desc = ptx::umma_smem_desc_sw128(a_base + j * 32, 0, 1024);
+            const uint64_t a_desc = A_MN ? ptx::umma_smem_desc_sw128(a_base + j * 2048, 8192, 1024) : ptx::umma_smem_desc_sw128(a_base + j * 32, 0, 1024);
             const uint64_t b_desc = B_MN ? ptx::umma_smem_desc_sw128(b_base + j * 2048, 8192, 1024) : ptx::umma_smem_desc_sw128(b_base + j * 32, 0, 1024);
             ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | j) != 0);
             if (EPI == PE_SWIGLU) {
@@ -136,22 +180,71 @@ __global__ void __launch_bounds__(PG_THREADS) grouped_persistent_kernel(const __
           }
           ptx::umma_commit(&empty[s]);
         }
-        if (ok) ptx::umma_commit(&acc_full[acc]);
+        __syncwarp();
       }
+      if (ok && ptx::elect_one()) ptx::umma_commit(&acc_full[acc]);
+      __syncwarp();
+      ++item;
     }
   } else {
     const int quarter = warp & 3, r_local = quarter * 32 + lane, group = (warp - 2) >> 2;      // the two warpgroups take alternate 16-column chunks
     uint32_t item = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x, ++item) {
-      int expert, row0, rows, n0;
-      decode(w, expert, row0, rows, n0);
+    for (int w = blockIdx.x; w < work_items && ok; w += gridDim.x) {
+      const PGWork k = decode(w);
+      if (k.num_kb == 0) continue;
+      const int rows = k.rows, n0 = k.n0;
       const int acc = item & 1;
+      const uint32_t lane_addr = tmem_base + acc * PG_ACC_COLS + (uint32_t(quarter * 32) << 16);
+      if (EPI == PE_WGRAD) {
+        // C is read before the accumulator is awaited and one chunk ahead of its use: the row-per-thread read-modify-write is
+        // latency bound otherwise
+        const int crow = k.m0 + r_local;
+        const bool live = crow < p.M, vec = p.ld0 % 4 == 0;
+        float* c_row = reinterpret_cast<float*>(p.out0) + k.expert * p.c_expert_stride + (long long)crow * p.ld0;
+        float4 cur[4], nxt[4];
+        auto fetch = [&](int c, float4 (&dst)[4]) {
+          if (live && vec && c + 16 <= p.N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) dst[v] = reinterpret_cast<const float4*>(c_row + c)[v];
+          }
+        };
+        fetch(n0 + 16 * group, cur);
+        if (!ptx::mbar_wait(&acc_full[acc], (item >> 1) & 1, 1u << 22)) { report_error(p.err, ERR_EPILOGUE_WAIT); ok = false; break; }
+        ptx::tc_fence_after();
+        for (int c0 = 16 * group; c0 < p.bn; c0 += 32) {
+          uint32_t r[16];
+          ptx::tmem_ld_32x32b_x16(lane_addr + c0, r);
+          if (c0 + 32 < p.bn) fetch(n0 + c0 + 32, nxt);
+          ptx::tmem_ld_wait();
+          const int c = n0 + c0;
+          if (live) {
+            if (vec && c + 16 <= p.N) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float4 o = cur[v];
+                o.x += __uint_as_float(r[4 * v]); o.y += __uint_as_float(r[4 * v + 1]);
+                o.z += __uint_as_float(r[4 * v + 2]); o.w += __uint_as_float(r[4 * v + 3]);
+                reinterpret_cast<float4*>(c_row + c)[v] = o;
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) if (c + e < p.N) c_row[c + e] += __uint_as_float(r[e]);
+            }
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v) cur[v] = nxt[v];
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&acc_empty[acc]);
+        ++item;
+        continue;
+      }
       if (!ptx::mbar_wait(&acc_full[acc], (item >> 1) & 1, 1u << 22)) { report_error(p.err, ERR_EPILOGUE_WAIT); ok = false; break; }
       ptx::tc_fence_after();
       const bool live = r_local < rows;
-      const long long row = row0 + r_local;
-      const uint32_t lane_addr = tmem_base + acc * PG_ACC_COLS + (uint32_t(quarter * 32) << 16);
+      const long long row = k.row0 + r_local;
       if (EPI == PE_DSWIGLU) {
         // accumulator = d(hmid) for f = p.N columns.  The gate/up values of a chunk do not depend on the accumulator, so they are
         // fetched one chunk ahead: the global-load latency hides behind the TMEM read and the arithmetic of the chunk before.
@@ -247,6 +340,7 @@ __global__ void __launch_bounds__(PG_THREADS) grouped_persistent_kernel(const __
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&acc_empty[acc]);
+      ++item;
     }
   }
   ptx::tc_fence_before();
@@ -276,9 +370,9 @@ static int pg_pick_bn(int N, int limit) {
   return best;
 }
 
-template <int EPI, bool B_MN>
+template <int EPI, bool B_MN, bool A_MN = false>
 static void pg_launch(const CUtensorMap& ta, const CUtensorMap& tb, PGroupedArgs p, int max_tiles, cudaStream_t stream) {
-  auto kernel = grouped_persistent_kernel<EPI, B_MN>;
+  auto kernel = grouped_persistent_kernel<EPI, B_MN, A_MN>;
   constexpr int nacc = EPI == PE_SWIGLU ? 2 : 1;
   p.bn_alloc = B_MN ? (p.bn + 63) / 64 * 64 : p.bn;
   const int smem = PG_STAGES * (PG_BM * PG_BK * 2 + nacc * p.bn_alloc * PG_BK * 2) + 1024 + 256;
@@ -342,6 +436,22 @@ void moe_grouped_dswiglu_p(const at::Tensor& dy, const at::Tensor& w_down, const
   p.sched = sched.data_ptr<int>(); p.bn = bn; p.tiles_n = (f + bn - 1) / bn; p.K = K; p.N = f; p.b_rows_per_expert = K;
   p.out0 = dgu.data_ptr(); p.ld0 = 2 * f; p.out1 = const_cast<void*>(gu.data_ptr()); p.ld1 = 2 * f; p.err = err.data_ptr<int>();
   pg_launch<PE_DSWIGLU, true>(ta, tb, p, max_tiles, at::cuda::getCurrentCUDAStream());
+}
+
+// grad[e] += a[rows of e]^T b[rows of e]:  a [P, M], b [P, N] sorted by expert, grad [E, M, N] fp32, offsets [E + 1]
+void moe_grouped_wgrad_p(const at::Tensor& a, const at::Tensor& b, at::Tensor& grad, const at::Tensor& offsets, at::Tensor& err) {
+  pg_check(a, "wgrad a"); pg_check(b, "wgrad b");
+  TORCH_CHECK(grad.is_cuda() && grad.scalar_type() == at::kFloat && grad.dim() == 3 && grad.is_contiguous(), "moe_grouped_wgrad: grad must be contiguous fp32 [E,M,N]");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int P = a.size(0), M = a.size(1), N = b.size(1), E = grad.size(0);
+  TORCH_CHECK(b.size(0) == P && grad.size(1) == M && grad.size(2) == N && M % 8 == 0 && N % 8 == 0 && offsets.numel() == E + 1, "moe_grouped_wgrad: shape mismatch");
+  const int bn = pg_pick_bn(N, 256);
+  CUtensorMap ta = make_tmap_bf16(a.data_ptr(), M, P, 1, M, 0, 64);
+  CUtensorMap tb = make_tmap_bf16(b.data_ptr(), N, P, 1, N, 0, 64);
+  PGroupedArgs p{};
+  p.offsets = offsets.data_ptr<int>(); p.experts = E; p.tiles_m = (M + PG_BM - 1) / PG_BM; p.M = M; p.c_expert_stride = (long long)M * N;
+  p.bn = bn; p.tiles_n = (N + bn - 1) / bn; p.N = N; p.K = 0; p.out0 = grad.data_ptr(); p.ld0 = N; p.err = err.data_ptr<int>();
+  pg_launch<PE_WGRAD, true, true>(ta, tb, p, E * p.tiles_m, at::cuda::getCurrentCUDAStream());
 }
 
 }  // namespace q38

@@ -86,7 +86,7 @@ class _MultiLinear(torch.autograd.Function):
                 w = _bf16_weight(weight)
                 if dx is None:
                     dx = backend.mm_nn(dy2, w)
-                elif w.shape[1] % 8 == 0 and backend.layouts["nn"] and os.environ.get("Q38_MULTI_LINEAR") == "2":
+                elif w.shape[1] % 8 == 0 and backend.layouts["nn"] and os.environ.get("Q38_MULTI_LINEAR", "2") == "2":
                     gemm(_tma_rows(dy2), w, out=dx, b_mn_major=True, accumulate=True)          # dx += dy_i W_i: the TMA unit adds the tile
                 elif w.shape[1] % 8 == 0 and backend.layouts["nn"]:
                     dx = gemm(_tma_rows(dy2), w, b_mn_major=True, addend=dx, beta=1.0)        # dx <- dy_i W_i + dx, one kernel
@@ -725,10 +725,11 @@ class Backend:
 
     def linears(self, x, *weights):
         """Projections of one input by several weights (tuple of outputs); their input gradients are summed inside the GEMMs."""
-        # Default: one autograd node per projection and autograd's own additions of the input gradients.  Q38_MULTI_LINEAR=1
-        # sums them in the GEMM epilogue instead; measured 1 % slower on q38_c2 (745 vs 737 ms per step): the epilogue reads the
-        # running sum row by row, which costs more than a separate, fully coalesced addition kernel saves.
-        if os.environ.get("Q38_MULTI_LINEAR", "0") not in ("1", "2"):
+        # Default (Q38_MULTI_LINEAR=2): one autograd node for the group; in its backward the second and later input-gradient GEMMs
+        # add their tiles onto the first one's output with the TMA unit's bf16 reduce-add, so no addition kernels run (measured
+        # 703.7 vs 712.0 ms per q38_c2 step).  =1 reads the running sum in the GEMM epilogue instead, row by row, which measured
+        # 1 % slower than separate additions; =0 is one autograd node per projection with autograd's own additions.
+        if os.environ.get("Q38_MULTI_LINEAR", "2") not in ("1", "2"):
             return tuple(self.linear(x, w) for w in weights)
         return _MultiLinear.apply(x, self, *weights)
 

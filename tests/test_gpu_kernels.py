@@ -270,13 +270,20 @@ def test_persistent_grouped_kernels_match_the_one_tile_kernels(ops, T, h, f, E, 
             raw.moe_grouped_dswiglu(dy, wd, gu, dgu, sched, err)
             dx = torch.zeros(P, h, device="cuda", dtype=torch.bfloat16)
             raw.moe_grouped_gemm(dgu, wgu, dx, sched, True, err)
-            got[mode] = (hmid, gu, y, dgu, dx)
+            gw = torch.zeros(E, 2 * f, h, device="cuda")
+            for _ in range(2):                                   # the second pass accumulates onto the first
+                raw.moe_grouped_wgrad(dgu, rows, gw, offsets, err)
+            gd = torch.zeros(E, h, f, device="cuda")
+            raw.moe_grouped_wgrad(dy, hmid, gd, offsets, err)
+            got[mode] = (hmid, gu, y, dgu, dx, gw, gd)
     finally:
         raw.moe_set_persistent(-1)
     ops.check_errors()
-    for a, b, name in zip(got[1], got[0], ("hmid", "gu", "y", "dgu", "dx")):
+    for a, b, name in zip(got[1], got[0], ("hmid", "gu", "y", "dgu", "dx", "grad gate_up", "grad down")):
         assert rel_err(a, b) < 1e-6, name
     off = offsets.tolist()
+    ref_gw = torch.stack([got[1][3][off[e]:off[e + 1]].float().T @ rows[off[e]:off[e + 1]].float() for e in range(E)])
+    assert rel_err(got[1][5], 2 * ref_gw) < 1e-3
     ref_gu = torch.zeros(P, 2 * f, device="cuda")
     for e in range(E):
         ref_gu[off[e]:off[e + 1]] = rows[off[e]:off[e + 1]].float() @ wgu[e].float().T

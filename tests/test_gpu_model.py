@@ -78,6 +78,30 @@ def test_backend_matches_cpu_specification(dense, monkeypatch):
     assert worst[0][0] < 0.2 and mean < 0.06, (mean, worst[:6])
 
 
+def test_recall_statistic_on_the_kernel_path():
+    """QSA_STAT on the kernel path records the same recall as the fp32 specification when both use the same selection."""
+    from q38 import ops
+    from q38.models import modeling
+    ops.install()
+    cfg, cpu_model = build()
+    gpu_model = copy.deepcopy(cpu_model).cuda()
+    gpu_model.tie_embeddings()
+    gpu_model.model.compute_dtype = torch.bfloat16
+    ids = torch.randint(1, 512, (2, 256))
+    recorded = {}
+    for name, model, batch in (("cpu", cpu_model, ids), ("gpu", gpu_model, ids.cuda())):
+        modeling.QSA_STAT.clear()
+        modeling.QSA_STAT["on"] = True
+        try:
+            losses(model, batch, False)
+            recorded[name] = list(modeling.QSA_STAT.get("recall", []))
+        finally:
+            modeling.QSA_STAT.clear()
+    ops.check_errors()
+    assert len(recorded["cpu"]) == len(recorded["gpu"]) == 1
+    assert 0.0 < recorded["gpu"][0] <= 1.0 and abs(recorded["gpu"][0] - recorded["cpu"][0]) < 0.05
+
+
 def test_public_training_step_reduces_loss():
     from q38.train import TRAIN_DEFAULTS, Trainer
     from q38 import ops
