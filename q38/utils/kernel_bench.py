@@ -1,7 +1,7 @@
 """Per-kernel benchmark at the shapes of a preset: device time (CUDA events), achieved FLOP/s or bytes/s and the
 fraction of the measured roofline.
 
-  python -m q38.utils.kernel_bench --preset q38_c2 [--kernels gemm,moe,mhc,gdn,qsa,conv] [--iters 20] [--json out.json]
+  python -m q38.utils.kernel_bench --preset q38_c2 [--kernels gemm,moe,mhc,gdn,qsa,conv,fp8,muon,ce,ngram] [--iters 20] [--json out.json]
 
 Denominators come from ``MEASURED_PEAKS.json`` at the repository root when present (copy bandwidth and cuBLAS bf16
 throughput measured on the same pool), otherwise 6.65 TB/s and 1.59 PFLOP/s.  Inputs are larger than the 126 MB L2 or
@@ -171,6 +171,10 @@ def bench_qsa(rows, shape, T, iters, pk, seq=4096):
     wi = torch.rand(B, seq, 4, device="cuda")
     t = timeit(lambda: lib.qsa_indexer_fwd(qi, ki, wi, 0.125), iters)
     report(rows, f"qsa_indexer_fwd B={B}", t, flops=4 * causal_tiles * 2.0 * 64 ** 3, pk=pk)
+    blse = lib.qsa_indexer_fwd(qi, ki, wi, 0.125)
+    dblse = torch.randn_like(blse) * 1e-3
+    t = timeit(lambda: lib.qsa_indexer_bwd(qi, ki, wi, blse, dblse, 1.0 / (B * seq), 0.125), iters)
+    report(rows, f"qsa_indexer_bwd (q and k kernels) B={B}", t, flops=3 * 4 * causal_tiles * 2.0 * 64 ** 3, pk=pk)
     lp = torch.randn(B, seq // 64, seq // 64, device="cuda")
     count, index = lib.qsa_select(lp, shape["qsa_blocks"])
     t = timeit(lambda: lib.qsa_attn_fwd(q, k, v, count, index, 0.125), iters)
@@ -255,6 +259,43 @@ def bench_muon(rows, shape, T, iters, pk):
     report(rows, f"muon step (prepass + 5 NS iterations + apply), {len(entries) * E} matrices", t, flops=flops, bytes_=26.0 * cursor, pk=pk)
 
 
+def bench_ce(rows, shape, T, iters, pk):
+    """In-place cross-entropy over one vocabulary chunk of bf16 logits: loss per row out, d(logits) left in the logits buffer."""
+    from .. import ops
+    lib = ops.load()
+    vocab, chunk = 10112, 8192
+    logits = [torch.randn(chunk, vocab, device="cuda").to(torch.bfloat16) for _ in range(2)]      # 2 x 166 MB: rotated, larger than L2
+    target = torch.randint(0, vocab, (chunk,), device="cuda")
+    state = {"i": 0}
+
+    def step():
+        state["i"] ^= 1
+        lib.ce_inplace(logits[state["i"]], target)
+
+    t = timeit(step, iters)
+    report(rows, f"ce_inplace {chunk}x{vocab}", t, bytes_=4.0 * chunk * vocab, pk=pk)
+
+
+def bench_ngram(rows, shape, T, iters, pk, seq=4096):
+    """Bigram/trigram hash embedding: gather + sum + RMSNorm forward, scatter-add backward into the fp32 tables."""
+    from .. import ops
+    from ..presets import model_config
+    lib = ops.load()
+    cfg = model_config(dict(shape), 10112, seq)
+    h, table_rows = shape["hidden"], cfg.ngram_rows
+    emb2 = torch.randn(table_rows, h, device="cuda") * 0.02
+    emb3 = torch.randn(table_rows, h, device="cuda") * 0.02
+    norm_w = torch.ones(h, device="cuda")
+    ids = torch.randint(1, 10112, (T // seq, seq), device="cuda")
+    t = timeit(lambda: lib.ngram_fwd(ids, emb2, emb3, norm_w, 10112, 53, 1e-6), iters)
+    report(rows, f"ngram_fwd T={T} h={h} rows={table_rows}", t, bytes_=T * h * (2 * 4 + 2.0), pk=pk)
+    e, rstd, picked = lib.ngram_fwd(ids, emb2, emb3, norm_w, 10112, 53, 1e-6)
+    de = torch.randn_like(e)
+    g2, g3 = torch.zeros_like(emb2), torch.zeros_like(emb3)
+    t = timeit(lambda: lib.ngram_bwd(de, picked, emb2, emb3, norm_w, rstd, g2, g3), iters)
+    report(rows, f"ngram_bwd T={T} h={h}", t, bytes_=T * h * (2.0 + 2 * 4 + 2 * 8), pk=pk)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--preset", default="q38_c2")
@@ -270,7 +311,7 @@ def main(argv=None):
     pk = peaks()
     rows = []
     torch.manual_seed(0)
-    BENCHES.update(fp8=bench_fp8, muon=bench_muon)
+    BENCHES.update(fp8=bench_fp8, muon=bench_muon, ce=bench_ce, ngram=bench_ngram)
     for name in a.kernels.split(","):
         BENCHES[name](rows, shape, a.tokens, a.iters, pk)
     ops.check_errors()
