@@ -4,7 +4,10 @@
 
 #include "host.h"
 
-namespace q38 { std::atomic<long long> g_launches{0}; }
+namespace q38 {
+std::atomic<long long> g_launches{0};
+at::Tensor qsa_first_query_lp(const at::Tensor& q_first, const at::Tensor& ki, const at::Tensor& w_first, double scale);   // qsa_first.cu
+}
 
 TORCH_LIBRARY(q38, m) {
   m.def("launch_count() -> int", []() -> int64_t { return (int64_t)q38::g_launches.load(); });
@@ -61,6 +64,7 @@ TORCH_LIBRARY(q38, m) {
   m.def("qsa_block_stats_tc(Tensor q, Tensor k, float scale, Tensor(a!) err) -> Tensor",
         [](const at::Tensor& q, const at::Tensor& k, double scale, at::Tensor& err) { return q38::qsa_block_stats_tc(q, k, scale, err); });
   m.def("qsa_indexer_fwd(Tensor qi, Tensor ki, Tensor wi, float scale) -> Tensor");
+  m.def("qsa_first_query_lp(Tensor q_first, Tensor ki, Tensor w_first, float scale) -> Tensor", &q38::qsa_first_query_lp);
   m.def("qsa_kl_combine(Tensor? stats, Tensor blse, int nq) -> Tensor[]");
   m.def("qsa_select(Tensor lp_blk, int budget) -> Tensor[]");
   m.def("qsa_indexer_bwd(Tensor qi, Tensor ki, Tensor wi, Tensor blse, Tensor dblse, float gscale, float scale) -> Tensor[]");

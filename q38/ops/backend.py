@@ -830,10 +830,15 @@ class Backend:
                 # no KL wanted (evaluation, or training steps that skip it): block selection only looks at the first query of each
                 # 64-token block, so only those S/64 queries are scored -> lp_blk [B, nb, nb]  (reference: modeling_qwen3_8_moe.py:1126)
                 with torch.no_grad():
-                    score = indexer(x.detach(), cos, sin, block_queries=True)
-                    pos = torch.arange(S, device=x.device)
-                    score = score.masked_fill(pos[None, :] > pos[::modeling.BLK][:, None], -1e9)
-                    lp_blk = score.log_softmax(-1).view(B, S // modeling.BLK, S // modeling.BLK, modeling.BLK).logsumexp(-1).contiguous()
+                    qi, ki, wi = indexer.project(x.detach(), cos, sin)
+                    if qi.dtype == torch.bfloat16 and ki.dtype == torch.bfloat16:
+                        lp_blk = load().qsa_first_query_lp(qi[:, :, ::modeling.BLK].contiguous(), ki.reshape(B, S, -1).contiguous(),
+                                                           wi[:, ::modeling.BLK].float().contiguous(), indexer.d_ih ** -0.5)
+                    else:
+                        score = indexer(x.detach(), cos, sin, block_queries=True)
+                        pos = torch.arange(S, device=x.device)
+                        score = score.masked_fill(pos[None, :] > pos[::modeling.BLK][:, None], -1e9)
+                        lp_blk = score.log_softmax(-1).view(B, S // modeling.BLK, S // modeling.BLK, modeling.BLK).logsumexp(-1).contiguous()
         if dense or indexer is None:
             o = _BlockAttention.apply(q, k, v, None, None, attn.scaling)
         else:

@@ -725,6 +725,27 @@ def test_block_statistics_on_tcgen05_match_fp32(ops, B, S, nq, nkv):
         assert ((stats[..., 1] - ref_sum)[causal].abs() / ref_sum[causal]).max() < 2e-3, name
 
 
+@pytest.mark.parametrize("B,S,NI", [(1, 128, 4), (2, 1024, 4), (1, 4096, 2)])
+def test_first_query_indexer_log_probabilities(ops, B, S, NI):
+    """Block log-probabilities of the indexer for the first query of every block (the selection-only path of evaluation) against
+    the specification: scores of those queries, causal mask, log-softmax over keys, log-sum-exp per 64-key block."""
+    torch.manual_seed(41)
+    nb = S // 64
+    qi = torch.randn(B, NI, S, 64, device="cuda").to(torch.bfloat16)
+    ki = torch.randn(B, S, 64, device="cuda").to(torch.bfloat16)
+    wi = torch.rand(B, S, NI, device="cuda") * NI ** -0.5
+    got = ops.load().qsa_first_query_lp(qi[:, :, ::64].contiguous(), ki, wi[:, ::64].contiguous(), 0.125)
+    ops.check_errors()
+    scores = torch.matmul(qi[:, :, ::64].float(), ki[:, None].float().transpose(-1, -2)).to(torch.bfloat16).float()      # [B,NI,nb,S], bf16 like the matmul output
+    score = torch.einsum("bhts,bth->bts", torch.relu(scores) * 0.125, wi[:, ::64])
+    pos = torch.arange(S, device="cuda")
+    score = score.masked_fill(pos[None, :] > pos[::64][:, None], -1e9)
+    ref = score.log_softmax(-1).view(B, nb, nb, 64).logsumexp(-1)
+    causal = torch.ones(nb, nb, device="cuda").tril().bool()
+    assert (got - ref)[:, causal].abs().max().item() < 2e-3
+    assert (got[:, ~causal] < -1e8).all()
+
+
 def test_gemm_accumulates_into_bf16_output(ops):
     """`out += A B^T` with a bf16 output: the epilogue hands the tile to the TMA unit, which adds it in bf16."""
     torch.manual_seed(36)
