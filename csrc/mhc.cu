@@ -763,7 +763,10 @@ std::vector<at::Tensor> mhc_pre_bwd_a(const at::Tensor& dxout, const at::Tensor&
   const int T = X.size(0), h = X.size(2), r = Lraw.size(1);
   auto f32 = X.options();
   auto dLraw = at::empty({T, r}, f32), c1 = at::empty({T}, f32), dxin = at::empty({T, h}, f32);
-  auto dBw = at::zeros({NCOEF, r}, f32), dbias = at::zeros({27}, f32), dnw = at::zeros({h}, f32);
+  // one zero fill for the three small accumulators (offsets kept multiples of 4 floats)
+  const int64_t n_bw = (int64_t)NCOEF * r, off_bias = (n_bw + 3) / 4 * 4, off_nw = off_bias + 28;
+  auto small = at::zeros({off_nw + h}, f32);
+  auto dBw = small.narrow(0, 0, n_bw).view({NCOEF, r}), dbias = small.narrow(0, off_bias, 27), dnw = small.narrow(0, off_nw, h);
   auto stream = at::cuda::getCurrentCUDAStream();
   MhcParams P = params_of(Bw, b_pre, b_post, b_res, alphas);
   const int nq = (h / 4 + 31) / 32;

@@ -114,7 +114,7 @@ class _RMSNorm(torch.autograd.Function):
         if dyc.dtype not in (torch.float32, torch.bfloat16):
             dyc = dyc.float()
         dx, dw = load().rmsnorm_bwd(dyc, x, weight.float().contiguous(), rstd)
-        return dx, dw.to(weight.dtype), None, None
+        return dx, DEFERRED_GRADS.take(weight, dw), None, None
 
 
 class _GatedRMSNorm(torch.autograd.Function):
@@ -129,7 +129,7 @@ class _GatedRMSNorm(torch.autograd.Function):
     def backward(ctx, dy):
         x, gate, weight = ctx.saved_tensors
         dx, dgate, dw = load().gated_rmsnorm_bwd(dy.contiguous(), x, gate, weight.float().contiguous(), ctx.eps)
-        return dx, dgate, dw.to(weight.dtype), None
+        return dx, dgate, DEFERRED_GRADS.take(weight, dw), None
 
 
 class _SideStream:
@@ -167,6 +167,35 @@ class _SideStream:
 
 
 WGRAD_STREAM = _SideStream()
+
+
+class _DeferredGrads:
+    """Gradients of the small parameters (norm weights, conv taps, gate vectors, the mHC biases) collected during a backward pass
+    and added into the parameters' gradient buffers by one multi-tensor launch at its end, instead of one `AccumulateGrad`
+    addition kernel per parameter and micro-step (about 190 launches for q38_c2).  A backward that defers returns None for that
+    parameter.  Only the trainer enables it, because whoever runs the backward must call `flush()` afterwards (the trainer
+    does so where it joins the weight-gradient stream); with `enabled` False every gradient is returned to autograd as usual."""
+
+    def __init__(self):
+        self.enabled = False
+        self.targets, self.deltas = [], []
+
+    def take(self, param, delta):
+        """Queue `param.grad += delta` and return None, or return `delta` in the parameter's dtype when deferral does not apply."""
+        grad = param.grad
+        if not self.enabled or grad is None or grad.dtype != torch.float32 or delta.dtype != torch.float32 or not grad.is_contiguous():
+            return delta.reshape(param.shape).to(param.dtype)
+        self.targets.append(grad)
+        self.deltas.append(delta.reshape(grad.shape))
+        return None
+
+    def flush(self):
+        if self.targets:
+            torch._foreach_add_(self.targets, self.deltas)
+            self.targets, self.deltas = [], []
+
+
+DEFERRED_GRADS = _DeferredGrads()
 
 
 # Every product that leaves the hand-written GEMM for a library matmul is counted here by call site (shapes the tensor-core
@@ -276,8 +305,9 @@ class _MhcPreNorm(torch.autograd.Function):
         dXo = ctx.link.dXo if ctx.link.dXo is not None else torch.zeros_like(Xf)
         ctx.link.dXo = None
         dX = ops.mhc_pre_bwd_c(G.view(T, n, h), dXo.contiguous().view(T, n, h), Xc.view(T, n, h), dxin, coef, c1)
-        return (dX.view(B_, S, n, h), dA, dBw.to(B_w.dtype), dbias[0:4].to(b_pre.dtype), dbias[4:8].to(b_post.dtype),
-                dbias[8:24].view(4, 4).to(b_res.dtype), dbias[24:27].to(alphas.dtype), dnw.to(norm_w.dtype), None, None, None, None)
+        take = DEFERRED_GRADS.take
+        return (dX.view(B_, S, n, h), dA, take(B_w, dBw), take(b_pre, dbias[0:4]), take(b_post, dbias[4:8]), take(b_res, dbias[8:24]),
+                take(alphas, dbias[24:27]), take(norm_w, dnw), None, None, None, None)
 
 
 class _MhcPost(torch.autograd.Function):
@@ -316,7 +346,7 @@ class _ConvSilu(torch.autograd.Function):
     def backward(ctx, dy):
         xc, weight = ctx.saved_tensors
         dx, dw = load().conv_silu_bwd(xc, weight.float().reshape(weight.shape[0], -1).contiguous(), dy.contiguous())
-        return dx, dw.view(weight.shape).to(weight.dtype)
+        return dx, DEFERRED_GRADS.take(weight, dw)
 
 
 class _GdnScan(torch.autograd.Function):
@@ -433,7 +463,7 @@ class _GdnGates(torch.autograd.Function):
         dbeta = torch.zeros_like(b_raw) if dbeta is None else dbeta.to(torch.bfloat16).contiguous()
         dg = torch.zeros(b_raw.shape, dtype=torch.float32, device=b_raw.device) if dg is None else dg.float().contiguous()
         db, da, dA, dbias = load().gdn_gates_bwd(dbeta, dg, b_raw, a_raw, A_log.float().contiguous(), dt_bias.float().contiguous())
-        return db, da, dA.to(A_log.dtype), dbias.to(dt_bias.dtype)
+        return db, da, DEFERRED_GRADS.take(A_log, dA), DEFERRED_GRADS.take(dt_bias, dbias)
 
 
 class _SwiGLU(torch.autograd.Function):
@@ -514,7 +544,7 @@ class _HeadPrep(torch.autograd.Function):
             dgate = torch.zeros(src.shape[0], src.shape[1], src.shape[2] * 64, dtype=torch.bfloat16, device=src.device)
         dsrc, dw = load().qsa_headprep_bwd(dout.to(torch.bfloat16).contiguous(), dgate.to(torch.bfloat16).contiguous() if ctx.split else None,
                                            src, w, cos, sin, rstd)
-        return dsrc, (None if weight is None else dw.to(weight.dtype)), None, None, None
+        return dsrc, (None if weight is None else DEFERRED_GRADS.take(weight, dw)), None, None, None
 
 
 def _head_prep(src, norm, cos, sin):
@@ -560,7 +590,7 @@ class _NGramEmbed(torch.autograd.Function):
         g2 = emb2.grad if in_place else torch.zeros_like(emb2)
         g3 = emb3.grad if in_place else torch.zeros_like(emb3)
         dw = load().ngram_bwd(de.to(torch.bfloat16).contiguous(), rows, emb2, emb3, norm_w.float().contiguous(), rstd, g2, g3)
-        return None, (None if in_place else g2), (None if in_place else g3), dw.to(norm_w.dtype), None, None, None
+        return None, (None if in_place else g2), (None if in_place else g3), DEFERRED_GRADS.take(norm_w, dw), None, None, None
 
 
 class _Route(torch.autograd.Function):

@@ -341,17 +341,22 @@ class Trainer:
         self._graphs = {}
         self.replayed_launches = 0            # kernels of this library executed through graph replays
         if dev.type == "cuda":
-            from .ops.backend import WGRAD_STREAM
+            from .ops.backend import DEFERRED_GRADS, WGRAD_STREAM
             WGRAD_STREAM.enabled = bool(getattr(a, "overlap_wgrad", 1))   # weight gradients on a second stream during backward
+            # small-parameter gradients are added into the arena by one multi-tensor launch per backward (flushed where the
+            # weight-gradient stream is joined)
+            DEFERRED_GRADS.enabled = os.environ.get("Q38_DEFER_SMALL_GRADS", "1") != "0"
 
     def close(self):
         """Release peer mappings and detach the expert-parallel context from the kernel backend."""
         from .models import modeling
         backend = modeling.get_backend()
         if self.dev.type == "cuda":
-            from .ops.backend import WGRAD_STREAM
+            from .ops.backend import DEFERRED_GRADS, WGRAD_STREAM
             WGRAD_STREAM.join()
             WGRAD_STREAM.enabled = False
+            DEFERRED_GRADS.flush()
+            DEFERRED_GRADS.enabled = False
         if backend is not None and getattr(backend, "ep", None) is not None:
             backend.ep = None
         if backend is not None:
@@ -374,8 +379,9 @@ class Trainer:
     def _join_weight_gradients(self):
         """Weight-gradient GEMMs run on a second stream during backward (see q38.ops.backend._SideStream); wait for them."""
         if self.dev.type == "cuda":
-            from .ops.backend import WGRAD_STREAM
+            from .ops.backend import DEFERRED_GRADS, WGRAD_STREAM
             WGRAD_STREAM.join()
+            DEFERRED_GRADS.flush()
 
     def _captured_micro_step(self, x, y, accum, dense):
         """Forward + backward of one micro-step through a CUDA graph (captured on first use of this configuration).
