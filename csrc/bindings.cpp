@@ -7,6 +7,7 @@
 namespace q38 {
 std::atomic<long long> g_launches{0};
 at::Tensor qsa_first_query_lp(const at::Tensor& q_first, const at::Tensor& ki, const at::Tensor& w_first, double scale);   // qsa_first.cu
+bool gemm_bf16_pair(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, double alpha, bool accumulate, at::Tensor& err);   // gemm_pair.cu
 }
 
 TORCH_LIBRARY(q38, m) {
@@ -64,6 +65,8 @@ TORCH_LIBRARY(q38, m) {
   m.def("qsa_block_stats_tc(Tensor q, Tensor k, float scale, Tensor(a!) err) -> Tensor",
         [](const at::Tensor& q, const at::Tensor& k, double scale, at::Tensor& err) { return q38::qsa_block_stats_tc(q, k, scale, err); });
   m.def("qsa_indexer_fwd(Tensor qi, Tensor ki, Tensor wi, float scale) -> Tensor");
+  m.def("gemm_pair(Tensor a, Tensor b, Tensor(a!) c, float alpha, bool accumulate, Tensor(b!) err) -> bool",
+        [](const at::Tensor& a, const at::Tensor& b, at::Tensor& c, double alpha, bool acc, at::Tensor& err) { return q38::gemm_bf16_pair(a, b, c, alpha, acc, err); });
   m.def("qsa_first_query_lp(Tensor q_first, Tensor ki, Tensor w_first, float scale) -> Tensor", &q38::qsa_first_query_lp);
   m.def("qsa_kl_combine(Tensor? stats, Tensor blse, int nq) -> Tensor[]");
   m.def("qsa_select(Tensor lp_blk, int budget) -> Tensor[]");

@@ -336,6 +336,9 @@ static void launch_p(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   }
 }
 
+bool gemm_pair_enabled();                                                                                                         // gemm_pair.cu
+bool gemm_bf16_pair(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, double alpha, bool accumulate, at::Tensor& err);   // gemm_pair.cu
+
 // Same contract as gemm_bf16 (bf16 operands only).
 void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, bool a_mn_major, bool b_mn_major, double alpha,
                           bool accumulate, at::Tensor& err, int64_t splits, const c10::optional<at::Tensor>& addend, double beta) {
@@ -356,6 +359,10 @@ void gemm_bf16_persistent(const at::Tensor& a, const at::Tensor& b, at::Tensor& 
   const bool tma_out = c.stride(1) % c_vec == 0 && (reinterpret_cast<uintptr_t>(c.data_ptr()) & 15) == 0 && (batch == 1 || c.stride(0) % c_vec == 0);
   // bf16 outputs accumulate through the TMA unit only (cp.reduce.async.bulk.tensor adds in the tensor's element type)
   TORCH_CHECK(!accumulate || out_fp32 || (tma_out && !tf32 && !addend.has_value()), "accumulating into a bf16 output requires a TMA-storable output and no addend");
+  // K-major x K-major products with a TMA-storable output may run on SM pairs (cta_group::2, gemm_pair.cu) when switched on
+  if (gemm_pair_enabled() && !tf32 && !a_mn_major && !b_mn_major && tma_out && !addend.has_value() && (!accumulate || !out_fp32) &&
+      gemm_bf16_pair(a, b, c, alpha, accumulate, err))
+    return;
   int bn = pick_bn(N, tma_out ? 32 : 16);
   if (b_mn_major) bn = (bn + 63) / 64 * 64;                    // MN-major B is loaded in 64-wide boxes
   bn = std::min(bn, 256);

@@ -746,6 +746,28 @@ def test_first_query_indexer_log_probabilities(ops, B, S, NI):
     assert (got[:, ~causal] < -1e8).all()
 
 
+@pytest.mark.parametrize("M,N,K,batch", [(512, 256, 128, 1), (4096, 2240, 576, 1), (1000, 200, 72, 1), (768, 96, 320, 3)])
+def test_gemm_on_sm_pairs(ops, M, N, K, batch):
+    """The cta_group::2 kernel (two CTAs per 256-row tile, each loading half of B) against the fp32 product, for bf16 and fp32
+    outputs, a scale factor, ragged edges, batches and accumulation into a bf16 output."""
+    torch.manual_seed(43)
+    lib, err = ops.load(), ops.error_flag()
+    a = (0.1 * torch.randn(batch, M, K, device="cuda")).to(torch.bfloat16)
+    b = (0.1 * torch.randn(batch, N, K, device="cuda")).to(torch.bfloat16)
+    ref = torch.matmul(a.float(), b.float().transpose(1, 2))
+    out = torch.empty(batch, M, N, device="cuda", dtype=torch.bfloat16)
+    assert lib.gemm_pair(a, b, out, 1.0, False, err)
+    out32 = torch.empty(batch, M, N, device="cuda", dtype=torch.float32)
+    assert lib.gemm_pair(a, b, out32, 0.5, False, err)
+    before = out.clone()
+    assert lib.gemm_pair(a, b, out, 1.0, True, err)
+    ops.check_errors()
+    assert rel_err(before, ref) < 5e-3 and rel_err(out32, 0.5 * ref) < 1e-5
+    assert rel_err(out, before.float() + ref) < 5e-3
+    small = torch.empty(1, 128, 64, device="cuda", dtype=torch.bfloat16)
+    assert not lib.gemm_pair(a[:1, :128], b[:1, :64], small, 1.0, False, err)          # fewer than 256 rows: left to the one-CTA kernel
+
+
 def test_gemm_accumulates_into_bf16_output(ops):
     """`out += A B^T` with a bf16 output: the epilogue hands the tile to the TMA unit, which adds it in bf16."""
     torch.manual_seed(36)
