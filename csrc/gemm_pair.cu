@@ -239,9 +239,10 @@ __global__ void __launch_bounds__(G2_THREADS) gemm_pair_kernel(const __grid_cons
   if (warp == 1) ptx2::tmem_dealloc_pair(tmem_base, 512);
 }
 
+static bool g_pair_failed = false;            // a cluster launch was refused once: stay on the one-CTA kernel
 bool gemm_pair_enabled() {
-  static const bool on = [] { const char* v = std::getenv("Q38_GEMM_PAIR"); return v != nullptr && v[0] == '1'; }();
-  return on;
+  static const bool on = [] { const char* v = std::getenv("Q38_GEMM_PAIR"); return v == nullptr || v[0] != '0'; }();
+  return on && !g_pair_failed;
 }
 
 // C = alpha * A B^T (+ C) for K-major bf16 A [batch, M, K] and B [batch, N, K]; C bf16 or fp32, storable by TMA.  Returns false when
@@ -290,7 +291,10 @@ bool gemm_bf16_pair(const at::Tensor& a, const at::Tensor& b, at::Tensor& c, dou
       if (cudaOccupancyMaxActiveClusters(&n, k, &probe) != cudaSuccess || n < 1) { (void)cudaGetLastError(); n = kNumSMs / 2; } \
       resident = n; if (std::getenv("Q38_GEMM_TRACE")) std::fprintf(stderr, "[gemm_pair] resident clusters %d\n", n); } \
     cfg.gridDim = dim3(2 * std::max(1, std::min(p.work_items, resident))); \
-    C10_CUDA_CHECK(cudaLaunchKernelEx(&cfg, k, ta, tb, tc, p)); }
+    { const cudaError_t st = cudaLaunchKernelEx(&cfg, k, ta, tb, tc, p); \
+      if (st != cudaSuccess) { (void)cudaGetLastError(); g_pair_failed = true; \
+        std::fprintf(stderr, "[q38] SM-pair GEMM launch refused (%s; grid %u, %d bytes of shared memory): using the one-CTA kernel from here on\n", \
+                     cudaGetErrorString(st), cfg.gridDim.x, smem); return false; } } }
   if (out_fp32) { if (accumulate) Q38_PAIR(float, true) else Q38_PAIR(float, false) }
   else { if (accumulate) Q38_PAIR(__nv_bfloat16, true) else Q38_PAIR(__nv_bfloat16, false) }
 #undef Q38_PAIR
