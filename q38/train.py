@@ -385,6 +385,19 @@ class Trainer:
             WGRAD_STREAM.join()
             DEFERRED_GRADS.flush()
 
+    def _reset_generator_after_failed_capture(self):
+        """A capture that ends with an error leaves the device's random-number generator marked as capturing, and the next
+        `torch.randn` on the device raises.  A small capture that succeeds clears the mark."""
+        try:
+            probe = torch.zeros(8, device=self.dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                probe += 1
+            torch.cuda.synchronize(self.dev)
+            torch.randn(1, device=self.dev)
+        except Exception as exc:                             # pragma: no cover - depends on the driver
+            print(f"[q38.train] could not reset the generator after the failed capture ({type(exc).__name__})", flush=True)
+
     def _captured_micro_step(self, x, y, accum, dense):
         """Forward + backward of one micro-step through a CUDA graph (captured on first use of this configuration).
         Returns the 4 loss terms, or None when capture is unavailable and the caller should run eagerly."""
@@ -421,6 +434,7 @@ class Trainer:
                     traceback.print_exc()
                 self.use_graphs = False
                 torch.cuda.synchronize(self.dev)
+                self._reset_generator_after_failed_capture()
                 return None
             self._graphs[key] = entry
         graph, sx, sy, parts, launches = entry
