@@ -7,12 +7,12 @@
 //
 //   warp 0     TMA producer (both CTAs): loads its A tile and its half of B; the bytes are counted on the LEADER's `full` barrier
 //   warp 1     MMA issuer (leader CTA only): tcgen05.mma.cta_group::2 into one of two 256-column accumulators; each commit is
-//              sent to the barrier of both CTAs (two plain commits, one to the peer's address, no cluster multicast)
+//              sent to the barrier of both CTAs (two plain commits, one of them to the peer's cluster address)
 //   warps 2-9  epilogue (both CTAs, two warpgroups on alternate 32-column chunks): each CTA drains its own 128 accumulator rows
 //              from its own TMEM, stages 32 x 32 boxes in swizzled shared memory and hands them to the TMA unit; the accumulator
 //              is released on the leader's barrier
 //
-// No TMA load here uses cluster multicast.  Every wait is bounded and reports through the error word; both CTAs reach the
+// Every load is an ordinary tiled TMA load into the issuing CTA's own shared memory.  Every wait is bounded and reports through the error word; both CTAs reach the
 // cluster barrier at the end on every path, so neither exits while its peer can still touch its shared memory.
 #include <torch/extension.h>
 #include <ATen/cuda/CUDAContext.h>
