@@ -252,6 +252,11 @@ class GradEngine:
         self.optimizer.load_state_dict(opt_state)
         self.arena.refresh_shadow()
 
+    def check_canaries(self):
+        """Guard bytes after every peer-mapped buffer of this rank are intact (no-op without the peer-memory transport)."""
+        if self.transport is not None:
+            self.transport.check_canaries()
+
     def describe_transport(self):
         """'collective', or 'p2p' with the reduce-scatter algorithm and the allocation back end of the peer arenas."""
         if self.transport is None:

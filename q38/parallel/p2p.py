@@ -36,6 +36,8 @@ import torch.distributed as dist
 
 from .. import ops
 
+CANARY_BYTES, CANARY_BYTE = 256, 0xA5
+
 
 class PeerTransport:
     def __init__(self, device, rank, world, wait_seconds=20.0):
@@ -43,7 +45,8 @@ class PeerTransport:
         self.device, self.rank, self.world = torch.device(device), rank, world
         self.ops = ops.load()
         self.wait_seconds = float(os.environ.get("Q38_PEER_WAIT_SECONDS", wait_seconds))
-        self.local = {}          # name -> uint8 tensor owning the allocation
+        self.local = {}          # name -> uint8 tensor owning the allocation (payload + canary)
+        self._payload = {}       # name -> payload bytes (the canary follows)
         self.peers = {}          # name -> list of device pointers (own pointer at index rank)
         self.multicast = {}      # name -> multicast address of the buffer (0 when there is none)
         self.epoch = 0
@@ -77,15 +80,29 @@ class PeerTransport:
         return "ipc"
 
     def _alloc_raw(self, name, nbytes):
+        """A buffer of at least `nbytes` in peer-mappable memory, followed by a 256-byte canary: peers write into these buffers
+        by raw address (reduce-scatter staging, parameter all-gather), so an overrun would land in whatever the allocator put
+        next; `check_canaries` finds it instead."""
         nbytes = (nbytes + 255) // 256 * 256
+        total = nbytes + CANARY_BYTES
         if self.alloc_backend == "symm":
             import torch.distributed._symmetric_memory as symm_mem
-            buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+            buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
             buf.zero_()
         else:
-            buf = self.ops.p2p_alloc(nbytes, self.device.index)
+            buf = self.ops.p2p_alloc(total, self.device.index)
+        buf[nbytes:].fill_(CANARY_BYTE)
         self.local[name] = buf
-        return buf
+        self._payload[name] = nbytes
+        return buf[:nbytes]
+
+    def check_canaries(self):
+        """Raise if the guard bytes after any peer-mapped buffer of this rank were overwritten (by this rank or by a peer)."""
+        for name, buf in self.local.items():
+            tail = buf[self._payload[name]:]
+            if not bool((tail == CANARY_BYTE).all()):
+                bad = int((tail != CANARY_BYTE).nonzero()[0])
+                raise RuntimeError(f"peer buffer '{name}' of rank {self.rank} was overrun: guard byte {bad} after its {self._payload[name]} bytes changed")
 
     def allocate(self, numel, dtype):
         """Zero-filled flat tensor in peer-mappable memory (called by `ParamArena` for params, grads and shadow)."""
@@ -188,6 +205,7 @@ class PeerTransport:
         if not self.peers:
             return
         torch.cuda.synchronize(self.device)
+        self.check_canaries()
         if dist.is_initialized():
             dist.barrier()
         if self.alloc_backend == "ipc":

@@ -695,6 +695,7 @@ def main(argv=None):
             dist.all_gather_object(states, state)
         else:
             states[0] = state
+        trainer.engine.check_canaries()                                 # no peer wrote past the end of an arena since the last checkpoint
         model_state, opt_state = trainer.engine.checkpoint_state()      # collective: owners publish their optimizer shards
         if rank == 0:
             write_checkpoint({"model": model_state, "opt": opt_state, "step": step, "tok_seen": tok_seen,

@@ -62,6 +62,19 @@ def main():
         assert torch.equal(arena.shadow, arena.params.to(torch.bfloat16)), f"{mode}: bf16 shadow out of sync"
         assert losses[-1][0] < losses[0][0], (mode, losses)
         results[mode] = (params, losses)
+        transport = trainer.engine.transport
+        if transport is not None:
+            transport.check_canaries()                          # nothing wrote past the end of a peer-mapped buffer
+            if mode == "p2p":                                   # and the check does see a guard byte that changed
+                torch.cuda.synchronize()
+                guard = transport.local["grads"]
+                guard[-1] = 0
+                try:
+                    transport.check_canaries()
+                    raise AssertionError("a changed guard byte went unnoticed")
+                except RuntimeError as exc:
+                    assert "overrun" in str(exc)
+                guard[-1] = 0xA5
         trainer.close()
     for variant in ("p2p_pull", "p2p_push"):
         rel_v = ((results[variant][0] - results["collective"][0]).norm() / results["collective"][0].norm()).item()
