@@ -173,9 +173,9 @@ class _DeferredGrads:
     """Gradients of the small parameters (norm weights, conv taps, gate vectors, the mHC biases) collected during a backward pass
     and added into the parameters' gradient buffers by one multi-tensor launch at its end, instead of one `AccumulateGrad`
     addition kernel per parameter and micro-step (about 190 launches for q38_c2).  A backward that defers returns None for that
-    parameter.  Only the trainer enables it (Q38_DEFER_SMALL_GRADS=1), because whoever runs the backward must call `flush()`
-    afterwards (the trainer does so where it joins the weight-gradient stream); with `enabled` False, the default, every
-    gradient is returned to autograd as usual."""
+    parameter.  Only the trainer enables it (Q38_DEFER_SMALL_GRADS=0 keeps it off), because whoever runs the backward must call
+    `flush()` afterwards (the trainer does so where it joins the weight-gradient stream); with `enabled` False every gradient
+    is returned to autograd as usual."""
 
     def __init__(self):
         self.enabled = False

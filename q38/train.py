@@ -343,11 +343,9 @@ class Trainer:
         if dev.type == "cuda":
             from .ops.backend import DEFERRED_GRADS, WGRAD_STREAM
             WGRAD_STREAM.enabled = bool(getattr(a, "overlap_wgrad", 1))   # weight gradients on a second stream during backward
-            # Q38_DEFER_SMALL_GRADS=1: small-parameter gradients are added into the arena by one multi-tensor launch per backward
-            # (flushed where the weight-gradient stream is joined): +1 % on q38_c2.  Off by default: with it, the capture of a
-            # second micro-step graph in one trainer (the switch from the dense to the sparse phase) fails with
-            # cudaErrorStreamCaptureIsolation and the trainer continues without CUDA graphs; the cause is not found.
-            DEFERRED_GRADS.enabled = os.environ.get("Q38_DEFER_SMALL_GRADS", "0") == "1"
+            # small-parameter gradients are added into the arena by one multi-tensor launch per backward, flushed where the
+            # weight-gradient stream is joined (+1 % on q38_c2; Q38_DEFER_SMALL_GRADS=0 returns them to autograd one by one)
+            DEFERRED_GRADS.enabled = os.environ.get("Q38_DEFER_SMALL_GRADS", "1") != "0"
 
     def close(self):
         """Release peer mappings and detach the expert-parallel context from the kernel backend."""
@@ -417,6 +415,9 @@ class Trainer:
                         loss, _ = self.micro_loss(sx, sy, accum)
                         loss.backward()
                         self._join_weight_gradients()
+                        # drop the warm-up graph now: while it lives, the parameters' gradient accumulators stay bound to this
+                        # warm-up stream and the captured backward would run them there, outside the capturing stream
+                        del loss, _
                 torch.cuda.current_stream(self.dev).wait_stream(side)
                 from . import ops
                 graph = torch.cuda.CUDAGraph()
