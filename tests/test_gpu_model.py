@@ -186,3 +186,22 @@ def test_two_runs_from_the_same_state_agree():
     assert all(float(u) == float(v) for u, v in zip(list(a)[:4], list(b)[:4])), (a, b)      # ce, aux, mtp, kl of step 1: bit-identical
     delta = (finals[0] - finals[1]).abs()
     assert delta.max().item() <= 1e-2 and delta.mean().item() <= 2e-4, (delta.max().item(), delta.mean().item())
+
+
+def test_cuda_graphs_survive_the_phase_switch():
+    """A trainer captures one micro-step graph per attention phase; the second capture (dense -> sparse) must succeed too, with
+    the small-parameter gradients deferred to one multi-tensor launch, and both graphs must be replayed afterwards."""
+    from q38.train import TRAIN_DEFAULTS, Trainer
+    from q38 import ops
+    cfg, _ = build()
+    torch.manual_seed(0)
+    args = SimpleNamespace(**{**TRAIN_DEFAULTS, "aux_coef": 0.001, "lr": 3e-3, "grad_sync": "collective", "cuda_graphs": 1})
+    trainer = Trainer(cfg, args, torch.device("cuda", 0))
+    x = torch.randint(1, 512, (2, 256)).pin_memory()
+    y = x.roll(-1, 1).pin_memory()
+    losses = [trainer.read_step(trainer.train_step([(x, y)], lr=3e-3, dense=step < 2))[0] for step in range(6)]
+    ops.check_errors()
+    assert trainer.use_graphs and len(trainer._graphs) == 2 and trainer.replayed_launches > 0
+    assert losses[-1] < losses[0]
+    trainer.close()
+    torch.randn(4, device="cuda")                          # the device generator is usable after the captures
