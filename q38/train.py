@@ -344,7 +344,7 @@ class Trainer:
             from .ops.backend import DEFERRED_GRADS, WGRAD_STREAM
             WGRAD_STREAM.enabled = bool(getattr(a, "overlap_wgrad", 1))   # weight gradients on a second stream during backward
             # small-parameter gradients are added into the arena by one multi-tensor launch per backward, flushed where the
-            # weight-gradient stream is joined (+1 % on q38_c2; Q38_DEFER_SMALL_GRADS=0 returns them to autograd one by one)
+            # weight-gradient stream is joined (up to +1 % on q38_c2; Q38_DEFER_SMALL_GRADS=0 returns them to autograd one by one)
             DEFERRED_GRADS.enabled = os.environ.get("Q38_DEFER_SMALL_GRADS", "1") != "0"
 
     def close(self):
