@@ -140,3 +140,26 @@ def test_launcher_builds_loopback_torchrun_command():
     multi = command("q38.train", 8, 29511, ["--preset", "q38_c2"])
     assert single[1:3] == ["-m", "q38.train"]
     assert "--nproc-per-node=8" in multi and multi[multi.index("--master-addr") + 1] == "127.0.0.1" and multi[-2:] == ["--preset", "q38_c2"]
+
+
+def test_owner_assignment_balances_segments_and_newton_schulz_work():
+    """Owner-computes layout of q38_c2 on 8 ranks (shapes only, meta device): no rank's segment is more than 1.35 x the mean and no
+    rank's Newton-Schulz work more than 1.3 x the mean; balancing the Newton-Schulz FLOPs alone left both n-gram tables on two
+    ranks with segments of twice the mean."""
+    import torch
+    from q38.models import Q38ForCausalLM
+    from q38.optim.hybrid import split_parameters
+    from q38.parallel.arena import GROUPS, Unit, assign_owners, newton_schulz_flops
+    cfg = model_config(load_preset("q38_c2")["model"], 10112, 4096)
+    with torch.device("meta"):
+        model = Q38ForCausalLM(cfg)
+    groups = split_parameters(model, True)
+    for world in (2, 4, 8):
+        units = [Unit(n, p, g, i) for g, items in zip(GROUPS, groups) for i, (n, p) in enumerate(items)]
+        load = assign_owners(units, world)
+        sizes = [sum(u.numel for u in units if u.owner == r) for r in range(world)]
+        work = [sum(newton_schulz_flops(tuple(u.param.shape)) for u in units if u.owner == r and u.group == "muon") for r in range(world)]
+        assert max(sizes) <= 1.35 * sum(sizes) / world, (world, sizes)
+        assert max(work) <= 1.3 * sum(work) / world, (world, work)
+        assert max(load) <= 1.05 * sum(load) / world
+        assert {u.owner for u in units} == set(range(world))
