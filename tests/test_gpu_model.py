@@ -205,3 +205,27 @@ def test_cuda_graphs_survive_the_phase_switch():
     assert losses[-1] < losses[0]
     trainer.close()
     torch.randn(4, device="cuda")                          # the device generator is usable after the captures
+
+
+def test_activation_checkpointing_in_the_captured_step_matches():
+    """`--grad_ckpt 1` (per-layer recomputation, the q38_c4 preset's setting) inside the captured micro-step: the graphs are
+    captured and replayed, and three optimizer steps end where the run without recomputation ends (the recomputed forward is
+    the same arithmetic; the remaining difference is the atomic-accumulation noise of two separate runs)."""
+    from q38.train import TRAIN_DEFAULTS, Trainer
+    from q38 import ops
+    cfg, _ = build()
+    x = torch.randint(1, 512, (2, 256), generator=torch.Generator().manual_seed(3)).pin_memory()
+    y = x.roll(-1, 1).pin_memory()
+    finals, first = {}, {}
+    for ckpt in (0, 1):
+        torch.manual_seed(0)
+        args = SimpleNamespace(**{**TRAIN_DEFAULTS, "aux_coef": 0.001, "lr": 3e-3, "grad_sync": "collective", "cuda_graphs": 1, "grad_ckpt": ckpt})
+        trainer = Trainer(cfg, args, torch.device("cuda", 0))
+        losses = [trainer.read_step(trainer.train_step([(x, y)], lr=3e-3, dense=False)) for _ in range(3)]
+        assert trainer.use_graphs and trainer.replayed_launches > 0, ckpt
+        first[ckpt], finals[ckpt] = losses[0], trainer.engine.arena.params.clone()
+        trainer.close()
+    ops.check_errors()
+    assert all(abs(a - b) <= 1e-5 * abs(a) + 1e-7 for a, b in zip(first[0][:4], first[1][:4])), (first[0], first[1])
+    delta = (finals[0] - finals[1]).abs()
+    assert delta.max().item() <= 1e-2 and delta.mean().item() <= 2e-4, (delta.max().item(), delta.mean().item())
