@@ -229,3 +229,25 @@ def test_activation_checkpointing_in_the_captured_step_matches():
     assert all(abs(a - b) <= 1e-5 * abs(a) + 1e-7 for a, b in zip(first[0][:4], first[1][:4])), (first[0], first[1])
     delta = (finals[0] - finals[1]).abs()
     assert delta.max().item() <= 1e-2 and delta.mean().item() <= 2e-4, (delta.max().item(), delta.mean().item())
+
+
+def test_inference_forward_matches_cpu_specification():
+    """Evaluation mode (`no_grad`, sparse attention with block selection from the first query of every block, scored by the
+    selection-only kernel): the next-token cross-entropy of the kernel path in bf16 agrees with the fp32 specification on the CPU."""
+    from q38 import ops
+    import torch.nn.functional as F
+    ops.install()
+    cfg, cpu_model = build(seq=512)
+    gpu_model = copy.deepcopy(cpu_model).cuda()
+    gpu_model.tie_embeddings()
+    gpu_model.model.compute_dtype = torch.bfloat16
+    ids = torch.randint(1, 512, (2, 512), generator=torch.Generator().manual_seed(9))
+    losses = {}
+    for name, model, batch in (("cpu", cpu_model, ids), ("gpu", gpu_model, ids.cuda())):
+        model.eval()
+        with torch.no_grad():
+            logits = model(input_ids=batch, use_cache=False).logits.float()
+        assert logits.shape == (2, 512, cfg.vocab_size) and torch.isfinite(logits).all()
+        losses[name] = F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).cpu(), ids[:, 1:].reshape(-1)).item()
+    ops.check_errors()
+    assert abs(losses["gpu"] - losses["cpu"]) <= 2e-2 * losses["cpu"], losses
