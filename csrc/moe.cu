@@ -87,20 +87,23 @@ __global__ void __launch_bounds__(256) moe_route_bwd_kernel(const float* __restr
   const int e0 = lane, e1 = lane + 32;
   const float p0 = e0 < E ? probs[(size_t)t * E + e0] : 0.f, p1 = e1 < E ? probs[(size_t)t * E + e1] : 0.f;
   float dp0 = (d_prob_sum && e0 < E) ? d_prob_sum[e0] : 0.f, dp1 = (d_prob_sum && e1 < E) ? d_prob_sum[e1] : 0.f;
+  // lane j < K holds slot j (expert id and incoming gradient), read once; the three passes below take them by shuffle instead
+  // of re-reading global memory in every iteration (the dependent loads were what this kernel waited for)
+  const int my_e = lane < K ? top_idx[(size_t)t * K + lane] : 0;
+  const float my_dw = lane < K ? d_top_w[(size_t)t * K + lane] : 0.f;
   float s = 0.f, dot = 0.f;
   for (int j = 0; j < K; ++j) {
-    const int e = top_idx[(size_t)t * K + j];
-    const float pe = __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);
-    s += pe;
+    const int e = __shfl_sync(0xffffffffu, my_e, j);
+    s += __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);
   }
   for (int j = 0; j < K; ++j) {
-    const int e = top_idx[(size_t)t * K + j];
+    const int e = __shfl_sync(0xffffffffu, my_e, j);
     const float pe = __shfl_sync(0xffffffffu, e < 32 ? p0 : p1, e & 31);
-    dot += d_top_w[(size_t)t * K + j] * (pe / s);          // unrounded weight for the derivative
+    dot += __shfl_sync(0xffffffffu, my_dw, j) * (pe / s);          // unrounded weight for the derivative
   }
   for (int j = 0; j < K; ++j) {
-    const int e = top_idx[(size_t)t * K + j];
-    const float g = (d_top_w[(size_t)t * K + j] - dot) / s;
+    const int e = __shfl_sync(0xffffffffu, my_e, j);
+    const float g = (__shfl_sync(0xffffffffu, my_dw, j) - dot) / s;
     if (e == e0) dp0 += g;
     if (e == e1) dp1 += g;
   }
