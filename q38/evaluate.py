@@ -165,9 +165,8 @@ def main(argv=None):
     n_steps = math.ceil(n_seq / global_bs)
 
     model = load_hf(a.model_path, dtype=torch.bfloat16 if use_cuda else torch.float32, device=device)
-    if use_cuda:
-        from . import ops
-        print(f"Kernel backend: {ops.install()}", flush=True)
+    from .inference import optimize_for_inference
+    print(f"Inference fast paths: {optimize_for_inference(model)}", flush=True)
     n_active = active_parameter_count(model)
     if n_active <= 0:
         raise ValueError("Non-vocabulary active parameter count must be positive")

@@ -202,3 +202,17 @@ def test_muon_orthogonalises_and_batches():
     Muon([p], lr=0.01).step()
     step = (p.detach() - before * (1 - 0.01 * 0.1)).norm() / before.numel() ** 0.5
     assert abs(step.item() / (0.01 * 0.2) - 1) < 0.4          # RMS of a semi-orthogonal update is 1/sqrt(max dim): step RMS ~ 0.2 lr
+
+
+def test_reference_import_paths_and_inference_entry_point(tiny_config):
+    """The import paths a user of the reference has in their scripts resolve here: the model package, the optimizer module and
+    `optimize_for_inference`, which on a CPU model only switches to evaluation mode and reports the module counts."""
+    from q38.inference import compile_inference_norms, optimize_for_inference
+    from q38.models.qwen3_8_moe import Qwen3_8MoeForCausalLM, Qwen3_8MoeTextConfig, source_info
+    from q38.muon import HybridOptimizer as FromOldPath
+    assert FromOldPath is HybridOptimizer and Qwen3_8MoeTextConfig is type(tiny_config)
+    assert Qwen3_8MoeForCausalLM.__name__ == "Qwen3_8MoeForCausalLM" and set(source_info()["files"]) == {"modeling_qwen3_8_moe.py", "configuration_qwen3_8_moe.py"}
+    model = Q38ForCausalLM(tiny_config).train()
+    info = optimize_for_inference(model)
+    assert not model.training and info["backend"] is None and info["mhc"] == 2 * tiny_config.num_hidden_layers
+    assert info["norms"] == compile_inference_norms(model) > 0 and info["gated_deltanet"] >= 3
