@@ -33,6 +33,7 @@ SHARED_CACHE = Path("/home/shared/qwen35_moe_sparse/cache/isoflops-gzy10k-16b-v1
 DEFAULT_DATA = SHARED_CACHE / "train.bin"
 DEFAULT_VAL_DATA = SHARED_CACHE / "valid.bin"
 MAX_CHARS_PER_CALL = 100_000          # very long documents are tokenised in slices of this many characters
+CHUNK_CHARS = MAX_CHARS_PER_CALL      # the reference's name for the same constant (q38/data.py:30)
 DOCS_PER_CALL = 512
 METADATA_FILES = ("meta.json", "parts_manifest.json", "manifest.json")
 

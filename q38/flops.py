@@ -18,6 +18,7 @@ from dataclasses import dataclass
 
 MEGATRON_COMMIT = "b92c3ed70029005fd5769d2cf4c65bc3d061a74b"
 BACKBONE_METHOD = "megatron_b92c3ed_plus_router_shared_gate_v1"
+ACCOUNTING_METHOD = BACKBONE_METHOD            # the name the reference exports for the backbone convention (q38/flops.py:11)
 Q38_METHOD = "q38_sparse_mhc_ngram_mtp_v2"
 QSA_BLOCK = 64
 

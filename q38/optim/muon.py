@@ -22,6 +22,7 @@ import torch
 
 NS_COEFFICIENTS = (3.4445, -4.7750, 2.0315)
 MAX_BATCH_ELEMENTS = 64 * 1024 * 1024      # bound on the temporaries of one batched Newton-Schulz call
+MUON_MAX_CHUNK_ELEMENTS = MAX_BATCH_ELEMENTS  # the reference's name for the same bound (q38/muon.py:9)
 
 
 @torch.no_grad()

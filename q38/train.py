@@ -295,6 +295,31 @@ def pick_device(name="auto", local_rank=0):
     return torch.device("cuda", local_rank)
 
 
+def gdn_kernel():
+    """Where the chunked gated delta rule runs on a GPU: this library's kernels (the reference returns the FLA modules here and
+    raises when the slow PyTorch fallback would be used, q38/train.py:267-273; so does this)."""
+    from . import ops
+    if not torch.cuda.is_available():
+        raise RuntimeError("chunk_gated_delta_rule would run on the PyTorch fallback: no CUDA device")
+    ops.load()
+    return ["q38.ops (csrc/gdn.cu: gdn_prep_fwd/bwd, gdn_scan_fwd/bwd)"]
+
+
+def install_fast_paths(model):
+    """The reference's name for switching a model to its training fast paths (q38/train.py:285-308).  Here the fast paths are
+    the process-wide kernel backend behind the model file's hooks: it is installed when the model is on a GPU, and the same
+    kind of summary is returned."""
+    from .inference import compile_inference_norms
+    parameter = next(model.parameters())
+    experts = "reference (PyTorch)"
+    if parameter.is_cuda:
+        from . import ops
+        ops.install()
+        experts = "grouped tcgen05 kernels"
+    gdn = sum(type(m).__name__ == "Qwen3_8MoeGatedDeltaNet" for m in model.modules())
+    return dict(experts=experts, gated_deltanet=gdn, norms=compile_inference_norms(model))
+
+
 def build_model(cfg, dev, grad_ckpt=False):
     """fp32 master weights on `dev`; on a GPU the sm_100a kernel backend is installed and activations run in bf16."""
     model = Q38ForCausalLM(cfg).to(dev, dtype=torch.float32)

@@ -209,7 +209,13 @@ def test_reference_import_paths_and_inference_entry_point(tiny_config):
     `optimize_for_inference`, which on a CPU model only switches to evaluation mode and reports the module counts."""
     from q38.inference import compile_inference_norms, optimize_for_inference
     from q38.models.qwen3_8_moe import Qwen3_8MoeForCausalLM, Qwen3_8MoeTextConfig, source_info
-    from q38.muon import HybridOptimizer as FromOldPath
+    from q38.muon import HybridOptimizer as FromOldPath, MUON_MAX_CHUNK_ELEMENTS
+    from q38.train import LossModel as FromTrain, gdn_kernel, install_fast_paths
+    from q38.flops import ACCOUNTING_METHOD
+    from q38.data import CHUNK_CHARS
+    assert (MUON_MAX_CHUNK_ELEMENTS, CHUNK_CHARS, ACCOUNTING_METHOD) == (64 * 1024 * 1024, 100_000, "megatron_b92c3ed_plus_router_shared_gate_v1")
+    assert FromTrain is LossModel and callable(gdn_kernel)
+    assert install_fast_paths(Q38ForCausalLM(tiny_config))["experts"] == "reference (PyTorch)"
     assert FromOldPath is HybridOptimizer and Qwen3_8MoeTextConfig is type(tiny_config)
     assert Qwen3_8MoeForCausalLM.__name__ == "Qwen3_8MoeForCausalLM" and set(source_info()["files"]) == {"modeling_qwen3_8_moe.py", "configuration_qwen3_8_moe.py"}
     model = Q38ForCausalLM(tiny_config).train()
