@@ -115,6 +115,38 @@ def manifest(runs):
     return dict(version=1, pool=POOL, runs=rows)
 
 
+def checks(runs):
+    """What was verified about the archive, recomputed every time it is generated (the reference keeps a hand-filled
+    ``checks.json`` beside its archive)."""
+    from .utils.audit_flops import MEGATRON_COMMIT, backbone_report
+    report = backbone_report(SEQ, VOCAB)
+    shortfall = max(c["accounting"]["compute_shortfall_fraction"] for c in runs.values())
+    deviation = [row["megatron_reaccounted_budget_fraction"] for row in report["archived_configs"]]
+    return dict(main_configs=len(runs), flops_accounting=next(iter(runs.values()))["accounting"]["accounting_method"], megatron_commit=MEGATRON_COMMIT,
+                megatron_formula_crosscheck_passed=not report["failures"], crosschecked_configs=len(report["archived_configs"]),
+                crosschecked_canonical_shapes=len(report["canonical_family"]),
+                original_megatron_function_evaluated=report["reference"]["original_function_evaluated"],
+                maximum_budget_shortfall_percent=100 * shortfall,
+                megatron_reference_budget_deviation_percent=[100 * min(deviation), 100 * max(deviation)],
+                training_started=False, gpu_benchmark_performed=False)
+
+
+README = """# Q35 IsoFLOPs sweep (archive)
+
+The 19 runs that preceded the Q38 presets: the backbone-only architecture at four compute budgets (1e16, 3e16, 1e17, 3e17 FLOPs),
+every width of the one-parameter family whose tokens per active parameter fall in [4, 400].  Generated by
+`python -m q38.make_isoflops` from the rules in its docstring; `--check` verifies that the files still are what the rules give.
+
+    <budget>/<shape>/config.json   one run: model shape, training settings, accounting
+    manifest.json                  one row per run
+    validation.json                the frozen validation split (dev / curve / report token ranges)
+    results.json                   measured outcomes of the completed runs; the scaling fit in `q38/make_configs.py` reads them
+    checks.json                    what was verified when the archive was generated
+
+The runs are history: they train the backbone without the Q38 additions and are not launched from this repository.
+"""
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--check", action="store_true", help="recompute and compare with the files on disk")
@@ -123,13 +155,24 @@ def main(argv=None):
     files = {ARCHIVE / budget / name / "config.json": config for (budget, name), config in runs.items()}
     files[ARCHIVE / "manifest.json"] = manifest(runs)
     files[ARCHIVE / "validation.json"] = VALIDATION
-    for path, content in files.items():
+    readme = ARCHIVE / "README.md"
+    if a.check:
+        if not readme.exists() or readme.read_text() != README:
+            raise SystemExit(f"Generated file differs: {readme}")
+    else:
+        ARCHIVE.mkdir(parents=True, exist_ok=True)
+        readme.write_text(README)
+    def emit(path, content):
         if a.check:
             if not path.exists() or json.loads(path.read_text()) != content:
                 raise SystemExit(f"Generated file differs: {path}")
         else:
             path.parent.mkdir(parents=True, exist_ok=True)
             path.write_text(json.dumps(content, indent=2, ensure_ascii=False) + "\n")
+
+    for path, content in files.items():
+        emit(path, content)
+    emit(ARCHIVE / "checks.json", checks(runs))              # last: the checks read the config files from disk
     for (budget, name), config in runs.items():
         acc = config["accounting"]
         print(f"{budget} {name}: Na={acc['active_nonvocab_params']:,} D={acc['train_tokens']:,} D/Na={acc['tokens_per_active_param']:.1f} "
