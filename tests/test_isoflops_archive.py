@@ -41,3 +41,14 @@ def test_published_figures_of_the_sweep_are_reproduced():
     for key, (per_token, tokens, steps, warmup, params) in PUBLISHED.items():
         row = rows[key]
         assert (row["train_flops_per_token"], row["train_tokens"], row["steps"], row["warmup_steps"], row["total_params"]) == (per_token, tokens, steps, warmup, params)
+
+
+def test_recomputed_checks_reproduce_the_published_ones():
+    """`checks.json` is recomputed from the FLOPs audit; its budget figures equal the ones published with the reference's
+    archive (configs/q35_isoflops/checks.json there)."""
+    checks = json.loads((ROOT / "configs/q35_isoflops/checks.json").read_text())
+    assert checks["main_configs"] == checks["crosschecked_configs"] == 19 and checks["crosschecked_canonical_shapes"] == 24
+    assert checks["megatron_formula_crosscheck_passed"] is True
+    assert abs(checks["maximum_budget_shortfall_percent"] - 0.0652218892287948) < 1e-12
+    low, high = checks["megatron_reference_budget_deviation_percent"]
+    assert abs(low + 0.7315429477580793) < 1e-9 and abs(high + 0.45544902819839583) < 1e-9
