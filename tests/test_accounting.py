@@ -163,3 +163,12 @@ def test_owner_assignment_balances_segments_and_newton_schulz_work():
         assert max(work) <= 1.3 * sum(work) / world, (world, work)
         assert max(load) <= 1.05 * sum(load) / world
         assert {u.owner for u in units} == set(range(world))
+
+
+def test_committed_audit_files_are_what_the_tools_generate(tmp_path):
+    from q38 import make_configs
+    from q38.utils import audit_flops
+    assert audit_flops.main(["--backbone", "--output", str(tmp_path / "flops_audit.json")]) == 0
+    make_configs.main(["--check", "--plan", str(tmp_path / "q38_config_plan.json")])
+    for name in ("flops_audit.json", "q38_config_plan.json"):
+        assert json.loads((tmp_path / name).read_text()) == json.loads((ROOT / "audits" / name).read_text()), name
